@@ -1,0 +1,302 @@
+#!/usr/bin/env python3
+"""Benchmark of the Qwen3-0.6B decode path on B200: microseconds per decode step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (`config.workload`): batch-1 greedy decode with the benchmark's weights (bf16 N(0, 0.02)
+matrices, unit RMSNorm gains, seeded), a KV cache built by prefilling 128 uniform-random token ids,
+then K consecutive steps starting at position 128; the cache grows on the device and each step's
+argmax feeds the next.  One "step" = one decode step.  With N GPUs every rank runs its own replica of
+that stream (no inter-GPU traffic), the time is the maximum over ranks.
+
+One JSON line is printed by rank 0.  `value` is the device-timed figure with everything resident in
+HBM; `e2e` is the same stream driven from host memory (token in from pinned memory, token out to the
+host, one synchronisation per step).  `--impl reference` times the CPU restatement of the reference's
+fp32 decode step (oracle/) on the host cores for the same workload, a bounded number of steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (str(ROOT), str(ROOT / "qwen3-megakernel_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+CTX0 = 128
+PUBLISHED_US = 373.6        # the reference kernel's steady microseconds per step on one B200 (its README)
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(ctx: int, layers: int = 28, vocab: int = 151936) -> int:
+    """HBM bytes one batch-1 decode step must move at cache length `ctx`: every weight once, the norm
+    gains, the cached K/V rows, the embedding row, the logits and the new K/V rows."""
+    per_layer_w = (2048 * 1024 + 2 * 1024 * 1024 + 1024 * 2048 + 2 * 3072 * 1024 + 1024 * 3072) * 2
+    weights = layers * per_layer_w + vocab * 1024 * 2
+    gains = layers * (1024 * 2 + 128 * 2) * 2 + 1024 * 2
+    kv_read = layers * ctx * 8 * 128 * 2 * 2
+    per_seq = 1024 * 2 + vocab * 4 + layers * 8 * 128 * 2 * 2
+    return weights + gains + kv_read + per_seq
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Polls NVML for the SM clock and the throttle reasons while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+        self._period = period_s
+
+    def _run(self):
+        nv = self._nv
+        names = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake_slowdown": 0x80, "sw_power_cap": 0x4}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for n, b in names.items():
+                    if bits & b:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(self._period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def build_workload(device, seed: int = 0):
+    """Weights on `device` and the 128-position cache prefilled on the GPU from seeded random ids."""
+    from qwen3mk import prefill, weights
+
+    w = weights.baseline_init(seed, device)
+    g = torch.Generator().manual_seed(seed + 1)
+    ids = torch.randint(0, 151936, (CTX0,), generator=g)
+    kc, vc, last = prefill.prefill(w, ids, device)
+    inputs = dict(w)
+    inputs.update(token=last.argmax().to(torch.int64).reshape(()), kcache=kc, vcache=vc)
+    return inputs, ids
+
+
+def cpu_baseline(seconds: float = 12.0, seed: int = 0) -> dict:
+    """The oracle's decode step on the host cores: same weights and cache length, a bounded number of steps."""
+    from oracle import qwen3_oracle as O
+
+    w = O.baseline_init(seed)
+    w32 = O.to_fp32(w)
+    g = torch.Generator().manual_seed(seed + 1)
+    kc = (torch.randn(28, CTX0, 8, 128, generator=g) * 0.1).to(torch.bfloat16)
+    vc = (torch.randn(28, CTX0, 8, 128, generator=g) * 0.1).to(torch.bfloat16)
+    tok = 1234
+    O.decode_step(w32, tok, kc, vc)  # warm-up
+    times = []
+    t_end = time.perf_counter() + seconds
+    while time.perf_counter() < t_end and len(times) < 200:
+        t0 = time.perf_counter()
+        out = O.decode_step(w32, tok, kc, vc)
+        times.append(time.perf_counter() - t0)
+        tok = int(out["next_token"])
+    return {"value": statistics.median(times) * 1e6, "unit": "us/step", "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": "port",
+            "sample": f"{len(times)} decode steps at position {CTX0} (fp32 torch on the host, median)"}
+
+
+def run_reference_arm(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 64))
+    from oracle import qwen3_oracle as O
+
+    w32 = O.to_fp32(O.baseline_init(0))
+    g = torch.Generator().manual_seed(1)
+    kc = (torch.randn(28, CTX0, 8, 128, generator=g) * 0.1).to(torch.bfloat16)
+    vc = (torch.randn(28, CTX0, 8, 128, generator=g) * 0.1).to(torch.bfloat16)
+    tok = 1234
+    for _ in range(max(1, min(args.warmup, 3))):
+        O.decode_step(w32, tok, kc, vc)
+    t0 = time.perf_counter()
+    res = O.greedy_decode(w32, tok, kc, vc, steps)
+    dt = time.perf_counter() - t0
+    us = dt / steps * 1e6
+    assert res["tokens"].numel() == steps
+    line = {"impl": "reference", "metric": "us_per_step_qwen3_0.6b_bs1_ctx128", "value": us, "unit": "us/step",
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": us / 1e3,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "bs1 greedy decode from position 128, cache grows on the host", "steps_sampled": steps},
+            "cpu_baseline": {"value": us, "unit": "us/step", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
+                             "kind": "port", "sample": f"{steps} greedy steps from position {CTX0}"},
+            "e2e": {"value": us, "unit": "us/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "tokens_per_s": 1e6 / us, "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--path", choices=["auto", "layered", "persist"], default="auto")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return 0
+
+    import torch.distributed as dist
+
+    from qwen3mk import Megakernel
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    K, W = args.steps, max(args.warmup, 3)
+
+    inputs, _ = build_workload(dev)
+    mk = Megakernel(dev, path=args.path, max_positions=max(8192, CTX0 + K + W + 8))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident: W warm-up steps, then exactly K chained steps on a fresh cache ------------
+    mk.bind(inputs, chained=True, grow=W)
+    for _ in range(W):
+        mk.launch()
+    torch.cuda.synchronize(dev)
+    mk.bind(inputs, chained=True, grow=K)
+    n0 = mk.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(K):
+            mk.launch()
+        e1.record()
+        barrier()
+    launches = mk.launch_count - n0
+    mk.status()
+    ms = e0.elapsed_time(e1)
+    last_token = int(mk.chain_token)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    us_step = ms * 1e3 / K
+
+    # ---- end to end from host memory: token H2D, step, token D2H, every step -------------------------
+    Ke = min(K, 128)
+    e2e_inputs = dict(inputs, token=inputs["token"].clone())   # the token buffer below is rewritten every step
+    mk.bind(e2e_inputs, chained=False, grow=Ke + 3)
+    tok_host = torch.empty(1, dtype=torch.int64).pin_memory()
+    out_host = torch.empty(1, dtype=torch.int64).pin_memory()
+    tok_dev = mk._tok[0]
+    bound = mk._out
+    tok_host[0] = int(inputs["token"])
+    t0 = time.perf_counter()
+    for i in range(3 + Ke):
+        if i == 3:
+            barrier()
+            t0 = time.perf_counter()
+        tok_dev.copy_(tok_host, non_blocking=True)
+        mk.launch()
+        out_host.copy_(bound[1].reshape(1), non_blocking=True)
+        torch.cuda.synchronize(dev)
+        tok_host[0] = out_host[0]
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t[0])
+    e2e_us = e2e_s / Ke * 1e6
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    mean_ctx = CTX0 + (K - 1) / 2.0
+    bytes_step = algorithmic_bytes(int(round(mean_ctx)))
+    peak, peak_kind = measured_peak_gbs()
+    achieved = bytes_step / (us_step * 1e-6) / 1e9
+    launches_per_step = launches / K
+    grid = mk.grid
+    line = {
+        "metric": "us_per_step_qwen3_0.6b_bs1_ctx128", "value": us_step, "unit": "us/step", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": us_step / 1e3, "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": us_step / PUBLISHED_US, "dtype": "bf16 weights, fp32 activations and accumulation",
+        "data": "synthetic",
+        "config": {"workload": f"Qwen3-0.6B bs1 greedy decode, {K} consecutive steps from position {CTX0} "
+                               f"(cache {CTX0 + 1}->{CTX0 + K} positions, grows on the device)",
+                   "weights": "bf16 N(0,0.02), RMSNorm gains 1, seed 0", "cache": "prefill of 128 uniform-random ids on the GPU",
+                   "replicas": world, "path": args.path, "launches_per_step": launches_per_step,
+                   "persistent_grid": grid, "l2": "inputs larger than L2: 1.19 GB of weights streamed every step"},
+        "tokens_per_s": world * 1e6 / us_step,
+        "hbm_frac_of_8tbs": bytes_step / (us_step * 1e-6) / 1e9 / NOMINAL_HBM_GBS,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "algorithmic_bytes_per_step": bytes_step,
+                     "kernel": "q3_persist_decode (one launch per step)" if launches_per_step <= 1.5 else
+                               f"whole step ({launches_per_step:.0f} launches)"},
+        "e2e": {"value": e2e_us, "unit": "us/step", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8, "steps": Ke},
+        "gpu_launches": launches, "clocks": clk.summary(), "last_token": last_token,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,150 @@
+/*
+ * q3mk.h — C ABI of the B200 (sm_100a) Qwen3-0.6B decode / prefill engine.
+ *
+ * This is the boundary a host language binds.  Plain pointers and sizes only; no C++ or
+ * torch types.  Every function returns Q3_OK (0) or a negative error code and never throws.
+ * All pointers named "device" are CUDA device addresses on the engine's GPU; the caller owns
+ * every input and output buffer, the engine owns only its scratch (allocated in q3_create).
+ *
+ * It replaces the reference project's host->device boundary, which is a Python class driving
+ * one NVRTC-compiled kernel through the CUDA driver API:
+ *     qwen3mk/kernel.py:109-233   class Megakernel (step / bind / launch / _launch)
+ *     csrc/qwen3_step.cu:382-394  extern "C" __global__ qwen3_step(25 pointers)
+ * Tensor layouts are the reference's (qwen3mk/kernel.py:27-50): bf16 weights in Hugging Face
+ * [out, in] row-major order stacked over layers, fp32 logits, int64 tokens, bf16 K/V rows.
+ *
+ * Model geometry is fixed to Qwen3-0.6B per head/row: hidden 1024, 16 query heads, 8 KV heads,
+ * head dim 128, FFN 3072, RoPE theta 1e6, eps 1e-6.  The layer count and vocabulary size are
+ * run-time values (28 and 151936 for the real model) so that small models can be tested.
+ */
+#ifndef Q3MK_H
+#define Q3MK_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q3_OK                 0
+#define Q3_ERR_INVALID       (-1)  /* bad argument (message in q3_last_error)               */
+#define Q3_ERR_CUDA          (-2)  /* a CUDA runtime call failed                            */
+#define Q3_ERR_NOT_RESIDENT  (-3)  /* the persistent grid cannot be co-resident on the GPU  */
+#define Q3_ERR_DEVICE_WAIT   (-4)  /* a bounded device-side wait gave up (see q3_status)    */
+#define Q3_ERR_UNSUPPORTED   (-5)  /* valid request this build cannot serve on that path    */
+
+/* q3_decode_args.flags */
+#define Q3_F_APPEND_KV    0x1u  /* write the new K/V rows into cache slot seq_len[b], then seq_len[b] += 1 */
+#define Q3_F_PATH_AUTO    0x0u  /* engine picks: persistent kernel for small batches, layered otherwise    */
+#define Q3_F_PATH_LAYERED 0x10u /* one launch per phase (debug ladder, large batches)                      */
+#define Q3_F_PATH_PERSIST 0x20u /* one persistent cooperative launch per step                              */
+#define Q3_F_PATH_MASK    0xf0u
+
+typedef struct q3_engine q3_engine; /* opaque */
+
+typedef struct q3_config {
+    int32_t n_layers;       /* 28 for Qwen3-0.6B                                                 */
+    int32_t vocab;          /* 151936 for Qwen3-0.6B; must be >= 1                               */
+    int32_t max_batch;      /* largest q3_decode_args.batch the scratch is sized for (>= 1)      */
+    int32_t max_tokens;     /* largest q3_prefill_args.n_tokens the scratch is sized for (0: no prefill) */
+    int32_t grid_limit;     /* 0 = one CTA per SM; otherwise cap the persistent grid (tests)     */
+    int32_t reserved;
+} q3_config;
+
+/* The 13 weight tensors, device pointers to bf16.  Replaces slots 1..13 of the reference's
+ * kernel argument list (qwen3mk/kernel.py:23-24, csrc/qwen3_step.cu:383-391). */
+typedef struct q3_weights {
+    const void* ln1;    /* [L, 1024]          */
+    const void* wq;     /* [L, 2048, 1024]    */
+    const void* wk;     /* [L, 1024, 1024]    */
+    const void* wv;     /* [L, 1024, 1024]    */
+    const void* qn;     /* [L, 128]           */
+    const void* kn;     /* [L, 128]           */
+    const void* wo;     /* [L, 1024, 2048]    */
+    const void* ln2;    /* [L, 1024]          */
+    const void* wg;     /* [L, 3072, 1024]    */
+    const void* wu;     /* [L, 3072, 1024]    */
+    const void* wd;     /* [L, 1024, 3072]    */
+    const void* fnorm;  /* [1024]             */
+    const void* embed;  /* [vocab, 1024], also the (tied) LM head */
+} q3_weights;
+
+/* One decode step for `batch` independent sequences.  Generalises the reference's fixed
+ * batch-1 / position-128 launch (qwen3mk/kernel.py:180-191): sequence b decodes position
+ * seq_len[b] against seq_len[b] cached positions.  The per-sequence descriptors live in device
+ * memory so that back-to-back launches need no host work. */
+typedef struct q3_decode_args {
+    int32_t batch;                   /* 1..max_batch                                                   */
+    int32_t max_len;                 /* host-side upper bound of seq_len[b] for this call (work split) */
+    uint32_t flags;                  /* Q3_F_*                                                         */
+    uint32_t reserved;
+    const int64_t* token;            /* device [batch]  input token ids                                */
+    const uint64_t* seq_k;           /* device [batch]  address of sequence b's K cache, bf16 [L][cap_b][8][128] */
+    const uint64_t* seq_v;           /* device [batch]  same for V                                     */
+    const int64_t* seq_layer_stride; /* device [batch]  elements between consecutive layers (cap_b * 1024) */
+    int32_t* seq_len;                /* device [batch]  cached positions = position of this token; written only with Q3_F_APPEND_KV */
+    float* logits;                   /* device [batch, vocab] fp32, or NULL                            */
+    int64_t* next_token;             /* device [batch]  argmax, ties -> lowest index                   */
+    void* k_write;                   /* device bf16 [batch, L, 8, 128] or NULL (K after head norm + RoPE) */
+    void* v_write;                   /* device bf16 [batch, L, 8, 128] or NULL                         */
+} q3_decode_args;
+
+/* Causal prefill of one prompt: replaces qwen3mk/prefill.py:46-81 (fp32 torch loop) by GPU kernels. */
+typedef struct q3_prefill_args {
+    int32_t n_tokens;        /* 1..max_tokens                                        */
+    int32_t cache_capacity;  /* positions per layer in kcache/vcache (>= n_tokens)   */
+    const int64_t* ids;      /* device [n_tokens]                                    */
+    void* kcache;            /* device bf16 [L, cache_capacity, 8, 128], slots [0, n_tokens) written */
+    void* vcache;            /* device bf16 [L, cache_capacity, 8, 128]              */
+    float* last_logits;      /* device [vocab] fp32, logits of the last position, or NULL */
+    int64_t* next_token;     /* device [1] argmax of last_logits, or NULL            */
+} q3_prefill_args;
+
+/* Create an engine on CUDA device `device` (makes it current).  Replaces Megakernel.__init__
+ * (qwen3mk/kernel.py:120-162): occupancy check, scratch, sync words. */
+int q3_create(int device, const q3_config* cfg, q3_engine** out);
+
+/* Free the engine's scratch.  Safe on NULL. */
+void q3_destroy(q3_engine* e);
+
+/* Record the weight pointers used by later calls (borrowed, never written).  Replaces the
+ * pointer marshalling of Megakernel.step / bind (qwen3mk/kernel.py:185-188,203-206). */
+int q3_set_weights(q3_engine* e, const q3_weights* w);
+
+/* RoPE table: device fp32 [n_positions][128], row p = cos(p * f_0..f_63) then sin(p * f_0..f_63),
+ * f_i = 1e6^(-2i/128).  Generalises the reference's single-position table
+ * (qwen3mk/kernel.py:102-106).  Borrowed. */
+int q3_set_rope(q3_engine* e, const float* table, int32_t n_positions);
+
+/* Enqueue one decode step on `stream` (a cudaStream_t; NULL = default stream).  No host sync.
+ * Replaces Megakernel._launch (qwen3mk/kernel.py:231-233). */
+int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream);
+
+/* Enqueue a causal prefill on `stream`. */
+int q3_prefill(q3_engine* e, const q3_prefill_args* a, void* stream);
+
+/* Synchronise `stream`, read the device status words and clear them.  Returns Q3_OK or
+ * Q3_ERR_DEVICE_WAIT; `words` (may be NULL) receives up to `n` raw status words:
+ * [0] error code, [1] where (phase id), [2] CTA index, [3] observed counter value. */
+int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n);
+
+/* Number of kernel launches this engine has enqueued since creation. */
+int64_t q3_launch_count(const q3_engine* e);
+
+/* Persistent-grid geometry chosen at creation: CTAs, threads per CTA, dynamic smem bytes. */
+int q3_grid_info(const q3_engine* e, int32_t* ctas, int32_t* threads, int32_t* smem_bytes);
+
+/* Engine-owned scratch for tools and tests: name in {"x","qkv","attn","hid","status"}; returns a
+ * device pointer and its size in bytes, or Q3_ERR_INVALID. */
+int q3_scratch(const q3_engine* e, const char* name, void** ptr, int64_t* bytes);
+
+/* Message of the last error on this engine (or of the last failed q3_create when e == NULL). */
+const char* q3_last_error(const q3_engine* e);
+
+/* Library version string, e.g. "q3mk-b200 0.1 sm_100a". */
+const char* q3_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q3MK_H */

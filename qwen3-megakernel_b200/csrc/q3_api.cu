@@ -1,0 +1,301 @@
+// C ABI of the engine (declared in include/q3mk.h): engine life cycle, argument checks, path
+// selection and the per-step launch sequence of the layered path.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "q3_engine.h"
+
+using namespace q3;
+
+static char g_create_error[512] = "";
+
+int q3::engine_fail(q3_engine* e, int code, const char* fmt, ...) {
+    char* dst = e ? e->err : g_create_error;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(dst, 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+#define fail q3::engine_fail
+
+#define CU(e, call)                                                                                  \
+    do {                                                                                             \
+        cudaError_t err__ = (call);                                                                  \
+        if (err__ != cudaSuccess)                                                                    \
+            return fail(e, Q3_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(err__), __FILE__, __LINE__); \
+    } while (0)
+
+static int alloc(q3_engine* e, void** p, size_t bytes) {
+    CU(e, cudaMalloc(p, bytes));
+    CU(e, cudaMemset(*p, 0, bytes));
+    return Q3_OK;
+}
+
+extern "C" const char* q3_version(void) { return "q3mk-b200 0.1 sm_100a"; }
+
+extern "C" const char* q3_last_error(const q3_engine* e) { return e ? e->err : g_create_error; }
+
+extern "C" int q3_create(int device, const q3_config* cfg, q3_engine** out) {
+    if (!cfg || !out) return fail(nullptr, Q3_ERR_INVALID, "q3_create: null argument");
+    *out = nullptr;
+    if (cfg->n_layers < 1 || cfg->vocab < 1 || cfg->max_batch < 1 || cfg->max_tokens < 0 || cfg->grid_limit < 0)
+        return fail(nullptr, Q3_ERR_INVALID, "q3_create: n_layers=%d vocab=%d max_batch=%d max_tokens=%d grid_limit=%d out of range",
+                    cfg->n_layers, cfg->vocab, cfg->max_batch, cfg->max_tokens, cfg->grid_limit);
+    CU(nullptr, cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CU(nullptr, cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(nullptr, Q3_ERR_UNSUPPORTED, "q3_create: device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+
+    q3_engine* e = new (std::nothrow) q3_engine();
+    if (!e) return fail(nullptr, Q3_ERR_INVALID, "q3_create: out of host memory");
+    memset(e, 0, sizeof(*e));
+    e->device = device;
+    e->cfg = *cfg;
+    e->sm_count = prop.multiProcessorCount;
+    e->max_splits = Q3_MAX_SPLITS;
+    e->lm_grid = e->sm_count * 8;
+    const size_t B = (size_t)cfg->max_batch;
+    int rc;
+    if ((rc = alloc(e, (void**)&e->x, B * HIDDEN * 4)) ||
+        (rc = alloc(e, (void**)&e->qkv, B * QKV_DIM * 4)) ||
+        (rc = alloc(e, (void**)&e->attn, B * Q_DIM * 4)) ||
+        (rc = alloc(e, (void**)&e->hid, B * INTER * 4)) ||
+        (rc = alloc(e, (void**)&e->part, B * Q_HEADS * e->max_splits * ATTN_PART_STRIDE * 4)) ||
+        (rc = alloc(e, (void**)&e->pval, B * e->lm_grid * 4)) ||
+        (rc = alloc(e, (void**)&e->pidx, B * e->lm_grid * 4)) ||
+        (rc = alloc(e, (void**)&e->status, Q3_STATUS_WORDS * 4)) ||
+        (rc = alloc(e, (void**)&e->sync, Q3_SYNC_WORDS * 4)) ||
+        (rc = alloc(e, (void**)&e->pf_desc, 64))) {
+        strncpy(g_create_error, e->err, sizeof(g_create_error) - 1);
+        q3_destroy(e);
+        return rc;
+    }
+    rc = persist_setup(e);
+    if (rc != Q3_OK) {
+        strncpy(g_create_error, e->err, sizeof(g_create_error) - 1);
+        q3_destroy(e);
+        return rc;
+    }
+    *out = e;
+    return Q3_OK;
+}
+
+extern "C" void q3_destroy(q3_engine* e) {
+    if (!e) return;
+    cudaSetDevice(e->device);
+    persist_teardown(e);
+    void* bufs[] = {e->x, e->qkv, e->attn, e->hid, e->part, e->pval, e->pidx, e->status, e->sync, e->pf_desc};
+    for (void* p : bufs)
+        if (p) cudaFree(p);
+    delete e;
+}
+
+extern "C" int q3_set_weights(q3_engine* e, const q3_weights* w) {
+    if (!e || !w) return fail(e, Q3_ERR_INVALID, "q3_set_weights: null argument");
+    const void* const* p = reinterpret_cast<const void* const*>(w);
+    static const char* names[13] = {"ln1", "wq", "wk", "wv", "qn", "kn", "wo", "ln2", "wg", "wu", "wd", "fnorm", "embed"};
+    for (int i = 0; i < 13; ++i) {
+        if (!p[i]) return fail(e, Q3_ERR_INVALID, "q3_set_weights: %s is null", names[i]);
+        if (reinterpret_cast<uintptr_t>(p[i]) & 15) return fail(e, Q3_ERR_INVALID, "q3_set_weights: %s is not 16-byte aligned", names[i]);
+    }
+    e->w = *w;
+    e->have_weights = 1;
+    return Q3_OK;
+}
+
+extern "C" int q3_set_rope(q3_engine* e, const float* table, int32_t n_positions) {
+    if (!e || !table || n_positions < 1) return fail(e, Q3_ERR_INVALID, "q3_set_rope: bad argument");
+    e->rope = table;
+    e->rope_n = n_positions;
+    return Q3_OK;
+}
+
+extern "C" int64_t q3_launch_count(const q3_engine* e) { return e ? e->launches : 0; }
+
+extern "C" int q3_grid_info(const q3_engine* e, int32_t* ctas, int32_t* threads, int32_t* smem_bytes) {
+    if (!e) return Q3_ERR_INVALID;
+    if (ctas) *ctas = e->p_grid;
+    if (threads) *threads = e->p_threads;
+    if (smem_bytes) *smem_bytes = e->p_smem;
+    return Q3_OK;
+}
+
+extern "C" int q3_scratch(const q3_engine* e, const char* name, void** ptr, int64_t* bytes) {
+    if (!e || !name || !ptr || !bytes) return Q3_ERR_INVALID;
+    const int64_t B = e->cfg.max_batch;
+    if (!strcmp(name, "x")) { *ptr = e->x; *bytes = B * HIDDEN * 4; }
+    else if (!strcmp(name, "qkv")) { *ptr = e->qkv; *bytes = B * QKV_DIM * 4; }
+    else if (!strcmp(name, "attn")) { *ptr = e->attn; *bytes = B * Q_DIM * 4; }
+    else if (!strcmp(name, "hid")) { *ptr = e->hid; *bytes = B * INTER * 4; }
+    else if (!strcmp(name, "status")) { *ptr = e->status; *bytes = Q3_STATUS_WORDS * 4; }
+    else return Q3_ERR_INVALID;
+    return Q3_OK;
+}
+
+extern "C" int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n) {
+    if (!e) return Q3_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t h[Q3_STATUS_WORDS];
+    CU(e, cudaStreamSynchronize(st));
+    CU(e, cudaMemcpy(h, e->status, sizeof(h), cudaMemcpyDeviceToHost));
+    for (int i = 0; words && i < n && i < Q3_STATUS_WORDS; ++i) words[i] = h[i];
+    if (h[0] == 0) return Q3_OK;
+    // leave the engine reusable: clear the status and the barrier words
+    CU(e, cudaMemset(e->status, 0, Q3_STATUS_WORDS * 4));
+    CU(e, cudaMemset(e->sync, 0, Q3_SYNC_WORDS * 4));
+    return fail(e, Q3_ERR_DEVICE_WAIT, "device status: code %u at site %u, CTA %u, value %u", h[0], h[1], h[2], h[3]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// layered decode step
+// ------------------------------------------------------------------------------------------------
+static int splits_for(const q3_engine* e, int batch, int max_len) {
+    const int n = max_len + 1;
+    int by_len = (n + 31) / 32;                                   // at least 32 positions per split
+    int by_fill = (2 * e->sm_count + KV_HEADS * batch - 1) / (KV_HEADS * batch);  // ~2 blocks per SM
+    int s = by_len < by_fill ? by_len : by_fill;
+    if (s < 1) s = 1;
+    if (s > e->max_splits) s = e->max_splits;
+    return s;
+}
+
+static int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
+    const int B = a->batch, L = e->cfg.n_layers, V = e->cfg.vocab;
+    const q3_weights& w = e->w;
+    const int append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
+    const int ns = splits_for(e, B, a->max_len);
+    auto bf = [](const void* p) { return reinterpret_cast<const bf16_raw*>(p); };
+#define LAUNCH(call)                                                                                   \
+    do {                                                                                               \
+        cudaError_t err__ = (call);                                                                    \
+        ++e->launches;                                                                                 \
+        if (err__ != cudaSuccess) return fail(e, Q3_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(err__)); \
+    } while (0)
+
+    LAUNCH(launch_embed(reinterpret_cast<const long long*>(a->token), bf(w.embed), V, e->x, e->status, B, st));
+    for (int l = 0; l < L; ++l) {
+        GemvArgs g{};
+        // qkv = rms(x, ln1) @ [wq; wk; wv]^T
+        g.seg[0] = {bf(w.wq) + (size_t)l * Q_DIM * HIDDEN, Q_DIM};
+        g.seg[1] = {bf(w.wk) + (size_t)l * KV_DIM * HIDDEN, KV_DIM};
+        g.seg[2] = {bf(w.wv) + (size_t)l * KV_DIM * HIDDEN, KV_DIM};
+        g.x = e->x; g.ldx = HIDDEN; g.gain = bf(w.ln1) + (size_t)l * HIDDEN;
+        g.out = e->qkv; g.ldo = QKV_DIM; g.n_rows = QKV_DIM; g.batch = B;
+        LAUNCH(launch_gemv(1024, EPI_STORE, g, QKV_DIM / 16, st));
+
+        HeadPrepArgs h{};
+        h.qkv = e->qkv; h.qn = bf(w.qn); h.kn = bf(w.kn); h.rope = e->rope; h.seq_len = a->seq_len;
+        h.k_write = reinterpret_cast<bf16_raw*>(a->k_write); h.v_write = reinterpret_cast<bf16_raw*>(a->v_write);
+        h.seq_k = a->seq_k; h.seq_v = a->seq_v; h.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
+        h.layer = l; h.n_layers = L; h.append = append;
+        LAUNCH(launch_head_prep(h, B, st));
+
+        AttnArgs t{};
+        t.qkv = e->qkv; t.seq_k = a->seq_k; t.seq_v = a->seq_v;
+        t.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
+        t.seq_len = a->seq_len; t.part = e->part; t.layer = l; t.n_splits = ns;
+        LAUNCH(launch_attn(t, e->attn, B, st));
+        ++e->launches;  // launch_attn is two kernels
+
+        // x += attn @ wo^T
+        g = GemvArgs{};
+        g.seg[0] = {bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN};
+        g.x = e->attn; g.ldx = Q_DIM; g.out = e->x; g.ldo = HIDDEN; g.resid = e->x; g.ldr = HIDDEN;
+        g.n_rows = HIDDEN; g.batch = B;
+        LAUNCH(launch_gemv(2048, EPI_RESID, g, HIDDEN / 16, st));
+
+        // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
+        g = GemvArgs{};
+        g.seg[0] = {bf(w.wg) + (size_t)l * INTER * HIDDEN, INTER};
+        g.w2 = bf(w.wu) + (size_t)l * INTER * HIDDEN;
+        g.x = e->x; g.ldx = HIDDEN; g.gain = bf(w.ln2) + (size_t)l * HIDDEN;
+        g.out = e->hid; g.ldo = INTER; g.n_rows = INTER; g.batch = B;
+        LAUNCH(launch_gemv(1024, EPI_SILU, g, INTER / 8, st));
+
+        // x += hid @ wd^T
+        g = GemvArgs{};
+        g.seg[0] = {bf(w.wd) + (size_t)l * HIDDEN * INTER, HIDDEN};
+        g.x = e->hid; g.ldx = INTER; g.out = e->x; g.ldo = HIDDEN; g.resid = e->x; g.ldr = HIDDEN;
+        g.n_rows = HIDDEN; g.batch = B;
+        LAUNCH(launch_gemv(3072, EPI_RESID, g, HIDDEN / 16, st));
+    }
+    // logits = rms(x, fnorm) @ embed^T ; next_token = argmax
+    GemvArgs g{};
+    g.seg[0] = {bf(w.embed), V};
+    g.x = e->x; g.ldx = HIDDEN; g.gain = bf(w.fnorm);
+    g.out = a->logits; g.ldo = V; g.n_rows = V; g.batch = B; g.pval = e->pval; g.pidx = e->pidx;
+    int lm_grid = (V + 15) / 16;
+    if (lm_grid > e->lm_grid) lm_grid = e->lm_grid;
+    LAUNCH(launch_gemv(1024, EPI_LOGITS, g, lm_grid, st));
+    LAUNCH(launch_argmax_final(e->pval, e->pidx, lm_grid, reinterpret_cast<long long*>(a->next_token), a->seq_len, append, B, st));
+#undef LAUNCH
+    return Q3_OK;
+}
+
+extern "C" int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream) {
+    if (!e || !a) return fail(e, Q3_ERR_INVALID, "q3_decode: null argument");
+    if (!e->have_weights) return fail(e, Q3_ERR_INVALID, "q3_decode: call q3_set_weights first");
+    if (!e->rope) return fail(e, Q3_ERR_INVALID, "q3_decode: call q3_set_rope first");
+    if (a->batch < 1 || a->batch > e->cfg.max_batch)
+        return fail(e, Q3_ERR_INVALID, "q3_decode: batch %d outside 1..%d", a->batch, e->cfg.max_batch);
+    if (a->max_len < 0 || a->max_len >= e->rope_n)
+        return fail(e, Q3_ERR_INVALID, "q3_decode: max_len %d needs a RoPE table of more than %d rows (have %d)", a->max_len, a->max_len, e->rope_n);
+    if (!a->token || !a->seq_k || !a->seq_v || !a->seq_layer_stride || !a->seq_len || !a->next_token)
+        return fail(e, Q3_ERR_INVALID, "q3_decode: token, seq_k, seq_v, seq_layer_stride, seq_len and next_token are required");
+    CU(e, cudaSetDevice(e->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t path = a->flags & Q3_F_PATH_MASK;
+    if (path == Q3_F_PATH_AUTO) path = persist_supports(e, a) ? Q3_F_PATH_PERSIST : Q3_F_PATH_LAYERED;
+    if (path == Q3_F_PATH_PERSIST) {
+        if (!persist_supports(e, a))
+            return fail(e, Q3_ERR_UNSUPPORTED, "q3_decode: the persistent kernel does not serve batch %d", a->batch);
+        return persist_decode(e, a, st);
+    }
+    if (path != Q3_F_PATH_LAYERED) return fail(e, Q3_ERR_INVALID, "q3_decode: unknown path flag 0x%x", path);
+    return decode_layered(e, a, st);
+}
+
+// Prefill by sequential decode: position t attends the t rows already appended to the cache.
+// Exact causal attention with bf16-rounded cached rows; the tensor-core prefill replaces this loop
+// for long prompts but keeps the entry point.
+static int prefill_sequential(q3_engine* e, const q3_prefill_args* a, cudaStream_t st) {
+    struct Desc { uint64_t k, v; long long stride; int len; int pad; long long tok; } h;
+    h.k = reinterpret_cast<uint64_t>(a->kcache);
+    h.v = reinterpret_cast<uint64_t>(a->vcache);
+    h.stride = (long long)a->cache_capacity * KV_DIM;
+    h.len = 0; h.pad = 0; h.tok = 0;
+    CU(e, cudaMemcpyAsync(e->pf_desc, &h, sizeof(h), cudaMemcpyHostToDevice, st));
+    char* d = reinterpret_cast<char*>(e->pf_desc);
+    for (int t = 0; t < a->n_tokens; ++t) {
+        const bool last = (t == a->n_tokens - 1);
+        q3_decode_args s{};
+        s.batch = 1; s.max_len = t; s.flags = Q3_F_APPEND_KV | Q3_F_PATH_LAYERED;
+        s.token = a->ids + t;
+        s.seq_k = reinterpret_cast<const uint64_t*>(d);
+        s.seq_v = reinterpret_cast<const uint64_t*>(d + 8);
+        s.seq_layer_stride = reinterpret_cast<const int64_t*>(d + 16);
+        s.seq_len = reinterpret_cast<int32_t*>(d + 24);
+        s.logits = last ? a->last_logits : nullptr;
+        s.next_token = (last && a->next_token) ? a->next_token : reinterpret_cast<int64_t*>(d + 32);
+        int rc = decode_layered(e, &s, st);
+        if (rc != Q3_OK) return rc;
+    }
+    return Q3_OK;
+}
+
+extern "C" int q3_prefill(q3_engine* e, const q3_prefill_args* a, void* stream) {
+    if (!e || !a) return fail(e, Q3_ERR_INVALID, "q3_prefill: null argument");
+    if (!e->have_weights) return fail(e, Q3_ERR_INVALID, "q3_prefill: call q3_set_weights first");
+    if (!e->rope) return fail(e, Q3_ERR_INVALID, "q3_prefill: call q3_set_rope first");
+    if (a->n_tokens < 1 || a->n_tokens > e->cfg.max_tokens)
+        return fail(e, Q3_ERR_INVALID, "q3_prefill: n_tokens %d outside 1..max_tokens (%d)", a->n_tokens, e->cfg.max_tokens);
+    if (a->cache_capacity < a->n_tokens) return fail(e, Q3_ERR_INVALID, "q3_prefill: cache_capacity %d < n_tokens %d", a->cache_capacity, a->n_tokens);
+    if (a->n_tokens > e->rope_n) return fail(e, Q3_ERR_INVALID, "q3_prefill: RoPE table has %d rows, need %d", e->rope_n, a->n_tokens);
+    if (!a->ids || !a->kcache || !a->vcache) return fail(e, Q3_ERR_INVALID, "q3_prefill: ids, kcache and vcache are required");
+    CU(e, cudaSetDevice(e->device));
+    return prefill_sequential(e, a, (cudaStream_t)stream);
+}

@@ -1,0 +1,48 @@
+// Engine state shared by the translation units behind the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/q3mk.h"
+#include "q3_common.cuh"
+#include "q3_layered.h"
+
+#define Q3_STATUS_WORDS 8
+#define Q3_SYNC_WORDS 64
+#define Q3_MAX_SPLITS 64
+
+struct q3_engine {
+    int device;
+    q3_config cfg;
+    q3_weights w;
+    int have_weights;
+    const float* rope;  // [rope_n, 128]
+    int rope_n;
+    int sm_count;
+    int max_splits;     // attention splits the partial buffer is sized for
+    int lm_grid;        // LM-head blocks the argmax partial buffers are sized for
+    // scratch (device)
+    float* x;       // [max_batch, 1024]  residual stream
+    float* qkv;     // [max_batch, 4096]
+    float* attn;    // [max_batch, 2048]
+    float* hid;     // [max_batch, 3072]
+    float* part;    // [max_batch, 16, max_splits, ATTN_PART_STRIDE]
+    float* pval;    // [max_batch, lm_grid]
+    int* pidx;      // [max_batch, lm_grid]
+    uint32_t* status;
+    uint32_t* sync;
+    void* pf_desc;  // 64 bytes: sequence descriptor + token slot used by q3_prefill
+    // persistent kernel geometry
+    int p_grid, p_threads, p_smem;
+    void* p_state;  // owned by q3_persist.cu
+    int64_t launches;
+    char err[512];
+};
+
+namespace q3 {
+int persist_setup(q3_engine* e);
+void persist_teardown(q3_engine* e);
+bool persist_supports(const q3_engine* e, const q3_decode_args* a);
+int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st);
+int engine_fail(q3_engine* e, int code, const char* fmt, ...);
+}  // namespace q3

@@ -1,0 +1,443 @@
+// Layered decode path: one launch per phase of the decode step.
+//
+// This is the path for batches too large for the persistent kernel's register-resident
+// activations, and the debugging ladder the persistent kernel is compared against: the same
+// arithmetic (bf16 weights, fp32 activations and accumulation), one phase per kernel, with
+// kernel boundaries as the only synchronisation.
+//
+// Phases per layer (reference: csrc/qwen3_step.cu:531-772, semantics qwen3mk/reference.py:61-82):
+//   gemv<RMS, STORE>      qkv  = rms(x, ln1) @ [wq; wk; wv]^T
+//   head_prep             q, k = rope(rms_head(.)), K/V rows written (bf16), optional cache append
+//   attn_split, attn_merge  softmax(q K^T / sqrt(128)) V over cached positions + the new one
+//   gemv<RESID>           x   += attn @ wo^T
+//   gemv<RMS, SILU>       hid  = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
+//   gemv<RESID>           x   += hid @ wd^T
+// and once per step: embed gather, gemv<RMS, LOGITS> (tied LM head) + argmax.
+
+#include "q3_common.cuh"
+#include "q3_layered.h"
+
+namespace q3 {
+
+// ------------------------------------------------------------------------------------------------
+// embedding gather: x[b, :] = float(embed[token[b], :])            (csrc/qwen3_step.cu:514-519)
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) embed_kernel(const long long* __restrict__ token,
+                                                    const bf16_raw* __restrict__ embed, int vocab,
+                                                    float* __restrict__ x, uint32_t* status) {
+    const int b = blockIdx.x;
+    long long t = token[b];
+    if (t < 0 || t >= vocab) {
+        if (threadIdx.x == 0) report(status, ST_BAD_TOKEN, 0, (uint32_t)t);
+        t = 0;
+    }
+    const uint2* row = reinterpret_cast<const uint2*>(embed + (size_t)t * HIDDEN);
+    const uint2 v = row[threadIdx.x];  // 4 bf16
+    float4 o = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
+    reinterpret_cast<float4*>(x + (size_t)b * HIDDEN)[threadIdx.x] = o;
+}
+
+// ------------------------------------------------------------------------------------------------
+// skinny GEMM: out[b, n] = sum_k act[b, k] * W[n, k] for a tile of BT sequences, CUDA cores.
+// ------------------------------------------------------------------------------------------------
+template <int K, int EPI, int BT>
+__global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
+    extern __shared__ __align__(16) float xs[];  // [BT][K], lane-interleaved
+    __shared__ float red[8];
+    __shared__ float rscale[BT];
+    __shared__ float s_bv[8][BT];
+    __shared__ int s_bi[8][BT];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b0 = blockIdx.y * BT;
+
+    // stage the activations; with a gain vector, apply RMSNorm: (x * rsqrt(mean(x^2) + eps)) * gain
+#pragma unroll
+    for (int bb = 0; bb < BT; ++bb) {
+        const int b = b0 + bb;
+        float ss = 0.f;
+        for (int e = tid; e < K; e += 256) {
+            const float v = (b < a.batch) ? a.x[(size_t)b * a.ldx + e] : 0.f;
+            ss = fmaf(v, v, ss);
+            xs[bb * K + act_slot(e)] = v;
+        }
+        if (a.gain != nullptr) {
+            ss = block_sum<8>(ss, red);
+            if (tid == 0) rscale[bb] = rsqrtf(ss / (float)K + EPS);
+        }
+    }
+    __syncthreads();
+    if (a.gain != nullptr) {
+#pragma unroll
+        for (int bb = 0; bb < BT; ++bb) {
+            const float r = rscale[bb];
+            for (int e = tid; e < K; e += 256) {
+                const int s = bb * K + act_slot(e);
+                xs[s] = (xs[s] * r) * bf_to_f(a.gain[e]);
+            }
+        }
+        __syncthreads();
+    }
+
+    float bestv[BT];
+    int besti[BT];
+#pragma unroll
+    for (int bb = 0; bb < BT; ++bb) { bestv[bb] = -INFINITY; besti[bb] = 0x7fffffff; }
+
+    // Each warp owns two weight rows per iteration.  For EPI_SILU these are the gate row and the
+    // up row of the same output; otherwise two consecutive output rows.
+    constexpr int OUT_PER_IT = (EPI == EPI_SILU) ? 1 : 2;
+    const int gw = blockIdx.x * 8 + warp, nw = gridDim.x * 8;
+    for (int n0 = gw * OUT_PER_IT; n0 < a.n_rows; n0 += nw * OUT_PER_IT) {
+        const uint4* rp[2];
+        if (EPI == EPI_SILU) {
+            rp[0] = reinterpret_cast<const uint4*>(a.seg[0].w + (size_t)n0 * K);
+            rp[1] = reinterpret_cast<const uint4*>(a.w2 + (size_t)n0 * K);
+        } else {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                int n = min(n0 + r, a.n_rows - 1);
+                const bf16_raw* base = a.seg[0].w;
+                if (n >= a.seg[0].rows) {
+                    n -= a.seg[0].rows;
+                    base = a.seg[1].w;
+                    if (n >= a.seg[1].rows) { n -= a.seg[1].rows; base = a.seg[2].w; }
+                }
+                rp[r] = reinterpret_cast<const uint4*>(base + (size_t)n * K);
+            }
+        }
+        float acc[2][BT];
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int bb = 0; bb < BT; ++bb) acc[r][bb] = 0.f;
+
+#pragma unroll
+        for (int c = 0; c < K / 1024; ++c) {
+            uint4 w[2][4];
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[r][j] = ld_stream(rp[r] + c * 128 + j * 32 + lane);
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int bb = 0; bb < BT; ++bb)
+                        acc[r][bb] += dot8(w[r][j], xs + bb * K + c * 1024, j, lane);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int bb = 0; bb < BT; ++bb) acc[r][bb] = warp_sum(acc[r][bb]);
+
+        if (lane == 0) {
+#pragma unroll
+            for (int bb = 0; bb < BT; ++bb) {
+                const int b = b0 + bb;
+                if (b >= a.batch) continue;
+                if (EPI == EPI_SILU) {
+                    const float g = acc[0][bb], u = acc[1][bb];
+                    a.out[(size_t)b * a.ldo + n0] = (g / (1.f + expf(-g))) * u;
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        const int n = n0 + r;
+                        if (n >= a.n_rows) continue;
+                        float v = acc[r][bb];
+                        if (EPI == EPI_RESID) v += a.resid[(size_t)b * a.ldr + n];
+                        if (EPI != EPI_LOGITS || a.out != nullptr) a.out[(size_t)b * a.ldo + n] = v;
+                        if (EPI == EPI_LOGITS && v > bestv[bb]) { bestv[bb] = v; besti[bb] = n; }
+                    }
+                }
+            }
+        }
+    }
+
+    if (EPI == EPI_LOGITS) {
+        // per-block argmax partial; ties -> lowest index
+        if (lane == 0) {
+#pragma unroll
+            for (int bb = 0; bb < BT; ++bb) { s_bv[warp][bb] = bestv[bb]; s_bi[warp][bb] = besti[bb]; }
+        }
+        __syncthreads();
+        if (tid < BT && b0 + tid < a.batch) {
+            float bv = s_bv[0][tid];
+            int bi = s_bi[0][tid];
+            for (int w = 1; w < 8; ++w) {
+                const float v = s_bv[w][tid];
+                const int i = s_bi[w][tid];
+                if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+            }
+            a.pval[(size_t)(b0 + tid) * gridDim.x + blockIdx.x] = bv;
+            a.pidx[(size_t)(b0 + tid) * gridDim.x + blockIdx.x] = bi;
+        }
+    }
+}
+
+// final argmax over per-block partials; optional seq_len[b] += 1 (the step's last kernel)
+__global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx,
+                                                           int nblk, long long* __restrict__ next_token,
+                                                           int* seq_len, int append) {
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < nblk; i += 256) {
+        const float v = pval[(size_t)b * nblk + i];
+        const int ix = pidx[(size_t)b * nblk + i];
+        if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+    }
+    sv[tid] = bv;
+    si[tid] = bi;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (tid < o) {
+            const float v = sv[tid + o];
+            const int ix = si[tid + o];
+            if (v > sv[tid] || (v == sv[tid] && ix < si[tid])) { sv[tid] = v; si[tid] = ix; }
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        next_token[b] = si[0];
+        if (append) seq_len[b] += 1;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// head_prep: per-head RMSNorm + RoPE on q and k; K/V rows out (bf16); optional cache append.
+// grid (24, B): blocks 0..15 = q heads, 16..23 = kv heads.  128 threads = head dims.
+// (csrc/qwen3_step.cu:597-629; qwen3mk/reference.py:66-75)
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) head_prep_kernel(const HeadPrepArgs a) {
+    __shared__ float red[4];
+    __shared__ float nv[HEAD_DIM];
+    const int hb = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const bool is_q = hb < Q_HEADS;
+    const int g = hb - Q_HEADS;
+    float* src = a.qkv + (size_t)b * QKV_DIM + (is_q ? hb * HEAD_DIM : Q_DIM + g * HEAD_DIM);
+    const bf16_raw* gain = (is_q ? a.qn : a.kn) + (size_t)a.layer * HEAD_DIM;
+    const int pos = a.seq_len[b];
+    const float v = src[d];
+    const float ss = block_sum<4>(v * v, red);
+    const float n = (v * rsqrtf(ss / (float)HEAD_DIM + EPS)) * bf_to_f(gain[d]);
+    nv[d] = n;
+    __syncthreads();
+    const float* tab = a.rope + (size_t)pos * HEAD_DIM;
+    const float c = tab[d & 63], s = tab[64 + (d & 63)];
+    const float rot = (d < 64) ? -nv[d + 64] : nv[d - 64];
+    const float o = n * c + rot * s;
+    src[d] = o;
+    if (!is_q) {
+        const float vv = a.qkv[(size_t)b * QKV_DIM + Q_DIM + KV_DIM + g * HEAD_DIM + d];
+        const bf16_raw kb = f_to_bf(o), vb = f_to_bf(vv);
+        const size_t wofs = (((size_t)b * a.n_layers + a.layer) * KV_HEADS + g) * HEAD_DIM + d;
+        if (a.k_write) a.k_write[wofs] = kb;
+        if (a.v_write) a.v_write[wofs] = vb;
+        if (a.append) {
+            const size_t cofs = (size_t)a.layer * a.seq_layer_stride[b] + (size_t)pos * KV_DIM + g * HEAD_DIM + d;
+            reinterpret_cast<bf16_raw*>(a.seq_k[b])[cofs] = kb;
+            reinterpret_cast<bf16_raw*>(a.seq_v[b])[cofs] = vb;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// attn_split: one block per (split, kv-head, sequence).  Both q heads of the GQA pair share the
+// K/V stream.  A quarter-warp owns one position at a time: lane `sub` of the quarter holds head
+// dims [8 sub, 8 sub + 8) and [64 + 8 sub, +8), i.e. two 16-byte units of the 256-byte row.
+// Cached rows are bf16; the new token's row (position seq_len[b]) is read in fp32 from `qkv`,
+// unrounded, as the reference does (qwen3mk/reference.py:74-78).
+// Output per (b, head, split): running max m, sum l, unnormalised o[128].
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+    f[0] = bf_lo(u.x); f[1] = bf_hi(u.x); f[2] = bf_lo(u.y); f[3] = bf_hi(u.y);
+    f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
+}
+
+__global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
+    __shared__ float s_m[32][2], s_l[32][2];
+    __shared__ __align__(16) float s_o[32][2][HEAD_DIM];  // 32 KB
+
+    const int sp = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int quarter = lane >> 3, sub = lane & 7;
+    const int len = a.seq_len[b];
+    const int n = len + 1;
+    const int chunk = (n + a.n_splits - 1) / a.n_splits;
+    const int p0 = sp * chunk, p1 = min(p0 + chunk, n);
+
+    const float* qkv = a.qkv + (size_t)b * QKV_DIM;
+    float q[2][16];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const float* qp = qkv + (2 * g + hh) * HEAD_DIM;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            q[hh][i] = qp[sub * 8 + i] * ATTN_SCALE;
+            q[hh][8 + i] = qp[64 + sub * 8 + i] * ATTN_SCALE;
+        }
+    }
+    const bf16_raw* kbase = reinterpret_cast<const bf16_raw*>(a.seq_k[b]) + (size_t)a.layer * a.seq_layer_stride[b] + g * HEAD_DIM;
+    const bf16_raw* vbase = reinterpret_cast<const bf16_raw*>(a.seq_v[b]) + (size_t)a.layer * a.seq_layer_stride[b] + g * HEAD_DIM;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float acc[2][16];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[hh][i] = 0.f;
+
+    for (int pb = p0 + warp * 4; pb < p1; pb += 32) {   // warp-uniform loop
+        const int p = pb + quarter;
+        const bool valid = p < p1;
+        float kf[16], vf[16];
+        if (valid && p < len) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)p * KV_DIM);
+            const uint4* vr = reinterpret_cast<const uint4*>(vbase + (size_t)p * KV_DIM);
+            const uint4 k0 = ld_stream(kr + sub), k1 = ld_stream(kr + 8 + sub);
+            const uint4 v0 = ld_stream(vr + sub), v1 = ld_stream(vr + 8 + sub);
+            unpack8(k0, kf); unpack8(k1, kf + 8);
+            unpack8(v0, vf); unpack8(v1, vf + 8);
+        } else if (valid) {   // the new token's own row
+            const float* kn = qkv + Q_DIM + g * HEAD_DIM;
+            const float* vn = qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                kf[i] = kn[sub * 8 + i]; kf[8 + i] = kn[64 + sub * 8 + i];
+                vf[i] = vn[sub * 8 + i]; vf[8 + i] = vn[64 + sub * 8 + i];
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+        }
+        float s[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float t = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t = fmaf(q[hh][i], kf[i], t);
+            t += __shfl_xor_sync(0xffffffffu, t, 1);
+            t += __shfl_xor_sync(0xffffffffu, t, 2);
+            t += __shfl_xor_sync(0xffffffffu, t, 4);
+            s[hh] = t;
+        }
+        if (valid) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const float mn = fmaxf(m[hh], s[hh]);
+                const float corr = expf(m[hh] - mn);   // exp(-inf) = 0 on the first row
+                const float pe = expf(s[hh] - mn);
+                l[hh] = l[hh] * corr + pe;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[hh][i] = fmaf(pe, vf[i], acc[hh][i] * corr);
+                m[hh] = mn;
+            }
+        }
+    }
+
+    // merge the 32 (warp, quarter) states of the block
+    const int st = warp * 4 + quarter;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        if (sub == 0) { s_m[st][hh] = m[hh]; s_l[st][hh] = l[hh]; }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            s_o[st][hh][sub * 8 + i] = acc[hh][i];
+            s_o[st][hh][64 + sub * 8 + i] = acc[hh][8 + i];
+        }
+    }
+    __syncthreads();
+    {
+        const int hh = tid >> 7, d = tid & 127;
+        float M = -INFINITY;
+        for (int i = 0; i < 32; ++i) M = fmaxf(M, s_m[i][hh]);
+        float L = 0.f, o = 0.f;
+        if (M > -INFINITY) {
+            for (int i = 0; i < 32; ++i) {
+                const float w = expf(s_m[i][hh] - M);   // 0 for empty states
+                L = fmaf(s_l[i][hh], w, L);
+                o = fmaf(s_o[i][hh][d], w, o);
+            }
+        }
+        float* out = a.part + (((size_t)b * Q_HEADS + 2 * g + hh) * a.n_splits + sp) * ATTN_PART_STRIDE;
+        if (d == 0) { out[0] = M; out[1] = L; }
+        out[4 + d] = o;
+    }
+}
+
+// attn_merge: combine the splits of one (sequence, head): grid (16, B), 128 threads
+__global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ part, int n_splits, float* __restrict__ attn) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const float* p = part + ((size_t)b * Q_HEADS + h) * n_splits * ATTN_PART_STRIDE;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * ATTN_PART_STRIDE]);
+    float L = 0.f, o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = p[s * ATTN_PART_STRIDE];
+        const float w = (ms > -INFINITY) ? expf(ms - M) : 0.f;
+        L = fmaf(p[s * ATTN_PART_STRIDE + 1], w, L);
+        o = fmaf(p[s * ATTN_PART_STRIDE + 4 + d], w, o);
+    }
+    attn[(size_t)b * Q_DIM + h * HEAD_DIM + d] = o / L;
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-side launchers
+// ------------------------------------------------------------------------------------------------
+template <int K, int EPI>
+static cudaError_t launch_gemv_k(const GemvArgs& a, int grid_x, cudaStream_t st) {
+    if (a.batch == 1) {
+        gemv_kernel<K, EPI, 1><<<dim3(grid_x, 1), 256, K * sizeof(float), st>>>(a);
+    } else {
+        constexpr int BT = 4;
+        const size_t smem = (size_t)BT * K * sizeof(float);
+        static bool attr_done = false;  // > 48 KB needs the opt-in once per function
+        if (!attr_done) {
+            cudaError_t e = cudaFuncSetAttribute(gemv_kernel<K, EPI, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            attr_done = true;
+        }
+        gemv_kernel<K, EPI, BT><<<dim3(grid_x, (a.batch + BT - 1) / BT), 256, smem, st>>>(a);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStream_t st) {
+#define Q3_CASE(KK, EE) if (K == KK && epi == EE) return launch_gemv_k<KK, EE>(a, grid_x, st)
+    Q3_CASE(1024, EPI_STORE);
+    Q3_CASE(1024, EPI_SILU);
+    Q3_CASE(1024, EPI_LOGITS);
+    Q3_CASE(2048, EPI_RESID);
+    Q3_CASE(3072, EPI_RESID);
+#undef Q3_CASE
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st) {
+    embed_kernel<<<batch, 256, 0, st>>>(token, embed, vocab, x, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st) {
+    argmax_final_kernel<<<batch, 256, 0, st>>>(pval, pidx, nblk, next_token, seq_len, append);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st) {
+    head_prep_kernel<<<dim3(Q_HEADS + KV_HEADS, batch), 128, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st) {
+    attn_split_kernel<<<dim3(a.n_splits, KV_HEADS, batch), 256, 0, st>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    attn_merge_kernel<<<dim3(Q_HEADS, batch), 128, 0, st>>>(a.part, a.n_splits, attn_out);
+    return cudaGetLastError();
+}
+
+}  // namespace q3

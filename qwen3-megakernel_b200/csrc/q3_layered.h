@@ -1,0 +1,66 @@
+// Argument blocks and launchers of the layered (one launch per phase) decode path.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace q3 {
+
+typedef unsigned short bf16_raw;
+
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU = 2, EPI_LOGITS = 3 };
+
+// floats per (sequence, head, split) attention partial: [0] max, [1] sum, [4..132) unnormalised output
+constexpr int ATTN_PART_STRIDE = 132;
+
+struct GemvSeg {
+    const bf16_raw* w;  // [rows, K] row-major bf16
+    int rows;
+};
+
+struct GemvArgs {
+    GemvSeg seg[3];        // weight rows: seg[0] rows first, then seg[1], then seg[2]
+    const bf16_raw* w2;    // EPI_SILU: the "up" matrix paired row-by-row with seg[0] ("gate")
+    const float* x;        // activations [batch, K], row stride ldx
+    int ldx;
+    const bf16_raw* gain;  // RMSNorm gain [K], or nullptr for no normalisation
+    float* out;            // [batch, ldo]
+    int ldo;
+    const float* resid;    // EPI_RESID: out = resid + acc
+    int ldr;
+    int n_rows;
+    int batch;
+    float* pval;           // EPI_LOGITS: per-block argmax partials [batch, gridDim.x]
+    int* pidx;
+};
+
+struct HeadPrepArgs {
+    float* qkv;                       // [batch, 4096] fp32: q | k | v, q and k rewritten in place
+    const bf16_raw* qn;               // [L, 128]
+    const bf16_raw* kn;               // [L, 128]
+    const float* rope;                // [positions, 128]: cos(64) | sin(64)
+    const int* seq_len;               // [batch]
+    bf16_raw* k_write;                // [batch, L, 8, 128] or nullptr
+    bf16_raw* v_write;
+    const uint64_t* seq_k;            // cache addresses, used when append != 0
+    const uint64_t* seq_v;
+    const long long* seq_layer_stride;
+    int layer, n_layers, append;
+};
+
+struct AttnArgs {
+    const float* qkv;                 // [batch, 4096] after head_prep
+    const uint64_t* seq_k;
+    const uint64_t* seq_v;
+    const long long* seq_layer_stride;
+    const int* seq_len;
+    float* part;                      // [batch, 16, n_splits, ATTN_PART_STRIDE]
+    int layer, n_splits;
+};
+
+cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStream_t st);
+cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st);
+cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st);
+cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st);
+cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st);
+
+}  // namespace q3

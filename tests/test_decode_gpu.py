@@ -1,0 +1,229 @@
+"""Parity of the CUDA engine with the CPU oracle, through the C ABI.  Needs a B200.
+
+Gates (reference: run.py:20-23,72-102; benchmark spec: tokens identical, logits and K/V within 2e-2
+relative):  next_token equal; logits rel-L2 <= 1e-4; k_write / v_write <= 2 bf16 ulps and rel-L2 <= 1e-2;
+max relative error <= 2e-2; inputs not mutated; repeated launches stable.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+
+pytestmark = pytest.mark.gpu
+
+GATE_LOGITS_REL_L2 = 1e-4
+GATE_KV_ULPS = 2
+GATE_KV_REL_L2 = 1e-2
+GATE_MAX_REL = 2e-2
+PATHS = ["layered"]
+
+
+def to_dev(d):
+    return {k: v.cuda() for k, v in d.items()}
+
+
+def gate_step(oracle, out, ref, what=""):
+    assert int(out["next_token"]) == int(ref["next_token"]), f"{what}: token {int(out['next_token'])} != {int(ref['next_token'])}"
+    e = oracle.rel_l2(out["logits"], ref["logits"])
+    assert e <= GATE_LOGITS_REL_L2, f"{what}: logits rel-L2 {e:.3e}"
+    assert oracle.max_rel(out["logits"], ref["logits"]) <= GATE_MAX_REL
+    for n in ("k_write", "v_write"):
+        r = oracle.rel_l2(out[n], ref[n])
+        u = oracle.bf16_ulps(out[n], ref[n])
+        assert r <= GATE_KV_REL_L2, f"{what}: {n} rel-L2 {r:.3e}"
+        assert u <= GATE_KV_ULPS, f"{what}: {n} {u:.1f} bf16 ulps"
+        assert oracle.max_rel(out[n], ref[n]) <= GATE_MAX_REL
+
+
+def engine(path, **kw):
+    from qwen3mk import Megakernel
+
+    try:
+        return Megakernel(path=path, **kw)
+    except RuntimeError as e:  # never a silent fallback: an engine that cannot be created fails the test
+        pytest.fail(f"engine creation failed: {e}")
+
+
+@pytest.fixture(scope="module")
+def small(oracle):
+    shp = oracle.Shape(layers=2, vocab=4096)
+    inp = oracle.synthetic(7, shp, context=40)
+    return shp, inp, oracle.to_fp32(inp)
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_small_model_step_vs_oracle_and_golden(oracle, small, path):
+    shp, inp, w = small
+    mk = engine(path, layers=2, vocab=4096)
+    dev = to_dev(inp)
+    snap = {k: v.clone() for k, v in dev.items()}
+    out = mk.step(dev)
+    mk.status()
+    ref = oracle.decode_step(w, inp["token"], inp["kcache"], inp["vcache"])
+    gate_step(oracle, out, ref, path)
+    fx = np.load(GOLDEN / "decode_small_seed7_pos40.npz")   # produced by the reference's own decode_step
+    assert int(out["next_token"]) == int(fx["next_token"])
+    assert oracle.rel_l2(out["logits"], torch.from_numpy(fx["logits"])) <= GATE_LOGITS_REL_L2
+    assert oracle.bf16_ulps(out["k_write"], torch.from_numpy(fx["k_write"])) <= GATE_KV_ULPS
+    assert all(torch.equal(dev[k], snap[k]) for k in dev), "an input was mutated"
+    # fresh outputs per call
+    out2 = mk.step(dev)
+    assert out2["logits"].data_ptr() != out["logits"].data_ptr()
+    assert mk.launch_count > 0
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("ctx", [0, 1, 7, 129, 515, 1500])
+def test_any_position(oracle, path, ctx):
+    shp = oracle.Shape(layers=2, vocab=2048)
+    inp = oracle.synthetic(100 + ctx, shp, context=max(ctx, 1))
+    if ctx == 0:
+        inp["kcache"], inp["vcache"] = inp["kcache"][:, :0].contiguous(), inp["vcache"][:, :0].contiguous()
+    mk = engine(path, layers=2, vocab=2048)
+    out = mk.step(to_dev(inp))
+    mk.status()
+    ref = oracle.decode_step(oracle.to_fp32(inp), inp["token"], inp["kcache"], inp["vcache"])
+    gate_step(oracle, out, ref, f"{path} ctx {ctx}")
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("batch", [2, 5, 8])
+def test_ragged_batch(oracle, path, batch):
+    from qwen3mk.kernel import SeqTable
+
+    shp = oracle.Shape(layers=2, vocab=2048)
+    inp = oracle.synthetic(31, shp, context=8)
+    w = oracle.to_fp32(inp)
+    g = torch.Generator().manual_seed(batch)
+    lens = torch.randint(1, 700, (batch,), generator=g).tolist()
+    toks = torch.randint(0, 2048, (batch,), generator=g)
+    kcs = [(torch.randn(2, n, 8, 128, generator=g) * 0.1).to(torch.bfloat16) for n in lens]
+    vcs = [(torch.randn(2, n, 8, 128, generator=g) * 0.1).to(torch.bfloat16) for n in lens]
+    mk = engine(path, layers=2, vocab=2048, max_batch=batch)
+    seqs = SeqTable([k.cuda() for k in kcs], [v.cuda() for v in vcs])
+    out = mk.bind_sequences(to_dev({k: inp[k] for k in oracle.WEIGHT_NAMES}), toks.cuda(), seqs)
+    mk.launch()
+    mk.status()
+    refs = oracle.decode_batch(w, toks.tolist(), kcs, vcs)
+    for b, ref in enumerate(refs):
+        gate_step(oracle, {k: out[k][b] for k in out}, ref, f"{path} seq {b} len {lens[b]}")
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_chained_growing_cache_matches_greedy_oracle(oracle, small, path):
+    shp, inp, w = small
+    steps = 24
+    mk = engine(path, layers=2, vocab=4096)
+    dev = to_dev(inp)
+    out = mk.bind(dev, chained=True, grow=steps)
+    toks = []
+    for _ in range(steps):
+        mk.launch()
+        toks.append(mk.chain_token.clone())
+    mk.status()
+    got = torch.stack(toks).cpu()
+    ref = oracle.greedy_decode(w, inp["token"], inp["kcache"], inp["vcache"], steps)
+    assert got.tolist() == ref["tokens"].tolist(), f"margins {ref['margins'].tolist()}"
+    assert oracle.rel_l2(out["logits"], ref["logits"]) <= GATE_LOGITS_REL_L2
+    with pytest.raises(RuntimeError, match="full"):
+        mk.launch()
+    assert torch.equal(dev["kcache"], inp["kcache"].cuda()), "the caller's cache was written"
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_rebound_launches_are_stable(oracle, small, path):
+    shp, inp, w = small
+    mk = engine(path, layers=2, vocab=4096)
+    dev = to_dev(inp)
+    first = {k: v.clone() for k, v in mk.step(dev).items()}
+    out = mk.bind(dev)
+    for _ in range(200):
+        mk.launch()
+    mk.status()
+    assert int(out["next_token"]) == int(first["next_token"])
+    assert oracle.rel_l2(out["logits"], first["logits"]) <= 1e-5
+    for n in ("k_write", "v_write"):
+        assert oracle.bf16_ulps(out[n], first[n]) <= GATE_KV_ULPS
+    mk.bind(dev, chained=True)
+    for _ in range(5):
+        mk.launch()
+    torch.cuda.synchronize()
+    assert 0 <= int(mk.chain_token) < 4096
+
+
+def test_prefill_matches_oracle(oracle, small):
+    from qwen3mk import prefill
+
+    shp, inp, w = small
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 4096, (37,), generator=g).tolist()
+    kc, vc, last = prefill.prefill(to_dev({k: inp[k] for k in oracle.WEIGHT_NAMES}), ids, "cuda", capacity=50)
+    rk, rv, rlast = oracle.prefill(w, ids)
+    assert tuple(kc.shape) == (2, 50, 8, 128) and kc.dtype == torch.bfloat16
+    # cached rows are bf16-rounded before later positions attend them, the oracle keeps fp32 inside
+    # the prompt: the spec's 2e-2 relative bound is the gate here
+    assert oracle.max_rel(kc[:, :37], rk) <= GATE_MAX_REL and oracle.max_rel(vc[:, :37], rv) <= GATE_MAX_REL
+    assert oracle.rel_l2(kc[:, :37], rk) <= GATE_KV_REL_L2
+    assert float(kc[:, 37:].abs().max()) == 0.0
+    assert oracle.max_rel(last, rlast) <= GATE_MAX_REL
+    assert int(last.argmax()) == int(rlast.argmax())
+
+
+def test_error_paths():
+    from qwen3mk import Megakernel, weights
+    from qwen3mk.kernel import SeqTable
+
+    mk = engine("layered", layers=1, vocab=512, max_batch=2)
+    with pytest.raises(RuntimeError, match="bind"):
+        mk.launch()
+    inp = weights.synthetic(0, "cuda", layers=1, vocab=512, context=4)
+    bad = dict(inp, wq=inp["wq"].float())
+    with pytest.raises(ValueError, match="input wq"):
+        mk.bind(bad)
+    k = [torch.zeros(1, 4, 8, 128, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    with pytest.raises(ValueError, match="max_batch"):
+        mk.bind_sequences(inp, torch.zeros(3, dtype=torch.int64, device="cuda"), SeqTable(k, k))
+    # a token outside the vocabulary is reported through the status words, without a fault
+    mk.step(dict(inp, token=torch.tensor(10 ** 6, dtype=torch.int64, device="cuda")))
+    with pytest.raises(RuntimeError, match="device status"):
+        mk.status()
+    assert mk.status()[0] == 0   # cleared, engine still usable
+    out = mk.step(inp)
+    mk.status()
+    assert 0 <= int(out["next_token"]) < 512
+    # positions beyond the RoPE table are refused on the host
+    short = Megakernel(layers=1, vocab=512, max_positions=4, path="layered")
+    with pytest.raises(ValueError, match="RoPE"):
+        short.step(inp)
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_full_model_vs_golden_and_oracle(oracle, synth_full, path):
+    """The reference's own configuration: 28 layers, vocabulary 151936, position 128, seed 0."""
+    inp = synth_full(0)
+    mk = engine(path)
+    dev = to_dev(inp)
+    out = mk.step(dev)
+    mk.status()
+    fx = np.load(GOLDEN / "decode_seed0_pos128.npz")
+    assert int(out["next_token"]) == int(fx["next_token"])
+    lg = out["logits"].cpu()
+    s = torch.from_numpy(fx["logits_sample"])
+    assert float((lg[::37] - s).double().norm() / s.double().norm()) <= GATE_LOGITS_REL_L2
+    assert oracle.bf16_ulps(out["k_write"], torch.from_numpy(fx["k_write"])) <= GATE_KV_ULPS
+    assert oracle.bf16_ulps(out["v_write"], torch.from_numpy(fx["v_write"])) <= GATE_KV_ULPS
+    ref = oracle.decode_step(oracle.to_fp32(inp), inp["token"], inp["kcache"], inp["vcache"])
+    gate_step(oracle, out, ref, f"{path} full")
+    # 64 greedy steps with a growing cache (positions 128..191) against the oracle's greedy loop
+    steps = 64
+    mk.bind(dev, chained=True, grow=steps)
+    toks = []
+    for _ in range(steps):
+        mk.launch()
+        toks.append(mk.chain_token.clone())
+    mk.status()
+    g = oracle.greedy_decode(oracle.to_fp32(inp), inp["token"], inp["kcache"], inp["vcache"], steps)
+    assert torch.stack(toks).cpu().tolist() == g["tokens"].tolist(), f"min margin {float(g['margins'].min()):.3e}"
