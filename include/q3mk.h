@@ -48,7 +48,7 @@ typedef struct q3_config {
     int32_t max_batch;      /* largest q3_decode_args.batch the scratch is sized for (>= 1)      */
     int32_t max_tokens;     /* largest q3_prefill_args.n_tokens the scratch is sized for (0: no prefill) */
     int32_t grid_limit;     /* 0 = one CTA per SM; otherwise cap the persistent grid (tests)     */
-    int32_t reserved;
+    int32_t pace_cycles;    /* 0 = default; nanoseconds the persistent kernel's producer warp sleeps between two <= 2 KB weight copies */
 } q3_config;
 
 /* The 13 weight tensors, device pointers to bf16.  Replaces slots 1..13 of the reference's
@@ -111,6 +111,12 @@ void q3_destroy(q3_engine* e);
  * pointer marshalling of Megakernel.step / bind (qwen3mk/kernel.py:185-188,203-206). */
 int q3_set_weights(q3_engine* e, const q3_weights* w);
 
+/* The persistent kernel streams an engine-owned re-layout of the seven layer matrices (built by
+ * q3_set_weights, about 0.9 GB for the full model) and rebuilds it only when a weight POINTER
+ * changes.  A caller that rewrites weights in place calls this before the next q3_set_weights.
+ * No counterpart in the reference, which reads the caller's tensors directly. */
+int q3_invalidate_weights(q3_engine* e);
+
 /* RoPE table: device fp32 [n_positions][128], row p = cos(p * f_0..f_63) then sin(p * f_0..f_63),
  * f_i = 1e6^(-2i/128).  Generalises the reference's single-position table
  * (qwen3mk/kernel.py:102-106).  Borrowed. */
@@ -127,6 +133,16 @@ int q3_prefill(q3_engine* e, const q3_prefill_args* a, void* stream);
  * Q3_ERR_DEVICE_WAIT; `words` (may be NULL) receives up to `n` raw status words:
  * [0] error code, [1] where (phase id), [2] CTA index, [3] observed counter value. */
 int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n);
+
+/* Phase tracing of the persistent kernel (the reference's trace came from an external tool:
+ * README.md:174-239).  `buf` is a device buffer of n_words 64-bit words, or NULL to switch tracing
+ * off.  While set and large enough (grid * (4 + 12 * n_layers) words), every persistent launch makes
+ * thread 0 of CTA c store %globaltimer (ns) at buf[c * (4 + 12 L) + ev].  ev 0 = start; for layer l,
+ * base = 1 + 12 l: +0 Q activations staged, +1 Q done, +2 barrier passed, +3 F q/k/v prepared,
+ * +4 F scores done, +5 F head output ready, +6 F done, +7 barrier passed, +8 GD activations staged,
+ * +9 GD hid ready, +10 GD done, +11 barrier passed; then 1 + 12 L = LM-head rows done, 2 + 12 L = end.
+ * Borrowed. */
+int q3_set_trace(q3_engine* e, uint64_t* buf, int64_t n_words);
 
 /* Number of kernel launches this engine has enqueued since creation. */
 int64_t q3_launch_count(const q3_engine* e);

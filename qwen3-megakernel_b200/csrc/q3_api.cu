@@ -41,7 +41,7 @@ extern "C" const char* q3_last_error(const q3_engine* e) { return e ? e->err : g
 extern "C" int q3_create(int device, const q3_config* cfg, q3_engine** out) {
     if (!cfg || !out) return fail(nullptr, Q3_ERR_INVALID, "q3_create: null argument");
     *out = nullptr;
-    if (cfg->n_layers < 1 || cfg->vocab < 1 || cfg->max_batch < 1 || cfg->max_tokens < 0 || cfg->grid_limit < 0)
+    if (cfg->n_layers < 1 || cfg->vocab < 1 || cfg->max_batch < 1 || cfg->max_tokens < 0 || cfg->grid_limit < 0 || cfg->pace_cycles < 0)
         return fail(nullptr, Q3_ERR_INVALID, "q3_create: n_layers=%d vocab=%d max_batch=%d max_tokens=%d grid_limit=%d out of range",
                     cfg->n_layers, cfg->vocab, cfg->max_batch, cfg->max_tokens, cfg->grid_limit);
     CU(nullptr, cudaSetDevice(device));
@@ -104,6 +104,13 @@ extern "C" int q3_set_weights(q3_engine* e, const q3_weights* w) {
     }
     e->w = *w;
     e->have_weights = 1;
+    CU(e, cudaSetDevice(e->device));
+    return persist_weights_changed(e);
+}
+
+extern "C" int q3_invalidate_weights(q3_engine* e) {
+    if (!e) return Q3_ERR_INVALID;
+    persist_invalidate_weights(e);
     return Q3_OK;
 }
 
@@ -111,6 +118,13 @@ extern "C" int q3_set_rope(q3_engine* e, const float* table, int32_t n_positions
     if (!e || !table || n_positions < 1) return fail(e, Q3_ERR_INVALID, "q3_set_rope: bad argument");
     e->rope = table;
     e->rope_n = n_positions;
+    return Q3_OK;
+}
+
+extern "C" int q3_set_trace(q3_engine* e, uint64_t* buf, int64_t n_words) {
+    if (!e || n_words < 0) return fail(e, Q3_ERR_INVALID, "q3_set_trace: bad argument");
+    e->trace = reinterpret_cast<unsigned long long*>(buf);
+    e->trace_words = buf ? n_words : 0;
     return Q3_OK;
 }
 
@@ -252,7 +266,7 @@ extern "C" int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream) {
     if (path == Q3_F_PATH_AUTO) path = persist_supports(e, a) ? Q3_F_PATH_PERSIST : Q3_F_PATH_LAYERED;
     if (path == Q3_F_PATH_PERSIST) {
         if (!persist_supports(e, a))
-            return fail(e, Q3_ERR_UNSUPPORTED, "q3_decode: the persistent kernel does not serve batch %d", a->batch);
+            return fail(e, Q3_ERR_UNSUPPORTED, "q3_decode: the persistent kernel does not serve batch %d at length %d", a->batch, a->max_len);
         return persist_decode(e, a, st);
     }
     if (path != Q3_F_PATH_LAYERED) return fail(e, Q3_ERR_INVALID, "q3_decode: unknown path flag 0x%x", path);

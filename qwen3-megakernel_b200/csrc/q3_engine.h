@@ -36,6 +36,8 @@ struct q3_engine {
     int p_grid, p_threads, p_smem;
     void* p_state;  // owned by q3_persist.cu
     int64_t launches;
+    unsigned long long* trace;  // caller-owned device buffer for phase time stamps, or nullptr
+    int64_t trace_words;
     char err[512];
 };
 
@@ -44,5 +46,7 @@ int persist_setup(q3_engine* e);
 void persist_teardown(q3_engine* e);
 bool persist_supports(const q3_engine* e, const q3_decode_args* a);
 int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st);
+int persist_weights_changed(q3_engine* e);
+void persist_invalidate_weights(q3_engine* e);
 int engine_fail(q3_engine* e, int code, const char* fmt, ...);
 }  // namespace q3

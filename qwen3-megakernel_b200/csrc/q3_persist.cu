@@ -1,9 +1,1121 @@
-// Persistent cooperative decode kernel (placeholder until the kernel lands).
+// Persistent cooperative decode kernel: one launch runs a whole batch-1 decode step.
+//
+// One CTA per SM: 16 consumer warps and one producer warp.  The schedule is static (every CTA owns
+// fixed weight rows) and a layer costs three grid barriers:
+//
+//   Q   x = X0 + dB;  qkv rows = rms(x, ln1) . [wq;wk;wv] rows                 -> qkv (global fp32)
+//   F   the 18 CTAs of a kv-head group (2 query heads x 9 Wo row slices) each attend 1/18 of the
+//       cached positions for both heads, publish (max, sum, output) partials, meet at a group
+//       counter, merge their own head with the new row, then Wo[slice rows, head columns] . o_h is
+//       added into dA                                                           (red.global.add)
+//   GD  x = X1 + dA;  hid rows = silu(gate) * up for this CTA's FFN rows, kept in shared memory,
+//       then the matching rows of the transposed down matrix scatter hid into dB (red.global.add)
+//
+// The residual stream lives as "materialised vector + pending delta": every consumer adds the two
+// on load, one CTA writes the sum back for the phase after next.
+//
+// Weights never wait for a barrier.  Each CTA's rows of the four matrices of a layer sit in four
+// shared-memory slots.  The producer warp refills a slot for the next layer as soon as the
+// consumers release it, with cp.async.bulk copies of at most 2 KB issued at a fixed pace, so that
+// HBM traffic is a steady stream instead of bursts: a burst of bulk copies queues in front of the
+// loads and atomics of the barrier that follows it and was measured to triple the barrier latency.
+// GEMV activations are held in registers; shared memory carries the weights only.
+//
+// A grid barrier is an arrive (red.release) and a later bounded wait (relaxed poll + acquire
+// fence); loads that do not depend on other CTAs (cached K/V rows, norm gains) sit between the two.
+// Every wait is bounded: a wait that gives up records a status word and turns the remaining
+// barriers of the CTA into no-ops, so a launch always terminates and the host reads the error.
+//
+// What the reference does for the same step: csrc/qwen3_step.cu:382-818 (four barriers per layer,
+// attention recomputed by every slice CTA, fixed position 128).
 #include "q3_engine.h"
 
 namespace q3 {
-int persist_setup(q3_engine* e) { e->p_grid = 0; e->p_threads = 0; e->p_smem = 0; return Q3_OK; }
-void persist_teardown(q3_engine*) {}
-bool persist_supports(const q3_engine*, const q3_decode_args*) { return false; }
-int persist_decode(q3_engine* e, const q3_decode_args*, cudaStream_t) { return engine_fail(e, Q3_ERR_UNSUPPORTED, "persistent kernel not built"); }
+
+constexpr int CW = 16;                        // consumer warps
+constexpr int CT = CW * 32;                   // consumer threads
+constexpr int PT = CT + 32;                   // + one producer warp
+constexpr int WO_SLICES = 9;                  // row slices of Wo; CTA c < 144 owns head c % 16, slice c / 16
+constexpr int F_CTAS = Q_HEADS * WO_SLICES;   // 144
+constexpr int GROUP_CTAS = 2 * WO_SLICES;     // CTAs sharing one kv head
+constexpr int WO_ROWS_MAX = 116;              // largest slice: 4 * ceil(256 / 9)
+constexpr int MIN_GRID = 147;                 // row shares must fit the shared-memory slots
+constexpr int SC_HALF = 128;                  // scores kept per head: the CTA's share of the cached positions
+constexpr int PERSIST_MAX_LEN = GROUP_CTAS * SC_HALF - GROUP_CTAS;   // 2286 cached positions
+constexpr int WROW = 1032;                    // elements between weight rows in shared memory: 1024 + 8 of padding, so that
+                                              // the eight row addresses of an ldmatrix fall into different banks
+constexpr int WOROW = 136;                    // the same for the 128-column Wo slice rows
+constexpr int ATT_WARPS = 8;                  // warps that attend positions (32 positions per pass)
+constexpr int N_ACC = 2;                      // accumulators for the FFN delta (halves same-address atomics)
+constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
+constexpr int PART_STRIDE = 132;              // floats per published partial: [0] max, [1] sum, [4..132) output
+constexpr int DEFAULT_PACE = 100;             // nanoseconds the producer sleeps after each bulk copy
+constexpr int COPY_BYTES = 16384;             // largest single bulk copy
+constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;   // patience of every device-side wait: 200 ms
+// fp32 tail of shared memory: 8 KB union | q_s[2][128] k_s v_s | o split [3][128] bf16 | hid split [3][32] bf16 | red lw misc | scores
+constexpr int FBUF_FLOATS = 2048 + 4 * 128 + 192 + 48 + 32 + 16 + 16 + 2 * SC_HALF;
+constexpr int TAIL_BYTES = FBUF_FLOATS * 4 + 8 * 8 + 16;
+
+struct PersistParams {
+    const bf16_raw *ln1, *qn, *kn, *ln2, *fnorm, *embed;
+    const bf16_raw* packed;   // [L][grid][share_elems(grid)]: every CTA's rows of the seven layer matrices, padded, in consumption order
+    const long long* token;
+    const uint64_t* seq_k;
+    const uint64_t* seq_v;
+    const long long* seq_layer_stride;
+    int* seq_len;
+    float* logits;
+    long long* next_token;
+    bf16_raw* k_write;
+    bf16_raw* v_write;
+    float* X0;        // [1024] materialised residual read by Q
+    float* X1;        // [1024] materialised residual read by GD
+    float* dA;        // [1024] attention delta
+    float* dB;        // [N_ACC][1024] FFN delta
+    float* qkv;       // [4096]
+    float* part;      // [8 groups][18 CTAs][2 heads][PART_STRIDE] attention partials
+    const float* rope;
+    unsigned* sync;   // [0] grid barrier counter, [2] end-of-step ticket, [8..15] kv-group counters
+    uint32_t* status;
+    float* pval;
+    int* pidx;
+    unsigned long long* trace;   // optional [grid][4 + 12 * n_layers] %globaltimer stamps of thread 0, or nullptr
+    int n_layers, vocab, append, pace;
+};
+
+struct PersistState {
+    bf16_raw* packed;       // the layer matrices re-laid per CTA (see pack_weights_kernel)
+    const void* src[7];     // the seven pointers `packed` was built from
+    float* X;               // X0 | X1 | dA | dB[N_ACC]
+    int grid, smem;
+};
+
+// Which rows of which matrix CTA c of a grid of G owns, and how many elements its packed share of
+// one layer takes.  Used by the decode kernel and by the kernel that packs the weights.
+struct Share {
+    int q0, nq, qmax;       // rows [q0, q0 + nq) of [wq; wk; wv], slot rows qmax
+    int i0, ni, imax;       // FFN rows [i0, i0 + ni) of gate, up and down^T, slot rows imax
+    int fh, fs, fr0, fn;    // F: query head, Wo row slice index, slice rows [fr0, fr0 + fn)
+    bool has_f;
+};
+__host__ __device__ inline Share share_of(int c, int G) {
+    Share s;
+    s.q0 = (int)((long long)c * QKV_DIM / G); s.nq = (int)((long long)(c + 1) * QKV_DIM / G) - s.q0; s.qmax = (QKV_DIM + G - 1) / G;
+    s.i0 = (int)((long long)c * INTER / G); s.ni = (int)((long long)(c + 1) * INTER / G) - s.i0; s.imax = (INTER + G - 1) / G;
+    s.has_f = c < F_CTAS;
+    s.fh = c % Q_HEADS; s.fs = c / Q_HEADS;
+    s.fr0 = (s.fs * 256 / WO_SLICES) * 4; s.fn = ((s.fs + 1) * 256 / WO_SLICES) * 4 - s.fr0;
+    return s;
+}
+// packed share of one (layer, CTA): A [qmax][WROW] | B [116][WOROW] | C [2 imax][WROW] | D [imax][WROW]
+__host__ __device__ inline size_t share_elems(int G) {
+    const int qmax = (QKV_DIM + G - 1) / G, imax = (INTER + G - 1) / G;
+    return (size_t)(qmax + 3 * imax) * WROW + (size_t)WO_ROWS_MAX * WOROW;
+}
+
+// ---- PTX helpers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+    asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// global -> shared bulk copy (TMA, no tensor map, no multicast); bytes and both addresses multiples of 16
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* b) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
+__device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+// barrier among the consumer warps only (the producer warp runs free)
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+
+// ---- counters in global memory: arrive and bounded wait ---------------------------------------------
+__device__ __forceinline__ void counter_arrive(unsigned* cnt) {   // one thread, after a cta_sync
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+}
+// thread 0 polls until *cnt has reached `target` (wrap-safe), then every consumer passes a cta_sync
+__device__ __forceinline__ void counter_wait(const unsigned* cnt, unsigned target, volatile int* abort_flag,
+                                             uint32_t* status, uint32_t site) {
+    if (threadIdx.x == 0 && !*abort_flag) {
+        unsigned v;
+        unsigned long long t0 = 0;
+        unsigned it = 0;
+        for (;;) {
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+            if ((int)(v - target) >= 0) break;
+            if ((++it & 1023u) == 0) {
+                const unsigned long long t = global_ns();
+                if (t0 == 0) t0 = t;
+                else if (t - t0 > WAIT_NS) {
+                    report(status, ST_BARRIER_TIMEOUT, site, v);
+                    *abort_flag = 1;
+                    break;
+                }
+            }
+        }
+        asm volatile("fence.acquire.gpu;" ::: "memory");
+    }
+    cta_sync();
+}
+// bounded wait on a shared-memory mbarrier; returns false when it gave up
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
+    unsigned it = 0;
+    unsigned long long t0 = 0;
+    while (!mbar_try_wait(b, parity)) {
+        if ((++it & 255u) == 0) {
+            const unsigned long long t = global_ns();
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > WAIT_NS) {
+                if ((threadIdx.x & 31) == 0) { report(status, ST_MBAR_TIMEOUT, site, parity); *abort_flag = 1; }
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// the same for a thread with nothing else to do: the hardware may suspend it up to 2 us per try
+__device__ __forceinline__ bool mbar_wait_sleepy(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
+    unsigned it = 0;
+    unsigned long long t0 = 0;
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(smem_u32(b)), "r"(parity), "r"(2000u) : "memory");
+        if (ok) return true;
+        if ((++it & 15u) == 0) {
+            const unsigned long long t = global_ns();
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > WAIT_NS) {
+                if ((threadIdx.x & 31) == 0) { report(status, ST_MBAR_TIMEOUT, site, parity); *abort_flag = 1; }
+                return false;
+            }
+        }
+    }
+}
+
+#ifdef Q3_FINE
+__device__ unsigned long long g_late[148 * 8];
+#endif
+// consumer side: one lane per warp polls, the rest of the warp waits at a warp barrier
+__device__ __forceinline__ void slot_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
+#ifdef Q3_FINE
+    if (threadIdx.x == 0) {   // debug: cycles thread 0 spends waiting for late slots, per CTA
+        if (!mbar_try_wait(b, parity)) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(b, parity)) {}
+            g_late[blockIdx.x * 8 + (site - 10)] += (unsigned long long)(clock64() - t0);
+            g_late[blockIdx.x * 8 + 4 + (site - 10)] += 1;
+        }
+    }
+#endif
+    if ((threadIdx.x & 31) == 0) mbar_wait(b, parity, abort_flag, status, site);
+    __syncwarp();
+}
+
+__device__ __forceinline__ void unpack8f(const uint4& u, float* f) {
+    f[0] = bf_lo(u.x); f[1] = bf_hi(u.x); f[2] = bf_lo(u.y); f[3] = bf_hi(u.y);
+    f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
+}
+// dot of one 16-byte weight unit with eight activations held in registers
+__device__ __forceinline__ float dot8r(const uint4& w, const float* x) {
+    float s = bf_lo(w.x) * x[0];
+    s = fmaf(bf_hi(w.x), x[1], s);
+    s = fmaf(bf_lo(w.y), x[2], s);
+    s = fmaf(bf_hi(w.y), x[3], s);
+    s = fmaf(bf_lo(w.z), x[4], s);
+    s = fmaf(bf_hi(w.z), x[5], s);
+    s = fmaf(bf_lo(w.w), x[6], s);
+    s = fmaf(bf_hi(w.w), x[7], s);
+    return s;
+}
+// ---- tensor-core GEMV pieces ------------------------------------------------------------------------
+// y = W x with bf16 W and fp32 x runs on mma.sync.m16n8k16: W tiles are the A operand (ldmatrix from
+// the padded shared-memory rows), and x enters as THREE bf16 columns of the B operand, x = hi + mid +
+// lo (each the bf16 rounding of what the previous ones left), so that the products are exact and the
+// fp32 accumulators hold W.hi, W.mid and W.lo; their sum is the fp32 dot product.  The other five
+// B columns are zero.  No warp shuffles, a handful of instructions per 16 x 16 tile.
+__device__ __forceinline__ void split3(float x, bf16_raw& h, bf16_raw& m, bf16_raw& l) {
+    h = f_to_bf(x);
+    const float r1 = x - bf_to_f(h);
+    m = f_to_bf(r1);
+    l = f_to_bf(r1 - bf_to_f(m));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&a)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&a)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// After the k loop: lanes with (lane & 3) == 0 hold columns 0, 1 (hi, mid) of rows g and g + 8, the
+// next lane holds column 2 (lo).  Returns the two row sums in the (lane & 3) == 0 lanes.
+__device__ __forceinline__ void fold_cols(const float (&c)[4], float& row_lo, float& row_hi) {
+    const float l0 = __shfl_down_sync(0xffffffffu, c[0], 1);
+    const float l1 = __shfl_down_sync(0xffffffffu, c[2], 1);
+    row_lo = (c[0] + c[1]) + l0;
+    row_hi = (c[2] + c[3]) + l1;
+}
+
+// this lane's 32 activations of a 1024-vector staged in shared memory (lane-interleaved layout)
+__device__ __forceinline__ void load_act_regs(const float* xs, int lane, float* xr) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float4 a = *reinterpret_cast<const float4*>(xs + k * 256 + lane * 4);
+        const float4 b = *reinterpret_cast<const float4*>(xs + k * 256 + 128 + lane * 4);
+        xr[k * 8 + 0] = a.x; xr[k * 8 + 1] = a.y; xr[k * 8 + 2] = a.z; xr[k * 8 + 3] = a.w;
+        xr[k * 8 + 4] = b.x; xr[k * 8 + 5] = b.y; xr[k * 8 + 6] = b.z; xr[k * 8 + 7] = b.w;
+    }
+}
+
+// ====================================================================================================
+__global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int c = blockIdx.x, G = gridDim.x;
+    const int L = p.n_layers;
+
+    // ---- static ownership ----
+    const Share sh = share_of(c, G);
+    const int q0 = sh.q0, nq = sh.nq, i0 = sh.i0, ni = sh.ni, qmax = sh.qmax, imax = sh.imax;
+    const bool has_f = sh.has_f;
+    const int fh = sh.fh, fs = sh.fs, fg = fh >> 1, fhh = fh & 1;
+    const int fj = fhh * WO_SLICES + fs;                          // index inside the kv-head group, 0..17
+    const int fr0 = sh.fr0, fn = sh.fn;
+    (void)i0;
+    const bool kv_writer = has_f && fj == 0;                      // one CTA per kv head stores the new K/V rows
+
+    // ---- shared memory carve-up ----
+    bf16_raw* sA = reinterpret_cast<bf16_raw*>(smem);                       // qkv rows        [qmax][WROW]
+    bf16_raw* sB = sA + (size_t)qmax * WROW;                                // Wo slice        [116][WOROW]
+    bf16_raw* sC = sB + WO_ROWS_MAX * WOROW;                                // gate | up rows  [2][imax][WROW]
+    bf16_raw* sD = sC + (size_t)2 * imax * WROW;                            // down^T rows     [imax][WROW]
+    float* fbuf = reinterpret_cast<float*>(sD + (size_t)imax * WROW);
+    // one 8 KB region with a different tenant per phase
+    uint32_t* xsp = reinterpret_cast<uint32_t*>(fbuf);   // Q, GD: activations split in three bf16 parts, [3][512] pairs (6 KB)
+    float* part = fbuf + 1536;                           // Q, GD: per-warp partial row sums (2 KB)
+    float* om = fbuf;                                    // F: [8 warps][2 heads][128] attention partials
+    float* wo_part = fbuf;                               // F: [2 k-halves][128] Wo slice partial sums (after the partials are published)
+    float* dout = fbuf;                                  // GD: [1024] down-projection outputs of this CTA (after the gate/up rows)
+    float* xs = fbuf;                                    // LM head: [1024] fp32 activations
+    float* q_s = fbuf + 2048;    // [2][128] both query heads of the group, scaled by 1/sqrt(128)
+    float* k_s = q_s + 256;      // [128] the new K row (after norm + RoPE), fp32
+    float* v_s = k_s + 128;      // [128] the new V row, fp32
+    uint32_t* osp = reinterpret_cast<uint32_t*>(v_s + 128);   // [3][64] pairs: attention output of this CTA's head, split
+    uint32_t* hsp = osp + 192;   // [3][16] pairs: this CTA's hid values, split
+    float* red = reinterpret_cast<float*>(hsp + 48);          // [32]
+    float* lw = red + 32;        // [16] per-warp probability sums, [w][head]
+    float* misc = lw + 16;       // [16]: [0] score of the new row for this CTA's head
+    float* sc = misc + 16;       // [2][SC_HALF] scores of this CTA's positions
+    float* out_s = sc;           // [128] Wo slice results (the scores are dead by then)
+    uint64_t* full = reinterpret_cast<uint64_t*>(sc + 2 * SC_HALF);   // [4] slot filled
+    uint64_t* empty = full + 4;                                        // [4] slot released by the consumers
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + 4);
+
+    const int n_ev = 4 + EV_PER_LAYER * L;
+#ifdef Q3_FINE
+#define Q3_FINE_T(k) do { if (p.trace != nullptr && tid == 0) p.trace[(size_t)G * n_ev + ((size_t)c * L + l) * 16 + (k)] = clock64(); } while (0)
+#else
+#define Q3_FINE_T(k) do {} while (0)
+#endif
+#define Q3_TRACE(ev) do { if (p.trace != nullptr && tid == 0) p.trace[(size_t)c * n_ev + (ev)] = global_ns(); } while (0)
+    Q3_TRACE(0);
+    if (tid == 0) {
+        for (int i = 0; i < 4; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();   // the only barrier the producer warp joins
+
+    // ================================================================================ producer warp
+    if (warp == CW) {
+        // Pacing: sleep between two copies instead of spinning, so that the producer warp leaves its
+        // scheduler's issue slots to the consumer warps that share it.
+        const unsigned pace = p.pace > 0 ? (unsigned)p.pace : (unsigned)DEFAULT_PACE;
+        auto pace_wait = [&]() { __nanosleep(pace); };
+        // The packed share is laid out exactly like the slots, padding included, so a slot is a few
+        // large contiguous copies (a bulk copy costs ~230 ns of TMA time whatever its size: 2 KB copies
+        // top out at 1.25 TB/s over the GPU, 16 KB copies stream above 7 TB/s).
+        const int slot_rows[4] = {qmax, WO_ROWS_MAX, 2 * imax, imax};
+        bf16_raw* const slot_dst[4] = {sA, sB, sC, sD};
+        bool alive = true;
+        for (int l = 0; l < L && alive; ++l) {
+            const bf16_raw* src = p.packed + ((size_t)l * G + c) * share_elems(G);
+            for (int slot = 0; slot < 4 && alive; ++slot) {
+                const uint32_t bytes = (uint32_t)slot_rows[slot] * (slot == 1 ? WOROW : WROW) * 2u;
+                if (!(slot == 1 && !has_f)) {
+                    if (l > 0) alive = mbar_wait_sleepy(&empty[slot], (l - 1) & 1, abort_flag, p.status, 20 + slot);
+                    if (!alive) break;
+                    if (lane == 0) {
+                        fence_proxy_async();
+                        mbar_expect_tx(&full[slot], bytes);
+                        for (uint32_t off = 0; off < bytes; off += COPY_BYTES) {
+                            const uint32_t n = min((uint32_t)COPY_BYTES, bytes - off);
+                            bulk_g2s(reinterpret_cast<unsigned char*>(slot_dst[slot]) + off, reinterpret_cast<const unsigned char*>(src) + off, n, &full[slot]);
+                            pace_wait();
+                        }
+                    }
+                    __syncwarp();
+                }
+                src += bytes / 2;
+            }
+        }
+        return;   // every copy issued here is awaited by the consumers before the CTA ends
+    }
+
+    // ================================================================================ consumer warps
+    long long tok = p.token[0];
+    if (tok < 0 || tok >= p.vocab) {
+        if (tid == 0) report(p.status, ST_BAD_TOKEN, 0, (uint32_t)tok);
+        tok = 0;
+    }
+    const int len = p.seq_len[0];
+    const bf16_raw* kcache = reinterpret_cast<const bf16_raw*>(p.seq_k[0]);
+    const bf16_raw* vcache = reinterpret_cast<const bf16_raw*>(p.seq_v[0]);
+    const long long lstride = p.seq_layer_stride[0];
+    const float* rope_row = p.rope + (size_t)len * HEAD_DIM;
+    float* dB0 = p.dB;
+    float* dB1 = p.dB + HIDDEN;
+    float* dBmine = p.dB + (size_t)(c & (N_ACC - 1)) * HIDDEN;
+
+    unsigned* bar = p.sync;
+    unsigned* grp = p.sync + 8 + fg;
+    unsigned target = 0, gtarget = 0;
+    const int quarter = lane >> 3, sub = lane & 7;
+    // ldmatrix.x4 row addresses of a 16 x 16 A tile: lanes 0-7 rows 0-7, 8-15 rows 8-15 (k 0-7); 16-31 the same rows at k 8-15
+    const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_k = (lane >> 4) * 8;
+    const int fr_n = lane >> 2, fr_k = (lane & 3) * 2;   // B fragment: column n, k pair; C fragment: rows fr_n, fr_n + 8
+
+    // this CTA's share of the cached positions of kv head fg: [cp0, cp1)
+    const int chunk = (len + GROUP_CTAS - 1) / GROUP_CTAS;
+    const int cp0 = min(len, fj * chunk), cp1 = min(len, cp0 + chunk);
+    const int npass = (cp1 - cp0 + 31) >> 5;                  // 32 positions per pass (warps 0..7, a quarter-warp each)
+    const int att_slot = warp * 4 + quarter;                  // < 32 for the attending warps
+
+    // gains of the next GEMV phase, fetched ahead of the barrier wait
+    uint32_t gain2 = *reinterpret_cast<const uint32_t*>(p.ln1 + 2 * tid);
+
+    for (int l = 0; l < L; ++l) {
+        const int ev = 1 + EV_PER_LAYER * l;
+        // ==================================================================== Q
+        {
+            float x0, x1;
+            if (l == 0) {
+                const uint32_t e = *reinterpret_cast<const uint32_t*>(p.embed + (size_t)tok * HIDDEN + 2 * tid);
+                x0 = bf_lo(e); x1 = bf_hi(e);
+            } else {
+                const float2 a = ldcg2(p.X0 + 2 * tid), d0 = ldcg2(dB0 + 2 * tid), d1 = ldcg2(dB1 + 2 * tid);
+                x0 = a.x + (d0.x + d1.x); x1 = a.y + (d0.y + d1.y);
+            }
+            if (c == 0) __stcg(reinterpret_cast<float2*>(p.X1 + 2 * tid), make_float2(x0, x1));
+            if (c == 1) __stcg(reinterpret_cast<float2*>(p.dA + 2 * tid), make_float2(0.f, 0.f));
+            {   // stage x * gain split in three bf16 parts (the 1/rms factor is applied to the row sums)
+                bf16_raw h0, m0, l0, h1, m1, l1;
+                split3(x0 * bf_lo(gain2), h0, m0, l0);
+                split3(x1 * bf_hi(gain2), h1, m1, l1);
+                xsp[tid] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+                xsp[512 + tid] = (uint32_t)m0 | ((uint32_t)m1 << 16);
+                xsp[1024 + tid] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+            }
+            const float ss = warp_sum(x0 * x0 + x1 * x1);
+            if (lane == 0) red[warp] = ss;
+            cta_sync();
+            Q3_TRACE(ev + 0);
+            float tot = (lane < CW) ? red[lane] : 0.f;
+            tot = warp_sum(tot);
+            const float r = rsqrtf(tot / (float)HIDDEN + EPS);
+            Q3_FINE_T(0);
+            // warp w: k range [64 w, 64 w + 64) of both 16-row tiles of this CTA's rows
+            uint32_t bq[4][2];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int kp = (64 * warp + 16 * t + fr_k) >> 1;
+                bq[t][0] = (fr_n < 3) ? xsp[fr_n * 512 + kp] : 0u;
+                bq[t][1] = (fr_n < 3) ? xsp[fr_n * 512 + kp + 4] : 0u;
+            }
+            Q3_FINE_T(1);
+            slot_wait(&full[0], l & 1, abort_flag, p.status, 10);
+            Q3_FINE_T(2);
+#pragma unroll
+            for (int rt = 0; rt < 2; ++rt) {
+                float cc[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t abase = smem_u32(sA + (size_t)(16 * rt + lm_row) * WROW + 64 * warp + lm_k);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    uint32_t af[4];
+                    ldsm_x4(af, abase + 32 * t);
+                    mma_bf16(cc, af, bq[t][0], bq[t][1]);
+                }
+                float r0, r1;
+                fold_cols(cc, r0, r1);
+                if ((lane & 3) == 0) { part[warp * 32 + 16 * rt + fr_n] = r0; part[warp * 32 + 16 * rt + fr_n + 8] = r1; }
+            }
+            cta_sync();
+            if (tid < nq) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < CW; ++w) v += part[w * 32 + tid];
+                __stcg(p.qkv + q0 + tid, v * r);
+            }
+            Q3_FINE_T(3);
+            cta_sync();
+            Q3_FINE_T(4);
+            Q3_TRACE(ev + 1);
+            if (tid == 0) counter_arrive(bar);
+            if (tid == 32) mbar_arrive(&empty[0]);
+        }
+        target += G;
+
+        // ---- between arrive and wait: what the F phase needs that no other CTA produces ----
+        uint4 kpre[2][2], vpre[2][2];
+        float gq[4] = {0.f, 0.f, 0.f, 0.f}, cs[4] = {0.f, 0.f, 0.f, 0.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+        const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
+        const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
+        if (has_f) {
+            if (warp < ATT_WARPS) {
+#pragma unroll
+                for (int ps = 0; ps < 2; ++ps) {
+                    const int pos = cp0 + ps * 32 + att_slot;
+                    if (pos < cp1) {
+                        const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
+                        const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
+                        kpre[ps][0] = ld_stream(kr + sub); kpre[ps][1] = ld_stream(kr + 8 + sub);
+                        vpre[ps][0] = ld_stream(vr + sub); vpre[ps][1] = ld_stream(vr + 8 + sub);
+                    } else {
+                        kpre[ps][0] = kpre[ps][1] = vpre[ps][0] = vpre[ps][1] = make_uint4(0, 0, 0, 0);
+                    }
+                }
+            }
+            if (warp >= 8 && warp < 11) {   // warps 8, 9 normalise the two q heads, warp 10 normalises k: dims 4*lane..
+                const bf16_raw* gsrc = (warp < 10 ? p.qn : p.kn) + (size_t)l * HEAD_DIM + lane * 4;
+                const uint2 gg = *reinterpret_cast<const uint2*>(gsrc);
+                gq[0] = bf_lo(gg.x); gq[1] = bf_hi(gg.x); gq[2] = bf_lo(gg.y); gq[3] = bf_hi(gg.y);
+                const float4 cc = *reinterpret_cast<const float4*>(rope_row + ((lane * 4) & 63));
+                const float4 sv = *reinterpret_cast<const float4*>(rope_row + 64 + ((lane * 4) & 63));
+                cs[0] = cc.x; cs[1] = cc.y; cs[2] = cc.z; cs[3] = cc.w;
+                sn[0] = sv.x; sn[1] = sv.y; sn[2] = sv.z; sn[3] = sv.w;
+            }
+        }
+        counter_wait(bar, target, abort_flag, p.status, 100 + l);
+        Q3_TRACE(ev + 2);
+
+        // ==================================================================== F
+        if (has_f) {
+            // ---- q (both heads of the group), k, v of the new position: warps 8..11 ----
+            if (warp >= 8 && warp < 12) {
+                const int role = warp - 8;   // 0, 1: q heads 2g, 2g+1;  2: k;  3: v
+                const float* src = p.qkv + (role < 2 ? (2 * fg + role) * HEAD_DIM : (role == 2 ? Q_DIM + fg * HEAD_DIM : Q_DIM + KV_DIM + fg * HEAD_DIM));
+                const float4 v4 = ldcg4(src + lane * 4);
+                float v[4] = {v4.x, v4.y, v4.z, v4.w};
+                float* dst = (role < 2) ? q_s + role * 128 : (role == 2 ? k_s : v_s);
+                if (role < 3) {
+                    const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+                    const float r = rsqrtf(ss / (float)HEAD_DIM + EPS);
+                    const float post = (role < 2) ? ATTN_SCALE : 1.f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float n = (v[i] * r) * gq[i];
+                        const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
+                        const float rot = (lane < 16) ? -partner : partner;
+                        v[i] = n * cs[i] + rot * sn[i];
+                    }
+                    *reinterpret_cast<float4*>(dst + lane * 4) = make_float4(v[0] * post, v[1] * post, v[2] * post, v[3] * post);
+                } else {
+                    *reinterpret_cast<float4*>(dst + lane * 4) = v4;
+                }
+                if (role >= 2 && kv_writer) {   // the new K (after norm + RoPE) and V rows, rounded to bf16
+                    uint2 pk;
+                    pk.x = (uint32_t)f_to_bf(v[0]) | ((uint32_t)f_to_bf(v[1]) << 16);
+                    pk.y = (uint32_t)f_to_bf(v[2]) | ((uint32_t)f_to_bf(v[3]) << 16);
+                    bf16_raw* wr = (role == 2) ? p.k_write : p.v_write;
+                    if (wr) *reinterpret_cast<uint2*>(wr + ((size_t)l * KV_HEADS + fg) * HEAD_DIM + lane * 4) = pk;
+                    if (p.append) {
+                        bf16_raw* cb = const_cast<bf16_raw*>(role == 2 ? kcache : vcache);
+                        *reinterpret_cast<uint2*>(cb + (size_t)l * lstride + (size_t)len * KV_DIM + fg * HEAD_DIM + lane * 4) = pk;
+                    }
+                }
+            }
+            cta_sync();
+            Q3_TRACE(ev + 3);
+
+            // ---- scores of this CTA's cached positions, both heads: a quarter-warp per position ----
+            float tmax0 = -INFINITY, tmax1 = -INFINITY;
+            if (warp < ATT_WARPS) {
+                float qa[2][16];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { qa[hh][i] = q_s[hh * 128 + sub * 8 + i]; qa[hh][8 + i] = q_s[hh * 128 + 64 + sub * 8 + i]; }
+                for (int ps = 0; ps < npass; ++ps) {
+                    const int idx = ps * 32 + att_slot, pos = cp0 + idx;
+                    uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0;
+                    if (ps == 0) { k0 = kpre[0][0]; k1 = kpre[0][1]; }
+                    else if (ps == 1) { k0 = kpre[1][0]; k1 = kpre[1][1]; }
+                    else if (pos < cp1) {
+                        const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
+                        k0 = ld_stream(kr + sub); k1 = ld_stream(kr + 8 + sub);
+                    }
+                    float kf[16];
+                    unpack8f(k0, kf); unpack8f(k1, kf + 8);
+                    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { s0 = fmaf(qa[0][i], kf[i], s0); s1 = fmaf(qa[1][i], kf[i], s1); }
+#pragma unroll
+                    for (int o = 1; o <= 4; o <<= 1) {
+                        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+                    }
+                    if (pos < cp1) {
+                        tmax0 = fmaxf(tmax0, s0); tmax1 = fmaxf(tmax1, s1);
+                        if (sub == 0) { sc[idx] = s0; sc[SC_HALF + idx] = s1; }
+                    }
+                }
+                tmax0 = warp_max(tmax0); tmax1 = warp_max(tmax1);
+                if (lane == 0) { red[warp] = tmax0; red[8 + warp] = tmax1; }
+            } else if (warp == 12) {   // the new row's score for this CTA's own head: q . k_new in fp32, unrounded
+                const float4 a = *reinterpret_cast<const float4*>(q_s + fhh * 128 + lane * 4);
+                const float4 b = *reinterpret_cast<const float4*>(k_s + lane * 4);
+                const float sn_ = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
+                if (lane == 0) misc[0] = sn_;
+            }
+            cta_sync();
+            float M0 = (lane < ATT_WARPS) ? red[lane] : -INFINITY, M1 = (lane < ATT_WARPS) ? red[8 + lane] : -INFINITY;
+            M0 = warp_max(M0); M1 = warp_max(M1);
+
+            // ---- probabilities and P.V against the CTA-wide maxima: the partial sums just add ----
+            if (warp < ATT_WARPS) {
+                float l0 = 0.f, l1 = 0.f, acc[2][16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { acc[0][i] = 0.f; acc[1][i] = 0.f; }
+                for (int ps = 0; ps < npass; ++ps) {
+                    const int idx = ps * 32 + att_slot, pos = cp0 + idx;
+                    uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+                    if (ps == 0) { v0 = vpre[0][0]; v1 = vpre[0][1]; }
+                    else if (ps == 1) { v0 = vpre[1][0]; v1 = vpre[1][1]; }
+                    else if (pos < cp1) {
+                        const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
+                        v0 = ld_stream(vr + sub); v1 = ld_stream(vr + 8 + sub);
+                    }
+                    if (pos < cp1) {
+                        const float p0 = __expf(sc[idx] - M0), p1 = __expf(sc[SC_HALF + idx] - M1);
+                        l0 += p0; l1 += p1;
+                        float vf[16];
+                        unpack8f(v0, vf); unpack8f(v1, vf + 8);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) { acc[0][i] = fmaf(p0, vf[i], acc[0][i]); acc[1][i] = fmaf(p1, vf[i], acc[1][i]); }
+                    }
+                }
+                // fold the four quarter-warp partials of the warp (lanes with equal `sub` hold the same dims)
+#pragma unroll
+                for (int off = 8; off <= 16; off <<= 1) {
+                    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+                    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        acc[0][i] += __shfl_xor_sync(0xffffffffu, acc[0][i], off);
+                        acc[1][i] += __shfl_xor_sync(0xffffffffu, acc[1][i], off);
+                    }
+                }
+                if (quarter == 0) {
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            om[(warp * 2 + hh) * 128 + sub * 8 + i] = acc[hh][i];
+                            om[(warp * 2 + hh) * 128 + 64 + sub * 8 + i] = acc[hh][8 + i];
+                        }
+                    if (sub == 0) { lw[warp * 2] = l0; lw[warp * 2 + 1] = l1; }
+                }
+            }
+            cta_sync();
+            // ---- publish the CTA's partial of both heads: (max, sum, unnormalised output) ----
+            if (tid < 256) {
+                const int hh = tid >> 7, d = tid & 127;
+                float o = 0.f, Ls = 0.f;
+#pragma unroll
+                for (int w = 0; w < ATT_WARPS; ++w) { o += om[(w * 2 + hh) * 128 + d]; Ls += lw[w * 2 + hh]; }
+                float* dst = p.part + ((size_t)(fg * GROUP_CTAS + fj) * 2 + hh) * PART_STRIDE;
+                if (d == 0) { __stcg(dst, hh ? M1 : M0); __stcg(dst + 1, Ls); }
+                __stcg(dst + 4 + d, o);
+            }
+            cta_sync();
+            Q3_TRACE(ev + 4);
+            if (tid == 0) counter_arrive(grp);
+            gtarget += GROUP_CTAS;
+            counter_wait(grp, gtarget, abort_flag, p.status, 400 + l);
+            Q3_TRACE(ev + 5);
+
+            // ---- merge the 18 partials of this CTA's head with the new row ----
+            if (tid < HEAD_DIM) {
+                const float* src = p.part + ((size_t)fg * GROUP_CTAS * 2 + fhh) * PART_STRIDE;
+                const float s_new = misc[0];
+                float mj[GROUP_CTAS], M = s_new;
+#pragma unroll
+                for (int j = 0; j < GROUP_CTAS; ++j) { mj[j] = __ldcg(src + (size_t)j * 2 * PART_STRIDE); M = fmaxf(M, mj[j]); }
+                const float pn = __expf(s_new - M);
+                float Ls = pn, o = pn * v_s[tid];
+#pragma unroll
+                for (int j = 0; j < GROUP_CTAS; ++j) {
+                    const float wgt = __expf(mj[j] - M);    // 0 for a CTA that had no positions (max = -inf)
+                    Ls = fmaf(__ldcg(src + (size_t)j * 2 * PART_STRIDE + 1), wgt, Ls);
+                    o = fmaf(__ldcg(src + (size_t)j * 2 * PART_STRIDE + 4 + tid), wgt, o);
+                }
+                bf16_raw h, m, lo_;
+                split3(o / Ls, h, m, lo_);
+                reinterpret_cast<bf16_raw*>(osp)[tid] = h;
+                reinterpret_cast<bf16_raw*>(osp + 64)[tid] = m;
+                reinterpret_cast<bf16_raw*>(osp + 128)[tid] = lo_;
+            }
+            cta_sync();
+
+            // ---- Wo slice on the tensor cores: warp (rt, kh) = 16 rows x 64 head dims ----
+            slot_wait(&full[1], l & 1, abort_flag, p.status, 11);
+            {
+                const int rt = warp >> 1, kh = warp & 1;
+                float cc[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t abase = smem_u32(sB + (size_t)(16 * rt + lm_row) * WOROW + 64 * kh + lm_k);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int kp = (64 * kh + 16 * t + fr_k) >> 1;
+                    const uint32_t b0 = (fr_n < 3) ? osp[fr_n * 64 + kp] : 0u;
+                    const uint32_t b1 = (fr_n < 3) ? osp[fr_n * 64 + kp + 4] : 0u;
+                    uint32_t af[4];
+                    ldsm_x4(af, abase + 32 * t);
+                    mma_bf16(cc, af, b0, b1);
+                }
+                float r0, r1;
+                fold_cols(cc, r0, r1);
+                if ((lane & 3) == 0) { wo_part[kh * 128 + 16 * rt + fr_n] = r0; wo_part[kh * 128 + 16 * rt + fr_n + 8] = r1; }
+            }
+            cta_sync();
+            if (tid < fn) out_s[tid] = wo_part[tid] + wo_part[128 + tid];
+            cta_sync();
+            if (tid < fn / 4) red_add_v4(p.dA + fr0 + 4 * tid, out_s[4 * tid], out_s[4 * tid + 1], out_s[4 * tid + 2], out_s[4 * tid + 3]);
+        } else if (c == G - 1) {
+            // an idle CTA clears the FFN delta accumulators for the coming GD phase
+            for (int i = tid; i < N_ACC * HIDDEN / 2; i += CT) __stcg(reinterpret_cast<float2*>(p.dB) + i, make_float2(0.f, 0.f));
+        }
+        cta_sync();
+        Q3_TRACE(ev + 6);
+        if (tid == 0) counter_arrive(bar);
+        if (tid == 32 && has_f) mbar_arrive(&empty[1]);
+        target += G;
+        gain2 = *reinterpret_cast<const uint32_t*>(p.ln2 + (size_t)l * HIDDEN + 2 * tid);
+        counter_wait(bar, target, abort_flag, p.status, 200 + l);
+        Q3_TRACE(ev + 7);
+
+        // ==================================================================== GD
+        {
+            const float2 a = ldcg2(p.X1 + 2 * tid), d = ldcg2(p.dA + 2 * tid);
+            const float x0 = a.x + d.x, x1 = a.y + d.y;
+            if (c == 0) __stcg(reinterpret_cast<float2*>(p.X0 + 2 * tid), make_float2(x0, x1));
+            {
+                bf16_raw h0, m0, l0, h1, m1, l1;
+                split3(x0 * bf_lo(gain2), h0, m0, l0);
+                split3(x1 * bf_hi(gain2), h1, m1, l1);
+                xsp[tid] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+                xsp[512 + tid] = (uint32_t)m0 | ((uint32_t)m1 << 16);
+                xsp[1024 + tid] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+            }
+            const float ss = warp_sum(x0 * x0 + x1 * x1);
+            if (lane == 0) red[warp] = ss;
+            cta_sync();
+            Q3_TRACE(ev + 8);
+            float tot = (lane < CW) ? red[lane] : 0.f;
+            tot = warp_sum(tot);
+            const float r = rsqrtf(tot / (float)HIDDEN + EPS);
+            {
+                Q3_FINE_T(5);
+                // warp (mat, ke): gate (0) or up (1) rows, k range [128 ke, 128 ke + 128), both 16-row tiles
+                const int mat = warp >> 3, ke = warp & 7;
+                uint32_t bx[8][2];
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    const int kp = (128 * ke + 16 * t + fr_k) >> 1;
+                    bx[t][0] = (fr_n < 3) ? xsp[fr_n * 512 + kp] : 0u;
+                    bx[t][1] = (fr_n < 3) ? xsp[fr_n * 512 + kp + 4] : 0u;
+                }
+                Q3_FINE_T(6);
+                slot_wait(&full[2], l & 1, abort_flag, p.status, 12);
+                Q3_FINE_T(7);
+#pragma unroll
+                for (int rt = 0; rt < 2; ++rt) {
+                    float cc[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint32_t abase = smem_u32(sC + (size_t)(mat * imax + 16 * rt + lm_row) * WROW + 128 * ke + lm_k);
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        uint32_t af[4];
+                        ldsm_x4(af, abase + 32 * t);
+                        mma_bf16(cc, af, bx[t][0], bx[t][1]);
+                    }
+                    float r0, r1;
+                    fold_cols(cc, r0, r1);
+                    if ((lane & 3) == 0) { part[ke * 64 + mat * 32 + 16 * rt + fr_n] = r0; part[ke * 64 + mat * 32 + 16 * rt + fr_n + 8] = r1; }
+                }
+                Q3_FINE_T(8);
+                cta_sync();
+                if (tid < 32) {   // hid of this CTA's rows, split for the down projection; rows past the share are zero
+                    float hv = 0.f;
+                    if (tid < ni) {
+                        float g = 0.f, u = 0.f;
+#pragma unroll
+                        for (int e8 = 0; e8 < 8; ++e8) { g += part[e8 * 64 + tid]; u += part[e8 * 64 + 32 + tid]; }
+                        g *= r; u *= r;
+                        hv = (g / (1.f + expf(-g))) * u;
+                    }
+                    bf16_raw h, m, lo_;
+                    split3(hv, h, m, lo_);
+                    reinterpret_cast<bf16_raw*>(hsp)[tid] = h;
+                    reinterpret_cast<bf16_raw*>(hsp + 16)[tid] = m;
+                    reinterpret_cast<bf16_raw*>(hsp + 32)[tid] = lo_;
+                }
+            }
+            cta_sync();   // hid ready; the activations and the gate/up slot are no longer needed
+            Q3_TRACE(ev + 9);
+            if (tid == 32) mbar_arrive(&empty[2]);
+
+            Q3_FINE_T(9);
+            slot_wait(&full[3], l & 1, abort_flag, p.status, 13);
+            Q3_FINE_T(10);
+            {   // out[n] = sum_i wdT[i][n] * hid[i]: A = transposed tiles of the slot, k = this CTA's (<= 32) rows
+                uint32_t bh[2][2];
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    const int kp = (16 * t + fr_k) >> 1;
+                    bh[t][0] = (fr_n < 3) ? hsp[fr_n * 16 + kp] : 0u;
+                    bh[t][1] = (fr_n < 3) ? hsp[fr_n * 16 + kp + 4] : 0u;
+                }
+                // transposed ldmatrix: lanes 0-7 / 8-15 / 16-23 / 24-31 address rows i of the blocks (n 0-7, i 0-7), (n 8-15, i 0-7), (n 0-7, i 8-15), (n 8-15, i 8-15)
+                const int ti = (lane & 7) + ((lane >> 4) & 1) * 8, tn = ((lane >> 3) & 1) * 8;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int n0 = 64 * warp + 16 * nt;
+                    float cc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        int i = 16 * t + ti;
+                        if (i >= ni) i = 0;   // hid is zero there; any finite row will do
+                        uint32_t af[4];
+                        ldsm_x4_trans(af, smem_u32(sD + (size_t)i * WROW + n0 + tn));
+                        mma_bf16(cc, af, bh[t][0], bh[t][1]);
+                    }
+                    float r0, r1;
+                    fold_cols(cc, r0, r1);
+                    if ((lane & 3) == 0) { dout[n0 + fr_n] = r0; dout[n0 + fr_n + 8] = r1; }
+                }
+            }
+            Q3_FINE_T(11);
+            cta_sync();
+            Q3_FINE_T(12);
+            if (tid < 256) {
+                const float4 t = *reinterpret_cast<const float4*>(dout + tid * 4);
+                red_add_v4(dBmine + tid * 4, t.x, t.y, t.z, t.w);
+            }
+            Q3_FINE_T(13);
+            cta_sync();
+            Q3_FINE_T(14);
+            Q3_TRACE(ev + 10);
+            if (tid == 0) counter_arrive(bar);
+            if (tid == 32) mbar_arrive(&empty[3]);
+        }
+        target += G;
+        gain2 = (l + 1 < L) ? *reinterpret_cast<const uint32_t*>(p.ln1 + (size_t)(l + 1) * HIDDEN + 2 * tid)
+                            : *reinterpret_cast<const uint32_t*>(p.fnorm + 2 * tid);
+        counter_wait(bar, target, abort_flag, p.status, 300 + l);
+        Q3_TRACE(ev + 11);
+    }
+
+    // ======================================================================== LM head + argmax
+    {
+        const float2 a = ldcg2(p.X0 + 2 * tid), d0 = ldcg2(dB0 + 2 * tid), d1 = ldcg2(dB1 + 2 * tid);
+        const float x0 = a.x + (d0.x + d1.x), x1 = a.y + (d0.y + d1.y);
+        const float ss = warp_sum(x0 * x0 + x1 * x1);
+        if (lane == 0) red[warp] = ss;
+        cta_sync();
+        float tot = (lane < CW) ? red[lane] : 0.f;
+        tot = warp_sum(tot);
+        const float r = rsqrtf(tot / (float)HIDDEN + EPS);
+        xs[act_slot(2 * tid)] = (x0 * r) * bf_lo(gain2);
+        xs[act_slot(2 * tid + 1)] = (x1 * r) * bf_hi(gain2);
+        cta_sync();
+
+        const int V = p.vocab;
+        const int v0 = (int)((long long)c * V / G), v1 = (int)((long long)(c + 1) * V / G);
+        float bestv = -INFINITY;
+        int besti = 0x7fffffff;
+        for (int base = v0 + warp * 4; base < v1; base += CW * 4) {
+            uint4 w[4][4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int row = min(base + k, v1 - 1);
+                const uint4* rp = reinterpret_cast<const uint4*>(p.embed + (size_t)row * HIDDEN);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[k][j] = ld_stream(rp + j * 32 + lane);
+            }
+            float acc[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[k] = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[k] += dot8(w[k][j], xs, j, lane);
+                acc[k] = warp_sum(acc[k]);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int row = base + k;
+                    if (row < v1) {
+                        if (p.logits) p.logits[row] = acc[k];
+                        if (acc[k] > bestv) { bestv = acc[k]; besti = row; }
+                    }
+                }
+            }
+        }
+        Q3_TRACE(1 + EV_PER_LAYER * L);
+        // CTA argmax (ties -> lowest index), then the last CTA to finish reduces over CTAs
+        float* bv_s = q_s;                       // reuse: [16] values, [16] indices
+        int* bi_s = reinterpret_cast<int*>(k_s);
+        if (lane == 0) { bv_s[warp] = bestv; bi_s[warp] = besti; }
+        cta_sync();
+        int* last_flag = reinterpret_cast<int*>(v_s);
+        if (tid == 0) {
+            float bv = bv_s[0];
+            int bi = bi_s[0];
+            for (int w = 1; w < CW; ++w)
+                if (bv_s[w] > bv || (bv_s[w] == bv && bi_s[w] < bi)) { bv = bv_s[w]; bi = bi_s[w]; }
+            __stcg(p.pval + c, bv);
+            __stcg(p.pidx + c, bi);
+            __threadfence();
+            const unsigned prev = atomicAdd(p.sync + 2, 1u);
+            *last_flag = (prev == (unsigned)G - 1u);
+            __threadfence();
+        }
+        cta_sync();
+        if (*last_flag) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int i = tid; i < G; i += CT) {
+                const float v = __ldcg(p.pval + i);
+                const int ix = __ldcg(p.pidx + i);
+                if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            cta_sync();
+            if (lane == 0) { bv_s[warp] = bv; bi_s[warp] = bi; }
+            cta_sync();
+            if (tid == 0) {
+                for (int w = 1; w < CW; ++w)
+                    if (bv_s[w] > bv || (bv_s[w] == bv && bi_s[w] < bi)) { bv = bv_s[w]; bi = bi_s[w]; }
+                p.next_token[0] = bi;
+                if (p.append) p.seq_len[0] = len + 1;
+                // every CTA has passed every barrier: rearm the counters for the next launch
+                p.sync[0] = 0;
+                p.sync[2] = 0;
+            }
+            if (tid >= 8 && tid < 16) p.sync[tid] = 0;
+        }
+        Q3_TRACE(2 + EV_PER_LAYER * L);
+    }
+#undef Q3_TRACE
+#undef Q3_FINE_T
+}
+
+#ifdef Q3_FINE
+extern "C" int q3_debug_late(unsigned long long* host, int clear) {
+    cudaMemcpyFromSymbol(host, g_late, sizeof(g_late));
+    if (clear) { static unsigned long long z[148 * 8]; cudaMemcpyToSymbol(g_late, z, sizeof(z)); }
+    return 0;
+}
+#endif
+
+// ---- weight packing ----------------------------------------------------------------------------------
+// packed[l][c] = everything CTA c streams for layer l, in the order and with the row padding of its
+// shared-memory slots: its rows of [wq; wk; wv], its Wo slice (the 128 columns of its head), its
+// gate and up rows, and its rows of the transposed down matrix.  Rows beyond a share are zero.
+struct PackArgs {
+    const bf16_raw *wq, *wk, *wv, *wo, *wg, *wu, *wd;
+    bf16_raw* packed;
+};
+__global__ void __launch_bounds__(256) pack_weights_kernel(const PackArgs a) {
+    const int c = blockIdx.x, G = gridDim.x, l = blockIdx.y;
+    const Share sh = share_of(c, G);
+    bf16_raw* dst = a.packed + ((size_t)l * G + c) * share_elems(G);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    // A: 129 16-byte units per row (128 of data, 1 of padding)
+    for (int u = threadIdx.x; u < sh.qmax * 129; u += 256) {
+        const int j = u / 129, k = u % 129;
+        uint4 v = zero;
+        if (j < sh.nq && k < 128) {
+            const int r = sh.q0 + j;
+            const bf16_raw* src = r < Q_DIM ? a.wq + ((size_t)l * Q_DIM + r) * HIDDEN
+                                : r < Q_DIM + KV_DIM ? a.wk + ((size_t)l * KV_DIM + (r - Q_DIM)) * HIDDEN
+                                                     : a.wv + ((size_t)l * KV_DIM + (r - Q_DIM - KV_DIM)) * HIDDEN;
+            v = reinterpret_cast<const uint4*>(src)[k];
+        }
+        reinterpret_cast<uint4*>(dst)[u] = v;
+    }
+    dst += (size_t)sh.qmax * WROW;
+    // B: 17 units per row
+    for (int u = threadIdx.x; u < WO_ROWS_MAX * 17; u += 256) {
+        const int j = u / 17, k = u % 17;
+        uint4 v = zero;
+        if (sh.has_f && j < sh.fn && k < 16)
+            v = reinterpret_cast<const uint4*>(a.wo + ((size_t)l * HIDDEN + sh.fr0 + j) * Q_DIM + sh.fh * HEAD_DIM)[k];
+        reinterpret_cast<uint4*>(dst)[u] = v;
+    }
+    dst += (size_t)WO_ROWS_MAX * WOROW;
+    // C: gate rows, then up rows
+    for (int u = threadIdx.x; u < 2 * sh.imax * 129; u += 256) {
+        const int jj = u / 129, k = u % 129;
+        const bool up = jj >= sh.imax;
+        const int j = up ? jj - sh.imax : jj;
+        uint4 v = zero;
+        if (j < sh.ni && k < 128) v = reinterpret_cast<const uint4*>((up ? a.wu : a.wg) + ((size_t)l * INTER + sh.i0 + j) * HIDDEN)[k];
+        reinterpret_cast<uint4*>(dst)[u] = v;
+    }
+    dst += (size_t)2 * sh.imax * WROW;
+    // D: row j holds wd[l][n][i0 + j] for n = 0..1023 (the down matrix transposed)
+    for (int e = threadIdx.x; e < sh.imax * WROW; e += 256) {
+        const int j = e / WROW, n = e % WROW;
+        bf16_raw v = 0;
+        if (j < sh.ni && n < HIDDEN) v = a.wd[((size_t)l * HIDDEN + n) * INTER + sh.i0 + j];
+        dst[e] = v;
+    }
+}
+
+// ====================================================================================================
+// host side
+// ====================================================================================================
+static int smem_bytes_for(int grid) {
+    const int qmax = (QKV_DIM + grid - 1) / grid, imax = (INTER + grid - 1) / grid;
+    return (qmax + 3 * imax) * WROW * 2 + WO_ROWS_MAX * WOROW * 2 + TAIL_BYTES;
+}
+
+int persist_setup(q3_engine* e) {
+    e->p_grid = 0; e->p_threads = PT; e->p_smem = 0; e->p_state = nullptr;
+    int grid = e->sm_count;
+    if (e->cfg.grid_limit > 0 && e->cfg.grid_limit < grid) grid = e->cfg.grid_limit;
+    if (grid < MIN_GRID) return Q3_OK;   // too few CTAs for the slot sizes: the layered path serves everything
+    const int smem = smem_bytes_for(grid);
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, e->device) != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "cudaGetDeviceProperties failed");
+    if ((size_t)smem > prop.sharedMemPerBlockOptin) return Q3_OK;
+    cudaError_t err = cudaFuncSetAttribute(q3_persist_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: set smem attribute (%d B): %s", smem, cudaGetErrorString(err));
+    int per_sm = 0;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, q3_persist_decode, PT, smem);
+    if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: occupancy query: %s", cudaGetErrorString(err));
+    if (per_sm < 1 || per_sm * e->sm_count < grid || !prop.cooperativeLaunch)
+        return engine_fail(e, Q3_ERR_NOT_RESIDENT, "persist: %d CTAs of %d threads and %d B shared memory cannot be co-resident", grid, PT, smem);
+    if ((size_t)KV_HEADS * GROUP_CTAS * 2 * PART_STRIDE > (size_t)e->cfg.max_batch * Q_HEADS * e->max_splits * ATTN_PART_STRIDE)
+        return engine_fail(e, Q3_ERR_INVALID, "persist: attention partial buffer too small");
+    PersistState* s = new PersistState();
+    s->packed = nullptr; s->X = nullptr; s->grid = grid; s->smem = smem;
+    for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
+    if (cudaMalloc(&s->X, (3 + N_ACC) * HIDDEN * sizeof(float)) != cudaSuccess ||
+        cudaMemset(s->X, 0, (3 + N_ACC) * HIDDEN * sizeof(float)) != cudaSuccess ||
+        cudaMalloc(&s->packed, (size_t)e->cfg.n_layers * grid * share_elems(grid) * sizeof(bf16_raw)) != cudaSuccess) {
+        if (s->X) cudaFree(s->X);
+        delete s;
+        return engine_fail(e, Q3_ERR_CUDA, "persist: scratch allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    e->p_state = s;
+    e->p_grid = grid; e->p_smem = smem;
+    return Q3_OK;
+}
+
+void persist_teardown(q3_engine* e) {
+    PersistState* s = static_cast<PersistState*>(e->p_state);
+    if (!s) return;
+    if (s->packed) cudaFree(s->packed);
+    if (s->X) cudaFree(s->X);
+    delete s;
+    e->p_state = nullptr;
+}
+
+bool persist_supports(const q3_engine* e, const q3_decode_args* a) {
+    return e->p_state != nullptr && a->batch == 1 && a->max_len <= PERSIST_MAX_LEN;
+}
+
+// (Re)pack the layer matrices when one of the caller's pointers changes.  Runs on the legacy default
+// stream and synchronises: weights change rarely, and later launches may use any stream.  The pack
+// is keyed on the pointers: a caller that rewrites weights in place must call q3_set_weights with
+// `Q3_W_REPACK` semantics, i.e. after q3_invalidate_weights.
+int persist_weights_changed(q3_engine* e) {
+    PersistState* s = static_cast<PersistState*>(e->p_state);
+    if (!s) return Q3_OK;
+    const void* now[7] = {e->w.wq, e->w.wk, e->w.wv, e->w.wo, e->w.wg, e->w.wu, e->w.wd};
+    bool same = true;
+    for (int i = 0; i < 7; ++i) same = same && (s->src[i] == now[i]);
+    if (same) return Q3_OK;
+    auto bf = [](const void* p) { return reinterpret_cast<const bf16_raw*>(p); };
+    PackArgs a{bf(now[0]), bf(now[1]), bf(now[2]), bf(now[3]), bf(now[4]), bf(now[5]), bf(now[6]), s->packed};
+    pack_weights_kernel<<<dim3(s->grid, e->cfg.n_layers), 256>>>(a);
+    ++e->launches;
+    cudaError_t err = cudaDeviceSynchronize();
+    if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: packing the weights failed: %s", cudaGetErrorString(err));
+    for (int i = 0; i < 7; ++i) s->src[i] = now[i];
+    return Q3_OK;
+}
+
+void persist_invalidate_weights(q3_engine* e) {
+    PersistState* s = static_cast<PersistState*>(e->p_state);
+    if (s) for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
+}
+
+int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
+    PersistState* s = static_cast<PersistState*>(e->p_state);
+    auto bf = [](const void* p) { return reinterpret_cast<const bf16_raw*>(p); };
+    PersistParams p{};
+    const q3_weights& w = e->w;
+    p.ln1 = bf(w.ln1); p.qn = bf(w.qn); p.kn = bf(w.kn); p.ln2 = bf(w.ln2); p.fnorm = bf(w.fnorm); p.embed = bf(w.embed);
+    p.packed = s->packed;
+    p.token = reinterpret_cast<const long long*>(a->token);
+    p.seq_k = a->seq_k; p.seq_v = a->seq_v; p.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
+    p.seq_len = a->seq_len; p.logits = a->logits; p.next_token = reinterpret_cast<long long*>(a->next_token);
+    p.k_write = reinterpret_cast<bf16_raw*>(a->k_write); p.v_write = reinterpret_cast<bf16_raw*>(a->v_write);
+    p.X0 = s->X; p.X1 = s->X + HIDDEN; p.dA = s->X + 2 * HIDDEN; p.dB = s->X + 3 * HIDDEN;
+    p.qkv = e->qkv; p.part = e->part; p.rope = e->rope; p.sync = e->sync; p.status = e->status; p.pval = e->pval; p.pidx = e->pidx;
+    p.trace = (e->trace && e->trace_words >= (int64_t)s->grid * (4 + EV_PER_LAYER * e->cfg.n_layers)) ? e->trace : nullptr;
+    p.n_layers = e->cfg.n_layers; p.vocab = e->cfg.vocab; p.append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
+    p.pace = e->cfg.pace_cycles;
+    void* args[] = {&p};
+    cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(q3_persist_decode), dim3(s->grid), dim3(PT), args, (size_t)s->smem, st);
+    ++e->launches;
+    if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: cooperative launch failed: %s", cudaGetErrorString(err));
+    return Q3_OK;
+}
+
 }  // namespace q3

@@ -10,15 +10,15 @@ OK, ERR_INVALID, ERR_CUDA, ERR_NOT_RESIDENT, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 
 F_APPEND_KV, F_PATH_AUTO, F_PATH_LAYERED, F_PATH_PERSIST = 0x1, 0x0, 0x10, 0x20
 
 # every symbol include/q3mk.h declares
-SYMBOLS = ("q3_create", "q3_destroy", "q3_set_weights", "q3_set_rope", "q3_decode", "q3_prefill", "q3_status",
-           "q3_launch_count", "q3_grid_info", "q3_scratch", "q3_last_error", "q3_version")
+SYMBOLS = ("q3_create", "q3_destroy", "q3_set_weights", "q3_invalidate_weights", "q3_set_rope", "q3_decode", "q3_prefill", "q3_status",
+           "q3_set_trace", "q3_launch_count", "q3_grid_info", "q3_scratch", "q3_last_error", "q3_version")
 
 WEIGHT_FIELDS = ("ln1", "wq", "wk", "wv", "qn", "kn", "wo", "ln2", "wg", "wu", "wd", "fnorm", "embed")
 
 
 class Config(C.Structure):
     _fields_ = [("n_layers", C.c_int32), ("vocab", C.c_int32), ("max_batch", C.c_int32), ("max_tokens", C.c_int32),
-                ("grid_limit", C.c_int32), ("reserved", C.c_int32)]
+                ("grid_limit", C.c_int32), ("pace_cycles", C.c_int32)]
 
 
 class Weights(C.Structure):
@@ -55,6 +55,8 @@ def load() -> C.CDLL:
     lib.q3_destroy.restype = None
     lib.q3_set_weights.argtypes = [C.c_void_p, C.POINTER(Weights)]
     lib.q3_set_weights.restype = C.c_int
+    lib.q3_invalidate_weights.argtypes = [C.c_void_p]
+    lib.q3_invalidate_weights.restype = C.c_int
     lib.q3_set_rope.argtypes = [C.c_void_p, C.c_void_p, C.c_int32]
     lib.q3_set_rope.restype = C.c_int
     lib.q3_decode.argtypes = [C.c_void_p, C.POINTER(DecodeArgs), C.c_void_p]
@@ -63,6 +65,8 @@ def load() -> C.CDLL:
     lib.q3_prefill.restype = C.c_int
     lib.q3_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32), C.c_int32]
     lib.q3_status.restype = C.c_int
+    lib.q3_set_trace.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
+    lib.q3_set_trace.restype = C.c_int
     lib.q3_launch_count.argtypes = [C.c_void_p]
     lib.q3_launch_count.restype = C.c_int64
     lib.q3_grid_info.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]

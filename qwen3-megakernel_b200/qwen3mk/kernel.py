@@ -134,18 +134,23 @@ class Megakernel:
     """
 
     def __init__(self, device=None, *, max_batch: int = 1, layers: int = LAYERS, vocab: int = VOCAB,
-                 max_positions: int = 8192, path: str = "auto", grid_limit: int = 0, max_tokens: int = 0):
+                 max_positions: int = 8192, path: str = "auto", grid_limit: int = 0, max_tokens: int = 0,
+                 pace_cycles: int = 0):
         if not torch.cuda.is_available():
             raise RuntimeError("Megakernel needs a CUDA device (sm_100a); there is no CPU path")
         self.lib = _cabi.load()
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError(f"Megakernel needs a CUDA device, got {self.device}")
+        if self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         torch.cuda.set_device(self.device)
         torch.zeros(1, device=self.device)  # make torch's primary context current
         major, minor = torch.cuda.get_device_capability(self.device)
         self.arch = f"sm_{major}{minor}"
         self.layers, self.vocab, self.max_batch = int(layers), int(vocab), int(max_batch)
         self._path_flag = {"auto": _cabi.F_PATH_AUTO, "layered": _cabi.F_PATH_LAYERED, "persist": _cabi.F_PATH_PERSIST}[path]
-        cfg = _cabi.Config(self.layers, self.vocab, self.max_batch, int(max_tokens), int(grid_limit), 0)
+        cfg = _cabi.Config(self.layers, self.vocab, self.max_batch, int(max_tokens), int(grid_limit), int(pace_cycles))
         h = ctypes.c_void_p()
         rc = self.lib.q3_create(self.device.index or 0, ctypes.byref(cfg), ctypes.byref(h))
         _cabi.check(self.lib, None, rc, "q3_create")
@@ -192,6 +197,12 @@ class Megakernel:
         _cabi.check(self.lib, self.handle, self.lib.q3_set_weights(self.handle, ctypes.byref(w)), "q3_set_weights")
         self._weights_key = key
 
+    def refresh_weights(self) -> None:
+        """Forget the engine's packed copy of the layer matrices.  Call it after rewriting weight tensors
+        in place: the copy is otherwise rebuilt only when a weight tensor's address changes."""
+        self.lib.q3_invalidate_weights(self.handle)
+        self._weights_key = None
+
     def check_inputs(self, inputs: dict) -> None:
         """Raise ValueError unless every input is a contiguous CUDA tensor of the expected shape and dtype."""
         ctx = inputs["kcache"].shape[1] if "kcache" in inputs and inputs["kcache"].dim() == 4 else CONTEXT
@@ -224,6 +235,18 @@ class Megakernel:
             __cuda_array_interface__ = {"shape": (n.value // 4,), "typestr": "<f4", "data": (p.value, False), "version": 3}
         torch.cuda.synchronize(self.device)
         return torch.as_tensor(_Raw(), device=self.device).clone()
+
+    def enable_trace(self, on: bool = True):
+        """Phase time stamps of the persistent kernel: returns the int64 device tensor [grid, 4 + 12 * layers]
+        that every later persistent launch overwrites with %globaltimer values (ns), or None when switched off."""
+        if not on or self.grid == 0:
+            self._trace = None
+            self.lib.q3_set_trace(self.handle, None, 0)
+            return None
+        self._trace = torch.zeros((self.grid, 4 + 12 * self.layers), dtype=torch.int64, device=self.device)
+        rc = self.lib.q3_set_trace(self.handle, self._trace.data_ptr(), self._trace.numel())
+        _cabi.check(self.lib, self.handle, rc, "q3_set_trace")
+        return self._trace
 
     def _decode(self, args, stream) -> None:
         rc = self.lib.q3_decode(self.handle, ctypes.byref(args), stream)

@@ -47,6 +47,8 @@ def prefill(w: dict, ids, device="cuda", *, capacity: int | None = None, engine:
     cast back, which is exact).  Returns kcache, vcache (bf16 [layers, capacity, 8, 128], slots
     [0, len(ids)) filled; capacity defaults to len(ids)) and the fp32 logits [vocab] of the last position."""
     dev = torch.device(device)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
     ids_t = torch.as_tensor(ids, dtype=torch.int64).to(dev).contiguous()
     n = ids_t.numel()
     cap = n if capacity is None else int(capacity)

@@ -18,7 +18,7 @@ GATE_LOGITS_REL_L2 = 1e-4
 GATE_KV_ULPS = 2
 GATE_KV_REL_L2 = 1e-2
 GATE_MAX_REL = 2e-2
-PATHS = ["layered"]
+PATHS = ["layered", "persist"]
 
 
 def to_dev(d):
@@ -76,20 +76,25 @@ def test_small_model_step_vs_oracle_and_golden(oracle, small, path):
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("ctx", [0, 1, 7, 129, 515, 1500])
+@pytest.mark.parametrize("ctx", [0, 1, 7, 17, 19, 64, 129, 515, 577, 1500, 2286, 2400])
 def test_any_position(oracle, path, ctx):
     shp = oracle.Shape(layers=2, vocab=2048)
     inp = oracle.synthetic(100 + ctx, shp, context=max(ctx, 1))
     if ctx == 0:
         inp["kcache"], inp["vcache"] = inp["kcache"][:, :0].contiguous(), inp["vcache"][:, :0].contiguous()
     mk = engine(path, layers=2, vocab=2048)
+    if path == "persist" and ctx > 2286:
+        # beyond its context limit the persistent kernel refuses; "auto" then takes the layered path
+        with pytest.raises(RuntimeError, match="persistent kernel"):
+            mk.step(to_dev(inp))
+        mk = engine("auto", layers=2, vocab=2048)
     out = mk.step(to_dev(inp))
     mk.status()
     ref = oracle.decode_step(oracle.to_fp32(inp), inp["token"], inp["kcache"], inp["vcache"])
     gate_step(oracle, out, ref, f"{path} ctx {ctx}")
 
 
-@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("path", ["layered", "auto"])
 @pytest.mark.parametrize("batch", [2, 5, 8])
 def test_ragged_batch(oracle, path, batch):
     from qwen3mk.kernel import SeqTable
