@@ -1,6 +1,6 @@
 // Persistent cooperative decode kernel: one launch runs a whole batch-1 decode step.
 //
-// One CTA per SM: 16 consumer warps and one producer warp.  The schedule is static (every CTA owns
+// One CTA per SM: 16 consumer warps and two producer warps.  The schedule is static (every CTA owns
 // fixed weight rows) and a layer costs three grid barriers:
 //
 //   Q   x = X0 + dB;  qkv rows = rms(x, ln1) . [wq;wk;wv] rows                 -> qkv (global fp32)
@@ -14,12 +14,12 @@
 // The residual stream lives as "materialised vector + pending delta": every consumer adds the two
 // on load, one CTA writes the sum back for the phase after next.
 //
-// Weights never wait for a barrier.  Each CTA's rows of the four matrices of a layer sit in four
-// shared-memory slots.  The producer warp refills a slot for the next layer as soon as the
-// consumers release it, with cp.async.bulk copies of at most 2 KB issued at a fixed pace, so that
-// HBM traffic is a steady stream instead of bursts: a burst of bulk copies queues in front of the
-// loads and atomics of the barrier that follows it and was measured to triple the barrier latency.
-// GEMV activations are held in registers; shared memory carries the weights only.
+// Weights never wait for a barrier.  Each CTA's rows of the seven matrices of a layer are packed
+// once (pack_weights_kernel) in the order and with the row padding of four shared-memory slots; two
+// producer warps refill a slot for the next layer as soon as the consumers release it, as a steady
+// stream of 16-byte cp.async copies with a bounded number in flight.  The matrix-vector products run
+// on the tensor cores (mma.sync m16n8k16) with the fp32 activation vector split into three bf16
+// columns, which is exact to fp32 and needs no warp-shuffle reductions.
 //
 // A grid barrier is an arrive (red.release) and a later bounded wait (relaxed poll + acquire
 // fence); loads that do not depend on other CTAs (cached K/V rows, norm gains) sit between the two.
@@ -34,7 +34,8 @@ namespace q3 {
 
 constexpr int CW = 16;                        // consumer warps
 constexpr int CT = CW * 32;                   // consumer threads
-constexpr int PT = CT + 32;                   // + one producer warp
+constexpr int NPW = 2;                        // producer warps
+constexpr int PT = CT + 32 * NPW;             // consumers + producers
 constexpr int WO_SLICES = 9;                  // row slices of Wo; CTA c < 144 owns head c % 16, slice c / 16
 constexpr int F_CTAS = Q_HEADS * WO_SLICES;   // 144
 constexpr int GROUP_CTAS = 2 * WO_SLICES;     // CTAs sharing one kv head
@@ -45,7 +46,9 @@ constexpr int PERSIST_MAX_LEN = GROUP_CTAS * SC_HALF - GROUP_CTAS;   // 2286 cac
 constexpr int WROW = 1032;                    // elements between weight rows in shared memory: 1024 + 8 of padding, so that
                                               // the eight row addresses of an ldmatrix fall into different banks
 constexpr int WOROW = 136;                    // the same for the 128-column Wo slice rows
-constexpr int ATT_WARPS = 8;                  // warps that attend positions (32 positions per pass)
+constexpr int ATT_WARPS = 8;                  // split attention: warps that attend positions (32 positions per pass)
+constexpr int LOCAL_PASSES = 6;               // local attention: passes of 64 positions a CTA runs on its own
+constexpr int LOCAL_ATTN_MAX = 64 * LOCAL_PASSES - 1;   // up to this many cached positions every CTA attends its whole head
 constexpr int N_ACC = 2;                      // accumulators for the FFN delta (halves same-address atomics)
 constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
 constexpr int PART_STRIDE = 132;              // floats per published partial: [0] max, [1] sum, [4..132) output
@@ -216,21 +219,13 @@ __device__ __forceinline__ bool mbar_wait_sleepy(uint64_t* b, uint32_t parity, v
     }
 }
 
-#ifdef Q3_FINE
-__device__ unsigned long long g_late[148 * 8];
-#endif
-// consumer side: one lane per warp polls, the rest of the warp waits at a warp barrier
+// consumer side: a single non-blocking test when the slot is already full (the normal case: the
+// producers run a layer ahead); a late slot is polled by one lane per warp
 __device__ __forceinline__ void slot_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
-#ifdef Q3_FINE
-    if (threadIdx.x == 0) {   // debug: cycles thread 0 spends waiting for late slots, per CTA
-        if (!mbar_try_wait(b, parity)) {
-            const long long t0 = clock64();
-            while (!mbar_try_wait(b, parity)) {}
-            g_late[blockIdx.x * 8 + (site - 10)] += (unsigned long long)(clock64() - t0);
-            g_late[blockIdx.x * 8 + 4 + (site - 10)] += 1;
-        }
-    }
-#endif
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    if (__all_sync(0xffffffffu, ok != 0)) return;
     if ((threadIdx.x & 31) == 0) mbar_wait(b, parity, abort_flag, status, site);
     __syncwarp();
 }
@@ -239,6 +234,7 @@ __device__ __forceinline__ void unpack8f(const uint4& u, float* f) {
     f[0] = bf_lo(u.x); f[1] = bf_hi(u.x); f[2] = bf_lo(u.y); f[3] = bf_hi(u.y);
     f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
 }
+__device__ __forceinline__ void f_unpack16(const uint4& a, const uint4& b, float* f) { unpack8f(a, f); unpack8f(b, f + 8); }
 // dot of one 16-byte weight unit with eight activations held in registers
 __device__ __forceinline__ float dot8r(const uint4& w, const float* x) {
     float s = bf_lo(w.x) * x[0];
@@ -295,6 +291,42 @@ __device__ __forceinline__ void load_act_regs(const float* xs, int lane, float* 
     }
 }
 
+// Local attention streams its K rows and then its V rows through one ring of four register buffers:
+// item i (K pass i for i < npl, V pass i - npl after that) lives in buffer i & 3, and the load of
+// item i + 4 is issued the moment item i has been consumed, so a row has four passes to arrive.
+__device__ __forceinline__ void ring_load(uint4 (&buf)[2], int item, int npl, int len, int att_slot, int sub,
+                                          const bf16_raw* kl, const bf16_raw* vl) {
+    const bool is_v = item >= npl;
+    const int pass = is_v ? item - npl : item;
+    const int pos = pass * 64 + att_slot;
+    if (pass < npl && pos < len) {
+        const uint4* row = reinterpret_cast<const uint4*>((is_v ? vl : kl) + (size_t)pos * KV_DIM);
+        buf[0] = ld_stream(row + sub);
+        buf[1] = ld_stream(row + 8 + sub);
+    } else {
+        buf[0] = buf[1] = make_uint4(0, 0, 0, 0);
+    }
+}
+template <int OFF>
+__device__ __forceinline__ void local_pv(uint4 (&ring)[4][2], const float (&sreg)[LOCAL_PASSES], float M, int npl, int len,
+                                         int att_slot, int sub, const bf16_raw* kl, const bf16_raw* vl, float& lsum, float (&acc)[16]) {
+#pragma unroll
+    for (int ps = 0; ps < LOCAL_PASSES; ++ps) {
+        if (ps < npl) {
+            constexpr int dummy = 0; (void)dummy;
+            const int b = (OFF + ps) & 3;
+            const uint4 v0 = ring[b][0], v1 = ring[b][1];
+            if (ps + 4 < npl) ring_load(ring[b], npl + ps + 4, npl, len, att_slot, sub, kl, vl);
+            const float pr = __expf(sreg[ps] - M);   // exp(-inf) = 0 for the slots past the cache
+            lsum += pr;
+            float vf[16];
+            f_unpack16(v0, v1, vf);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = fmaf(pr, vf[i], acc[i]);
+        }
+    }
+}
+
 // ====================================================================================================
 __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -348,46 +380,50 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 #define Q3_TRACE(ev) do { if (p.trace != nullptr && tid == 0) p.trace[(size_t)c * n_ev + (ev)] = global_ns(); } while (0)
     Q3_TRACE(0);
     if (tid == 0) {
-        for (int i = 0; i < 4; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 4; ++i) { mbar_init(&full[i], 32 * NPW); mbar_init(&empty[i], 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();   // the only barrier the producer warp joins
+    __syncthreads();   // the only barrier the producer warps join
 
-    // ================================================================================ producer warp
-    if (warp == CW) {
-        // Pacing: sleep between two copies instead of spinning, so that the producer warp leaves its
-        // scheduler's issue slots to the consumer warps that share it.
-        const unsigned pace = p.pace > 0 ? (unsigned)p.pace : (unsigned)DEFAULT_PACE;
-        auto pace_wait = [&]() { __nanosleep(pace); };
-        // The packed share is laid out exactly like the slots, padding included, so a slot is a few
-        // large contiguous copies (a bulk copy costs ~230 ns of TMA time whatever its size: 2 KB copies
-        // top out at 1.25 TB/s over the GPU, 16 KB copies stream above 7 TB/s).
+    // ================================================================================ producer warps
+    // Weights reach shared memory through cp.async (16-byte LDGSTS copies on the load/store path),
+    // not through the TMA unit: measured on B200, a grid barrier that runs while bulk copies stream
+    // takes 2.1 us at 2.4 TB/s of background traffic and 2.6 us at 4.7 TB/s (1.55 us idle), whereas
+    // the same traffic issued as cp.async by two warps (3.4 TB/s) leaves it at 1.66 us.  Each producer
+    // lane keeps up to 8 groups of 16 copies in flight (64 KB per warp); a lane's arrival on the
+    // slot's mbarrier is tied to the completion of its copies (cp.async.mbarrier.arrive.noinc).
+    if (warp >= CW) {
+        const int pw = warp - CW;
         const int slot_rows[4] = {qmax, WO_ROWS_MAX, 2 * imax, imax};
         bf16_raw* const slot_dst[4] = {sA, sB, sC, sD};
         bool alive = true;
+        int in_group = 0;
         for (int l = 0; l < L && alive; ++l) {
-            const bf16_raw* src = p.packed + ((size_t)l * G + c) * share_elems(G);
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(p.packed + ((size_t)l * G + c) * share_elems(G));
             for (int slot = 0; slot < 4 && alive; ++slot) {
-                const uint32_t bytes = (uint32_t)slot_rows[slot] * (slot == 1 ? WOROW : WROW) * 2u;
+                const int bytes = slot_rows[slot] * (slot == 1 ? WOROW : WROW) * 2;
                 if (!(slot == 1 && !has_f)) {
                     if (l > 0) alive = mbar_wait_sleepy(&empty[slot], (l - 1) & 1, abort_flag, p.status, 20 + slot);
                     if (!alive) break;
-                    if (lane == 0) {
-                        fence_proxy_async();
-                        mbar_expect_tx(&full[slot], bytes);
-                        for (uint32_t off = 0; off < bytes; off += COPY_BYTES) {
-                            const uint32_t n = min((uint32_t)COPY_BYTES, bytes - off);
-                            bulk_g2s(reinterpret_cast<unsigned char*>(slot_dst[slot]) + off, reinterpret_cast<const unsigned char*>(src) + off, n, &full[slot]);
-                            pace_wait();
+                    const uint32_t dst = smem_u32(slot_dst[slot]);
+                    const int pieces = bytes >> 4;
+                    for (int i = pw * 32 + lane; i < pieces; i += NPW * 32) {
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 16), "l"(src + (size_t)i * 16) : "memory");
+                        if (++in_group == 16) {
+                            asm volatile("cp.async.commit_group;" ::: "memory");
+                            asm volatile("cp.async.wait_group 7;" ::: "memory");
+                            in_group = 0;
                         }
                     }
-                    __syncwarp();
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[slot])) : "memory");
                 }
-                src += bytes / 2;
+                src += bytes;
             }
         }
-        return;   // every copy issued here is awaited by the consumers before the CTA ends
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        return;
     }
 
     // ================================================================================ consumer warps
@@ -418,6 +454,10 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     const int cp0 = min(len, fj * chunk), cp1 = min(len, cp0 + chunk);
     const int npass = (cp1 - cp0 + 31) >> 5;                  // 32 positions per pass (warps 0..7, a quarter-warp each)
     const int att_slot = warp * 4 + quarter;                  // < 32 for the attending warps
+    // Short caches: every CTA recomputes the attention of its own head over all positions (no exchange between
+    // CTAs; the K/V rows come from L2).  Longer caches: the 18 CTAs of a kv group split the positions.
+    const bool local_attn = len <= LOCAL_ATTN_MAX;
+    const int npl = (len + 63) >> 6;                          // local attention: passes of 64 positions (16 warps x 4 quarter-warps)
 
     // gains of the next GEMV phase, fetched ahead of the barrier wait
     uint32_t gain2 = *reinterpret_cast<const uint32_t*>(p.ln1 + 2 * tid);
@@ -463,19 +503,33 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             Q3_FINE_T(1);
             slot_wait(&full[0], l & 1, abort_flag, p.status, 10);
             Q3_FINE_T(2);
+            {
+                uint32_t af[2][4][4];
 #pragma unroll
-            for (int rt = 0; rt < 2; ++rt) {
-                float cc[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint32_t abase = smem_u32(sA + (size_t)(16 * rt + lm_row) * WROW + 64 * warp + lm_k);
+                for (int rt = 0; rt < 2; ++rt) {
+                    const uint32_t abase = smem_u32(sA + (size_t)(16 * rt + lm_row) * WROW + 64 * warp + lm_k);
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    uint32_t af[4];
-                    ldsm_x4(af, abase + 32 * t);
-                    mma_bf16(cc, af, bq[t][0], bq[t][1]);
+                    for (int t = 0; t < 4; ++t) ldsm_x4(af[rt][t], abase + 32 * t);
                 }
-                float r0, r1;
-                fold_cols(cc, r0, r1);
-                if ((lane & 3) == 0) { part[warp * 32 + 16 * rt + fr_n] = r0; part[warp * 32 + 16 * rt + fr_n + 8] = r1; }
+                float cc[2][2][4];
+#pragma unroll
+                for (int rt = 0; rt < 2; ++rt)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) cc[rt][h][i] = 0.f;
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int rt = 0; rt < 2; ++rt) mma_bf16(cc[rt][t & 1], af[rt][t], bq[t][0], bq[t][1]);
+#pragma unroll
+                for (int rt = 0; rt < 2; ++rt) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) cc[rt][0][i] += cc[rt][1][i];
+                    float r0, r1;
+                    fold_cols(cc[rt][0], r0, r1);
+                    if ((lane & 3) == 0) { part[warp * 32 + 16 * rt + fr_n] = r0; part[warp * 32 + 16 * rt + fr_n + 8] = r1; }
+                }
             }
             cta_sync();
             if (tid < nq) {
@@ -494,22 +548,25 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         target += G;
 
         // ---- between arrive and wait: what the F phase needs that no other CTA produces ----
-        uint4 kpre[2][2], vpre[2][2];
+        uint4 ring[4][2];   // local attention: the K/V ring; split attention: [0], [1] = K passes, [2], [3] = V passes
         float gq[4] = {0.f, 0.f, 0.f, 0.f}, cs[4] = {0.f, 0.f, 0.f, 0.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
         const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
         const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
         if (has_f) {
-            if (warp < ATT_WARPS) {
+            if (local_attn) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl, vl);
+            } else if (warp < ATT_WARPS) {
 #pragma unroll
                 for (int ps = 0; ps < 2; ++ps) {
                     const int pos = cp0 + ps * 32 + att_slot;
                     if (pos < cp1) {
                         const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
                         const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
-                        kpre[ps][0] = ld_stream(kr + sub); kpre[ps][1] = ld_stream(kr + 8 + sub);
-                        vpre[ps][0] = ld_stream(vr + sub); vpre[ps][1] = ld_stream(vr + 8 + sub);
+                        ring[ps][0] = ld_stream(kr + sub); ring[ps][1] = ld_stream(kr + 8 + sub);
+                        ring[2 + ps][0] = ld_stream(vr + sub); ring[2 + ps][1] = ld_stream(vr + 8 + sub);
                     } else {
-                        kpre[ps][0] = kpre[ps][1] = vpre[ps][0] = vpre[ps][1] = make_uint4(0, 0, 0, 0);
+                        ring[ps][0] = ring[ps][1] = ring[2 + ps][0] = ring[2 + ps][1] = make_uint4(0, 0, 0, 0);
                     }
                 }
             }
@@ -565,135 +622,212 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             cta_sync();
             Q3_TRACE(ev + 3);
 
-            // ---- scores of this CTA's cached positions, both heads: a quarter-warp per position ----
-            float tmax0 = -INFINITY, tmax1 = -INFINITY;
-            if (warp < ATT_WARPS) {
-                float qa[2][16];
+            if (local_attn) {
+                // ---- local attention of head fh over all cached positions: scores stay in registers ----
+                float qa[16];
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh)
+                for (int i = 0; i < 8; ++i) { qa[i] = q_s[fhh * 128 + sub * 8 + i]; qa[8 + i] = q_s[fhh * 128 + 64 + sub * 8 + i]; }
+                float sreg[LOCAL_PASSES];
+                float tmax = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) { qa[hh][i] = q_s[hh * 128 + sub * 8 + i]; qa[hh][8 + i] = q_s[hh * 128 + 64 + sub * 8 + i]; }
-                for (int ps = 0; ps < npass; ++ps) {
-                    const int idx = ps * 32 + att_slot, pos = cp0 + idx;
-                    uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0;
-                    if (ps == 0) { k0 = kpre[0][0]; k1 = kpre[0][1]; }
-                    else if (ps == 1) { k0 = kpre[1][0]; k1 = kpre[1][1]; }
-                    else if (pos < cp1) {
-                        const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
-                        k0 = ld_stream(kr + sub); k1 = ld_stream(kr + 8 + sub);
-                    }
-                    float kf[16];
-                    unpack8f(k0, kf); unpack8f(k1, kf + 8);
-                    float s0 = 0.f, s1 = 0.f;
+                for (int ps = 0; ps < LOCAL_PASSES; ++ps) {
+                    sreg[ps] = -INFINITY;
+                    if (ps < npl) {
+                        const int pos = ps * 64 + att_slot;
+                        const uint4 k0 = ring[ps & 3][0], k1 = ring[ps & 3][1];
+                        if (ps + 4 < 2 * npl) ring_load(ring[ps & 3], ps + 4, npl, len, att_slot, sub, kl, vl);
+                        float kf[16];
+                        unpack8f(k0, kf); unpack8f(k1, kf + 8);
+                        float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) { s0 = fmaf(qa[0][i], kf[i], s0); s1 = fmaf(qa[1][i], kf[i], s1); }
-#pragma unroll
-                    for (int o = 1; o <= 4; o <<= 1) {
-                        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-                    }
-                    if (pos < cp1) {
-                        tmax0 = fmaxf(tmax0, s0); tmax1 = fmaxf(tmax1, s1);
-                        if (sub == 0) { sc[idx] = s0; sc[SC_HALF + idx] = s1; }
+                        for (int i = 0; i < 8; ++i) { s0 = fmaf(qa[i], kf[i], s0); s1 = fmaf(qa[8 + i], kf[8 + i], s1); }
+                        s0 += s1;
+                        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+                        s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+                        s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
+                        if (pos < len) { sreg[ps] = s0; tmax = fmaxf(tmax, s0); }
                     }
                 }
-                tmax0 = warp_max(tmax0); tmax1 = warp_max(tmax1);
-                if (lane == 0) { red[warp] = tmax0; red[8 + warp] = tmax1; }
-            } else if (warp == 12) {   // the new row's score for this CTA's own head: q . k_new in fp32, unrounded
-                const float4 a = *reinterpret_cast<const float4*>(q_s + fhh * 128 + lane * 4);
-                const float4 b = *reinterpret_cast<const float4*>(k_s + lane * 4);
-                const float sn_ = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
-                if (lane == 0) misc[0] = sn_;
-            }
-            cta_sync();
-            float M0 = (lane < ATT_WARPS) ? red[lane] : -INFINITY, M1 = (lane < ATT_WARPS) ? red[8 + lane] : -INFINITY;
-            M0 = warp_max(M0); M1 = warp_max(M1);
+                if (warp == 12) {   // the new row's score: q . k_new in fp32, unrounded
+                    const float4 a = *reinterpret_cast<const float4*>(q_s + fhh * 128 + lane * 4);
+                    const float4 b = *reinterpret_cast<const float4*>(k_s + lane * 4);
+                    const float sn_ = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
+                    if (lane == 0) misc[0] = sn_;
+                    tmax = fmaxf(tmax, sn_);
+                }
+                tmax = warp_max(tmax);
+                if (lane == 0) red[warp] = tmax;
+                cta_sync();
+                float M = (lane < CW) ? red[lane] : -INFINITY;
+                M = warp_max(M);
 
-            // ---- probabilities and P.V against the CTA-wide maxima: the partial sums just add ----
-            if (warp < ATT_WARPS) {
-                float l0 = 0.f, l1 = 0.f, acc[2][16];
+                float lsum = 0.f, acc[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) { acc[0][i] = 0.f; acc[1][i] = 0.f; }
-                for (int ps = 0; ps < npass; ++ps) {
-                    const int idx = ps * 32 + att_slot, pos = cp0 + idx;
-                    uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
-                    if (ps == 0) { v0 = vpre[0][0]; v1 = vpre[0][1]; }
-                    else if (ps == 1) { v0 = vpre[1][0]; v1 = vpre[1][1]; }
-                    else if (pos < cp1) {
-                        const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
-                        v0 = ld_stream(vr + sub); v1 = ld_stream(vr + 8 + sub);
-                    }
-                    if (pos < cp1) {
-                        const float p0 = __expf(sc[idx] - M0), p1 = __expf(sc[SC_HALF + idx] - M1);
-                        l0 += p0; l1 += p1;
-                        float vf[16];
-                        unpack8f(v0, vf); unpack8f(v1, vf + 8);
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) { acc[0][i] = fmaf(p0, vf[i], acc[0][i]); acc[1][i] = fmaf(p1, vf[i], acc[1][i]); }
-                    }
+                for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+                switch (npl & 3) {   // V pass 0 sits in ring buffer npl & 3
+                    case 0: local_pv<0>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
+                    case 1: local_pv<1>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
+                    case 2: local_pv<2>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
+                    default: local_pv<3>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
                 }
-                // fold the four quarter-warp partials of the warp (lanes with equal `sub` hold the same dims)
 #pragma unroll
                 for (int off = 8; off <= 16; off <<= 1) {
-                    l0 += __shfl_xor_sync(0xffffffffu, l0, off);
-                    l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+                    lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        acc[0][i] += __shfl_xor_sync(0xffffffffu, acc[0][i], off);
-                        acc[1][i] += __shfl_xor_sync(0xffffffffu, acc[1][i], off);
-                    }
+                    for (int i = 0; i < 16; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
                 }
                 if (quarter == 0) {
 #pragma unroll
+                    for (int i = 0; i < 8; ++i) { om[warp * 128 + sub * 8 + i] = acc[i]; om[warp * 128 + 64 + sub * 8 + i] = acc[8 + i]; }
+                    if (sub == 0) lw[warp] = lsum;
+                }
+                cta_sync();
+                Q3_TRACE(ev + 4);
+                Q3_TRACE(ev + 5);
+                if (tid < HEAD_DIM) {
+                    const float pn = __expf(misc[0] - M);
+                    float Ls = pn, o = pn * v_s[tid];
+#pragma unroll
+                    for (int w = 0; w < CW; ++w) { Ls += lw[w]; o += om[w * 128 + tid]; }
+                    bf16_raw h, m, lo_;
+                    split3(o / Ls, h, m, lo_);
+                    reinterpret_cast<bf16_raw*>(osp)[tid] = h;
+                    reinterpret_cast<bf16_raw*>(osp + 64)[tid] = m;
+                    reinterpret_cast<bf16_raw*>(osp + 128)[tid] = lo_;
+                }
+                cta_sync();
+            } else {
+            // ---- scores of this CTA's cached positions, both heads: a quarter-warp per position ----
+                float tmax0 = -INFINITY, tmax1 = -INFINITY;
+                if (warp < ATT_WARPS) {
+                    float qa[2][16];
+#pragma unroll
                     for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            om[(warp * 2 + hh) * 128 + sub * 8 + i] = acc[hh][i];
-                            om[(warp * 2 + hh) * 128 + 64 + sub * 8 + i] = acc[hh][8 + i];
+                        for (int i = 0; i < 8; ++i) { qa[hh][i] = q_s[hh * 128 + sub * 8 + i]; qa[hh][8 + i] = q_s[hh * 128 + 64 + sub * 8 + i]; }
+                    for (int ps = 0; ps < npass; ++ps) {
+                        const int idx = ps * 32 + att_slot, pos = cp0 + idx;
+                        uint4 k0 = make_uint4(0, 0, 0, 0), k1 = k0;
+                        if (ps == 0) { k0 = ring[0][0]; k1 = ring[0][1]; }
+                        else if (ps == 1) { k0 = ring[1][0]; k1 = ring[1][1]; }
+                        else if (pos < cp1) {
+                            const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
+                            k0 = ld_stream(kr + sub); k1 = ld_stream(kr + 8 + sub);
                         }
-                    if (sub == 0) { lw[warp * 2] = l0; lw[warp * 2 + 1] = l1; }
-                }
-            }
-            cta_sync();
-            // ---- publish the CTA's partial of both heads: (max, sum, unnormalised output) ----
-            if (tid < 256) {
-                const int hh = tid >> 7, d = tid & 127;
-                float o = 0.f, Ls = 0.f;
+                        float kf[16];
+                        unpack8f(k0, kf); unpack8f(k1, kf + 8);
+                        float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-                for (int w = 0; w < ATT_WARPS; ++w) { o += om[(w * 2 + hh) * 128 + d]; Ls += lw[w * 2 + hh]; }
-                float* dst = p.part + ((size_t)(fg * GROUP_CTAS + fj) * 2 + hh) * PART_STRIDE;
-                if (d == 0) { __stcg(dst, hh ? M1 : M0); __stcg(dst + 1, Ls); }
-                __stcg(dst + 4 + d, o);
-            }
-            cta_sync();
-            Q3_TRACE(ev + 4);
-            if (tid == 0) counter_arrive(grp);
-            gtarget += GROUP_CTAS;
-            counter_wait(grp, gtarget, abort_flag, p.status, 400 + l);
-            Q3_TRACE(ev + 5);
+                        for (int i = 0; i < 16; ++i) { s0 = fmaf(qa[0][i], kf[i], s0); s1 = fmaf(qa[1][i], kf[i], s1); }
+#pragma unroll
+                        for (int o = 1; o <= 4; o <<= 1) {
+                            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+                        }
+                        if (pos < cp1) {
+                            tmax0 = fmaxf(tmax0, s0); tmax1 = fmaxf(tmax1, s1);
+                            if (sub == 0) { sc[idx] = s0; sc[SC_HALF + idx] = s1; }
+                        }
+                    }
+                    tmax0 = warp_max(tmax0); tmax1 = warp_max(tmax1);
+                    if (lane == 0) { red[warp] = tmax0; red[8 + warp] = tmax1; }
+                } else if (warp == 12) {   // the new row's score for this CTA's own head: q . k_new in fp32, unrounded
+                    const float4 a = *reinterpret_cast<const float4*>(q_s + fhh * 128 + lane * 4);
+                    const float4 b = *reinterpret_cast<const float4*>(k_s + lane * 4);
+                    const float sn_ = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
+                    if (lane == 0) misc[0] = sn_;
+                }
+                cta_sync();
+                float M0 = (lane < ATT_WARPS) ? red[lane] : -INFINITY, M1 = (lane < ATT_WARPS) ? red[8 + lane] : -INFINITY;
+                M0 = warp_max(M0); M1 = warp_max(M1);
 
-            // ---- merge the 18 partials of this CTA's head with the new row ----
-            if (tid < HEAD_DIM) {
-                const float* src = p.part + ((size_t)fg * GROUP_CTAS * 2 + fhh) * PART_STRIDE;
-                const float s_new = misc[0];
-                float mj[GROUP_CTAS], M = s_new;
+                // ---- probabilities and P.V against the CTA-wide maxima: the partial sums just add ----
+                if (warp < ATT_WARPS) {
+                    float l0 = 0.f, l1 = 0.f, acc[2][16];
 #pragma unroll
-                for (int j = 0; j < GROUP_CTAS; ++j) { mj[j] = __ldcg(src + (size_t)j * 2 * PART_STRIDE); M = fmaxf(M, mj[j]); }
-                const float pn = __expf(s_new - M);
-                float Ls = pn, o = pn * v_s[tid];
+                    for (int i = 0; i < 16; ++i) { acc[0][i] = 0.f; acc[1][i] = 0.f; }
+                    for (int ps = 0; ps < npass; ++ps) {
+                        const int idx = ps * 32 + att_slot, pos = cp0 + idx;
+                        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+                        if (ps == 0) { v0 = ring[2][0]; v1 = ring[2][1]; }
+                        else if (ps == 1) { v0 = ring[3][0]; v1 = ring[3][1]; }
+                        else if (pos < cp1) {
+                            const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
+                            v0 = ld_stream(vr + sub); v1 = ld_stream(vr + 8 + sub);
+                        }
+                        if (pos < cp1) {
+                            const float p0 = __expf(sc[idx] - M0), p1 = __expf(sc[SC_HALF + idx] - M1);
+                            l0 += p0; l1 += p1;
+                            float vf[16];
+                            unpack8f(v0, vf); unpack8f(v1, vf + 8);
 #pragma unroll
-                for (int j = 0; j < GROUP_CTAS; ++j) {
-                    const float wgt = __expf(mj[j] - M);    // 0 for a CTA that had no positions (max = -inf)
-                    Ls = fmaf(__ldcg(src + (size_t)j * 2 * PART_STRIDE + 1), wgt, Ls);
-                    o = fmaf(__ldcg(src + (size_t)j * 2 * PART_STRIDE + 4 + tid), wgt, o);
+                            for (int i = 0; i < 16; ++i) { acc[0][i] = fmaf(p0, vf[i], acc[0][i]); acc[1][i] = fmaf(p1, vf[i], acc[1][i]); }
+                        }
+                    }
+                    // fold the four quarter-warp partials of the warp (lanes with equal `sub` hold the same dims)
+#pragma unroll
+                    for (int off = 8; off <= 16; off <<= 1) {
+                        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+                        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            acc[0][i] += __shfl_xor_sync(0xffffffffu, acc[0][i], off);
+                            acc[1][i] += __shfl_xor_sync(0xffffffffu, acc[1][i], off);
+                        }
+                    }
+                    if (quarter == 0) {
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                om[(warp * 2 + hh) * 128 + sub * 8 + i] = acc[hh][i];
+                                om[(warp * 2 + hh) * 128 + 64 + sub * 8 + i] = acc[hh][8 + i];
+                            }
+                        if (sub == 0) { lw[warp * 2] = l0; lw[warp * 2 + 1] = l1; }
+                    }
                 }
-                bf16_raw h, m, lo_;
-                split3(o / Ls, h, m, lo_);
-                reinterpret_cast<bf16_raw*>(osp)[tid] = h;
-                reinterpret_cast<bf16_raw*>(osp + 64)[tid] = m;
-                reinterpret_cast<bf16_raw*>(osp + 128)[tid] = lo_;
+                cta_sync();
+                // ---- publish the CTA's partial of both heads: (max, sum, unnormalised output) ----
+                if (tid < 256) {
+                    const int hh = tid >> 7, d = tid & 127;
+                    float o = 0.f, Ls = 0.f;
+#pragma unroll
+                    for (int w = 0; w < ATT_WARPS; ++w) { o += om[(w * 2 + hh) * 128 + d]; Ls += lw[w * 2 + hh]; }
+                    float* dst = p.part + ((size_t)(fg * GROUP_CTAS + fj) * 2 + hh) * PART_STRIDE;
+                    if (d == 0) { __stcg(dst, hh ? M1 : M0); __stcg(dst + 1, Ls); }
+                    __stcg(dst + 4 + d, o);
+                }
+                cta_sync();
+                Q3_TRACE(ev + 4);
+                if (tid == 0) counter_arrive(grp);
+                gtarget += GROUP_CTAS;
+                counter_wait(grp, gtarget, abort_flag, p.status, 400 + l);
+                Q3_TRACE(ev + 5);
+
+                // ---- merge the 18 partials of this CTA's head with the new row ----
+                if (tid < HEAD_DIM) {
+                    const float* src = p.part + ((size_t)fg * GROUP_CTAS * 2 + fhh) * PART_STRIDE;
+                    const float s_new = misc[0];
+                    float mj[GROUP_CTAS], M = s_new;
+#pragma unroll
+                    for (int j = 0; j < GROUP_CTAS; ++j) { mj[j] = __ldcg(src + (size_t)j * 2 * PART_STRIDE); M = fmaxf(M, mj[j]); }
+                    const float pn = __expf(s_new - M);
+                    float Ls = pn, o = pn * v_s[tid];
+#pragma unroll
+                    for (int j = 0; j < GROUP_CTAS; ++j) {
+                        const float wgt = __expf(mj[j] - M);    // 0 for a CTA that had no positions (max = -inf)
+                        Ls = fmaf(__ldcg(src + (size_t)j * 2 * PART_STRIDE + 1), wgt, Ls);
+                        o = fmaf(__ldcg(src + (size_t)j * 2 * PART_STRIDE + 4 + tid), wgt, o);
+                    }
+                    bf16_raw h, m, lo_;
+                    split3(o / Ls, h, m, lo_);
+                    reinterpret_cast<bf16_raw*>(osp)[tid] = h;
+                    reinterpret_cast<bf16_raw*>(osp + 64)[tid] = m;
+                    reinterpret_cast<bf16_raw*>(osp + 128)[tid] = lo_;
+                }
+                cta_sync();
+
             }
-            cta_sync();
 
             // ---- Wo slice on the tensor cores: warp (rt, kh) = 16 rows x 64 head dims ----
             slot_wait(&full[1], l & 1, abort_flag, p.status, 11);
@@ -767,16 +901,17 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 Q3_FINE_T(7);
 #pragma unroll
                 for (int rt = 0; rt < 2; ++rt) {
-                    float cc[4] = {0.f, 0.f, 0.f, 0.f};
                     const uint32_t abase = smem_u32(sC + (size_t)(mat * imax + 16 * rt + lm_row) * WROW + 128 * ke + lm_k);
+                    uint32_t af[8][4];
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) {
-                        uint32_t af[4];
-                        ldsm_x4(af, abase + 32 * t);
-                        mma_bf16(cc, af, bx[t][0], bx[t][1]);
-                    }
+                    for (int t = 0; t < 8; ++t) ldsm_x4(af[t], abase + 32 * t);
+                    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int t = 0; t < 8; t += 2) { mma_bf16(c0, af[t], bx[t][0], bx[t][1]); mma_bf16(c1, af[t + 1], bx[t + 1][0], bx[t + 1][1]); }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) c0[i] += c1[i];
                     float r0, r1;
-                    fold_cols(cc, r0, r1);
+                    fold_cols(c0, r0, r1);
                     if ((lane & 3) == 0) { part[ke * 64 + mat * 32 + 16 * rt + fr_n] = r0; part[ke * 64 + mat * 32 + 16 * rt + fr_n + 8] = r1; }
                 }
                 Q3_FINE_T(8);
@@ -814,20 +949,29 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 }
                 // transposed ldmatrix: lanes 0-7 / 8-15 / 16-23 / 24-31 address rows i of the blocks (n 0-7, i 0-7), (n 8-15, i 0-7), (n 0-7, i 8-15), (n 8-15, i 8-15)
                 const int ti = (lane & 7) + ((lane >> 4) & 1) * 8, tn = ((lane >> 3) & 1) * 8;
+                uint32_t af[4][2][4];
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    const int n0 = 64 * warp + 16 * nt;
-                    float cc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
                         int i = 16 * t + ti;
                         if (i >= ni) i = 0;   // hid is zero there; any finite row will do
-                        uint32_t af[4];
-                        ldsm_x4_trans(af, smem_u32(sD + (size_t)i * WROW + n0 + tn));
-                        mma_bf16(cc, af, bh[t][0], bh[t][1]);
+                        ldsm_x4_trans(af[nt][t], smem_u32(sD + (size_t)i * WROW + 64 * warp + 16 * nt + tn));
                     }
+                float cc[4][4];
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) cc[nt][i] = 0.f;
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) mma_bf16(cc[nt], af[nt][t], bh[t][0], bh[t][1]);
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const int n0 = 64 * warp + 16 * nt;
                     float r0, r1;
-                    fold_cols(cc, r0, r1);
+                    fold_cols(cc[nt], r0, r1);
                     if ((lane & 3) == 0) { dout[n0 + fr_n] = r0; dout[n0 + fr_n + 8] = r1; }
                 }
             }
@@ -952,13 +1096,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 #undef Q3_FINE_T
 }
 
-#ifdef Q3_FINE
-extern "C" int q3_debug_late(unsigned long long* host, int clear) {
-    cudaMemcpyFromSymbol(host, g_late, sizeof(g_late));
-    if (clear) { static unsigned long long z[148 * 8]; cudaMemcpyToSymbol(g_late, z, sizeof(z)); }
-    return 0;
-}
-#endif
 
 // ---- weight packing ----------------------------------------------------------------------------------
 // packed[l][c] = everything CTA c streams for layer l, in the order and with the row padding of its
