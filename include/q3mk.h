@@ -129,6 +129,18 @@ int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream);
 /* Enqueue a causal prefill on `stream`. */
 int q3_prefill(q3_engine* e, const q3_prefill_args* a, void* stream);
 
+/* One layered decode step WITHOUT an engine and without any device allocation, for callers that may
+ * not call cudaMalloc where they decode (a plugin inside another runtime's memory budget, a process
+ * whose device memory is fully pre-carved).  It has no counterpart in the reference.  The scratch is a
+ * device array inside the library (about 0.4 MB per GPU, held until the process exits), which limits a
+ * call to Q3_NOALLOC_MAX_BATCH sequences; larger batches are rejected with Q3_ERR_INVALID.  The first
+ * call on a device looks up the array's address (make it before any stream capture).  All calls share
+ * the array: do not let two calls overlap on the GPU.  `w`, `rope` and `a` are as for q3_set_weights,
+ * q3_set_rope and q3_decode; only the layered path is available. */
+#define Q3_NOALLOC_MAX_BATCH 2
+int q3_decode_noalloc(const q3_weights* w, const float* rope, int32_t rope_positions, int32_t n_layers, int32_t vocab,
+                      const q3_decode_args* a, void* stream);
+
 /* Synchronise `stream`, read the device status words and clear them.  Returns Q3_OK or
  * Q3_ERR_DEVICE_WAIT; `words` (may be NULL) receives up to `n` raw status words:
  * [0] error code, [1] where (phase id), [2] CTA index, [3] observed counter value. */

@@ -177,7 +177,7 @@ static int splits_for(const q3_engine* e, int batch, int max_len) {
     return s;
 }
 
-static int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
+int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
     const int B = a->batch, L = e->cfg.n_layers, V = e->cfg.vocab;
     const q3_weights& w = e->w;
     const int append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;

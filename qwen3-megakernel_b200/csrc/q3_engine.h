@@ -49,4 +49,6 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st);
 int persist_weights_changed(q3_engine* e);
 void persist_invalidate_weights(q3_engine* e);
 int engine_fail(q3_engine* e, int code, const char* fmt, ...);
+// the layered decode step on engine `e` (one launch per phase); `e` supplies weights, RoPE table and scratch
+int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st);
 }  // namespace q3
