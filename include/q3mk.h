@@ -141,6 +141,16 @@ int q3_prefill(q3_engine* e, const q3_prefill_args* a, void* stream);
 int q3_decode_noalloc(const q3_weights* w, const float* rope, int32_t rope_positions, int32_t n_layers, int32_t vocab,
                       const q3_decode_args* a, void* stream);
 
+/* out[t, n] = (resid[t, n] +) sum_k w[n, k] * x[t, k] on the tensor cores (tcgen05 / TMEM / TMA): w bf16
+ * [n_rows, K] row-major (n_rows a multiple of 128, K of 64), x fp32 [n_tok, K], out and resid fp32
+ * [n_tok, n_rows] (resid may be NULL or alias out).  x is split into `nsplit` bf16 planes (1: rounded to
+ * bf16, 3: exact to fp32) in the caller's `planes` buffer of at least nsplit * round_up(n_tok, tile) * K * 2
+ * bytes, tile = 32 / 64 / 128 for n_tok <= 32 / <= 64 / more.  This is the dense product the reference's
+ * prefill writes as `xn @ w.T` (qwen3mk/prefill.py:61-80); the engine uses it for prefill and for decode
+ * batches too large for the persistent kernel.  Allocates nothing. */
+int q3_linear_tc(const void* w, const float* x, float* out, const float* resid, int32_t n_rows, int32_t n_tok, int32_t K,
+                 int32_t nsplit, void* planes, int64_t planes_bytes, void* stream);
+
 /* Synchronise `stream`, read the device status words and clear them.  Returns Q3_OK or
  * Q3_ERR_DEVICE_WAIT; `words` (may be NULL) receives up to `n` raw status words:
  * [0] error code, [1] where (phase id), [2] CTA index, [3] observed counter value. */

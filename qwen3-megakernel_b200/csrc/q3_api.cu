@@ -6,6 +6,7 @@
 #include <new>
 
 #include "q3_engine.h"
+#include "q3_gemm_tc.h"
 
 using namespace q3;
 
@@ -58,18 +59,27 @@ extern "C" int q3_create(int device, const q3_config* cfg, q3_engine** out) {
     e->sm_count = prop.multiProcessorCount;
     e->max_splits = Q3_MAX_SPLITS;
     e->lm_grid = e->sm_count * 8;
-    const size_t B = (size_t)cfg->max_batch;
+    e->cap = cfg->max_batch > cfg->max_tokens ? cfg->max_batch : cfg->max_tokens;
+    const size_t B = (size_t)e->cap;
+    // attention partials: up to 64 splits for small batches, at least 2 per token for large ones
+    e->part_slots = (int)((B < 16 ? B : 16) * Q3_MAX_SPLITS > 2 * B ? (B < 16 ? B : 16) * Q3_MAX_SPLITS : 2 * B);
+    const bool tc = e->cap >= Q3_TC_MIN_BATCH;
+    const size_t cap_pad = (B + 127) / 128 * 128;
     int rc;
     if ((rc = alloc(e, (void**)&e->x, B * HIDDEN * 4)) ||
         (rc = alloc(e, (void**)&e->qkv, B * QKV_DIM * 4)) ||
         (rc = alloc(e, (void**)&e->attn, B * Q_DIM * 4)) ||
         (rc = alloc(e, (void**)&e->hid, B * INTER * 4)) ||
-        (rc = alloc(e, (void**)&e->part, B * Q_HEADS * e->max_splits * ATTN_PART_STRIDE * 4)) ||
-        (rc = alloc(e, (void**)&e->pval, B * e->lm_grid * 4)) ||
-        (rc = alloc(e, (void**)&e->pidx, B * e->lm_grid * 4)) ||
+        (rc = alloc(e, (void**)&e->part, (size_t)e->part_slots * Q_HEADS * ATTN_PART_STRIDE * 4)) ||
+        (rc = alloc(e, (void**)&e->pval, (size_t)cfg->max_batch * e->lm_grid * 4)) ||
+        (rc = alloc(e, (void**)&e->pidx, (size_t)cfg->max_batch * e->lm_grid * 4)) ||
         (rc = alloc(e, (void**)&e->status, Q3_STATUS_WORDS * 4)) ||
         (rc = alloc(e, (void**)&e->sync, Q3_SYNC_WORDS * 4)) ||
-        (rc = alloc(e, (void**)&e->pf_desc, 64))) {
+        (rc = alloc(e, (void**)&e->pf_desc, 64 + B * 32)) ||
+        (tc && ((rc = alloc(e, &e->planes, 3 * cap_pad * INTER * 2)) ||
+                (rc = alloc(e, (void**)&e->gate, B * INTER * 4)) ||
+                (rc = alloc(e, (void**)&e->up, B * INTER * 4)) ||
+                (cfg->max_batch >= Q3_TC_MIN_BATCH && (rc = alloc(e, (void**)&e->logits_tc, (size_t)cfg->max_batch * cfg->vocab * 4)))))) {
         strncpy(g_create_error, e->err, sizeof(g_create_error) - 1);
         q3_destroy(e);
         return rc;
@@ -88,7 +98,7 @@ extern "C" void q3_destroy(q3_engine* e) {
     if (!e) return;
     cudaSetDevice(e->device);
     persist_teardown(e);
-    void* bufs[] = {e->x, e->qkv, e->attn, e->hid, e->part, e->pval, e->pidx, e->status, e->sync, e->pf_desc};
+    void* bufs[] = {e->x, e->qkv, e->attn, e->hid, e->part, e->pval, e->pidx, e->status, e->sync, e->pf_desc, e->planes, e->gate, e->up, e->logits_tc};
     for (void* p : bufs)
         if (p) cudaFree(p);
     delete e;
@@ -140,7 +150,7 @@ extern "C" int q3_grid_info(const q3_engine* e, int32_t* ctas, int32_t* threads,
 
 extern "C" int q3_scratch(const q3_engine* e, const char* name, void** ptr, int64_t* bytes) {
     if (!e || !name || !ptr || !bytes) return Q3_ERR_INVALID;
-    const int64_t B = e->cfg.max_batch;
+    const int64_t B = e->cap;
     if (!strcmp(name, "x")) { *ptr = e->x; *bytes = B * HIDDEN * 4; }
     else if (!strcmp(name, "qkv")) { *ptr = e->qkv; *bytes = B * QKV_DIM * 4; }
     else if (!strcmp(name, "attn")) { *ptr = e->attn; *bytes = B * Q_DIM * 4; }
@@ -174,14 +184,22 @@ static int splits_for(const q3_engine* e, int batch, int max_len) {
     int s = by_len < by_fill ? by_len : by_fill;
     if (s < 1) s = 1;
     if (s > e->max_splits) s = e->max_splits;
+    if (e->part_slots > 0 && s * batch > e->part_slots) s = e->part_slots / batch;
+    if (s < 1) s = 1;
     return s;
 }
 
-int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
+int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes, bool last_token_only) {
     const int B = a->batch, L = e->cfg.n_layers, V = e->cfg.vocab;
     const q3_weights& w = e->w;
     const int append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
     const int ns = splits_for(e, B, a->max_len);
+    // From Q3_TC_MIN_BATCH tokens on, the projections are tensor-core GEMMs over bf16 planes of the
+    // activations (tc_planes = 3: exact to fp32); below that, CUDA-core matrix-vector kernels.
+    const bool tc = B >= Q3_TC_MIN_BATCH && e->planes != nullptr;
+    const int tile = B <= 32 ? 32 : (B <= 64 ? 64 : 128);
+    const int prow = (B + tile - 1) / tile * tile;
+    bf16_raw* planes = reinterpret_cast<bf16_raw*>(e->planes);
     auto bf = [](const void* p) { return reinterpret_cast<const bf16_raw*>(p); };
 #define LAUNCH(call)                                                                                   \
     do {                                                                                               \
@@ -189,17 +207,29 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
         ++e->launches;                                                                                 \
         if (err__ != cudaSuccess) return fail(e, Q3_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(err__)); \
     } while (0)
+    // out[:, col0 : col0 + rows] (+)= planes @ wmat^T
+    auto gemm = [&](const bf16_raw* wmat, int rows, int K, float* out, int ldo, const float* resid, int ldr) -> cudaError_t {
+        GemmTcCall c{wmat, planes, out, resid, ldo, ldr, rows, B, K, tc_planes, prow, e->status};
+        return launch_gemm_tc(c, st);
+    };
 
     LAUNCH(launch_embed(reinterpret_cast<const long long*>(a->token), bf(w.embed), V, e->x, e->status, B, st));
     for (int l = 0; l < L; ++l) {
         GemvArgs g{};
         // qkv = rms(x, ln1) @ [wq; wk; wv]^T
-        g.seg[0] = {bf(w.wq) + (size_t)l * Q_DIM * HIDDEN, Q_DIM};
-        g.seg[1] = {bf(w.wk) + (size_t)l * KV_DIM * HIDDEN, KV_DIM};
-        g.seg[2] = {bf(w.wv) + (size_t)l * KV_DIM * HIDDEN, KV_DIM};
-        g.x = e->x; g.ldx = HIDDEN; g.gain = bf(w.ln1) + (size_t)l * HIDDEN;
-        g.out = e->qkv; g.ldo = QKV_DIM; g.n_rows = QKV_DIM; g.batch = B;
-        LAUNCH(launch_gemv(1024, EPI_STORE, g, QKV_DIM / 16, st));
+        if (tc) {
+            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln1) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st));
+            LAUNCH(gemm(bf(w.wq) + (size_t)l * Q_DIM * HIDDEN, Q_DIM, HIDDEN, e->qkv, QKV_DIM, nullptr, 0));
+            LAUNCH(gemm(bf(w.wk) + (size_t)l * KV_DIM * HIDDEN, KV_DIM, HIDDEN, e->qkv + Q_DIM, QKV_DIM, nullptr, 0));
+            LAUNCH(gemm(bf(w.wv) + (size_t)l * KV_DIM * HIDDEN, KV_DIM, HIDDEN, e->qkv + Q_DIM + KV_DIM, QKV_DIM, nullptr, 0));
+        } else {
+            g.seg[0] = {bf(w.wq) + (size_t)l * Q_DIM * HIDDEN, Q_DIM};
+            g.seg[1] = {bf(w.wk) + (size_t)l * KV_DIM * HIDDEN, KV_DIM};
+            g.seg[2] = {bf(w.wv) + (size_t)l * KV_DIM * HIDDEN, KV_DIM};
+            g.x = e->x; g.ldx = HIDDEN; g.gain = bf(w.ln1) + (size_t)l * HIDDEN;
+            g.out = e->qkv; g.ldo = QKV_DIM; g.n_rows = QKV_DIM; g.batch = B;
+            LAUNCH(launch_gemv(1024, EPI_STORE, g, QKV_DIM / 16, st));
+        }
 
         HeadPrepArgs h{};
         h.qkv = e->qkv; h.qn = bf(w.qn); h.kn = bf(w.kn); h.rope = e->rope; h.seq_len = a->seq_len;
@@ -215,37 +245,62 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
         LAUNCH(launch_attn(t, e->attn, B, st));
         ++e->launches;  // launch_attn is two kernels
 
-        // x += attn @ wo^T
-        g = GemvArgs{};
-        g.seg[0] = {bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN};
-        g.x = e->attn; g.ldx = Q_DIM; g.out = e->x; g.ldo = HIDDEN; g.resid = e->x; g.ldr = HIDDEN;
-        g.n_rows = HIDDEN; g.batch = B;
-        LAUNCH(launch_gemv(2048, EPI_RESID, g, HIDDEN / 16, st));
+        if (tc) {
+            // x += attn @ wo^T
+            LAUNCH(launch_act_split(e->attn, Q_DIM, Q_DIM, nullptr, planes, prow, tc_planes, B, st));
+            LAUNCH(gemm(bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN, Q_DIM, e->x, HIDDEN, e->x, HIDDEN));
+            // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
+            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st));
+            LAUNCH(gemm(bf(w.wg) + (size_t)l * INTER * HIDDEN, INTER, HIDDEN, e->gate, INTER, nullptr, 0));
+            LAUNCH(gemm(bf(w.wu) + (size_t)l * INTER * HIDDEN, INTER, HIDDEN, e->up, INTER, nullptr, 0));
+            LAUNCH(launch_silu_mul(e->gate, e->up, e->hid, (size_t)B * INTER, st));
+            // x += hid @ wd^T
+            LAUNCH(launch_act_split(e->hid, INTER, INTER, nullptr, planes, prow, tc_planes, B, st));
+            LAUNCH(gemm(bf(w.wd) + (size_t)l * HIDDEN * INTER, HIDDEN, INTER, e->x, HIDDEN, e->x, HIDDEN));
+        } else {
+            // x += attn @ wo^T
+            g = GemvArgs{};
+            g.seg[0] = {bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN};
+            g.x = e->attn; g.ldx = Q_DIM; g.out = e->x; g.ldo = HIDDEN; g.resid = e->x; g.ldr = HIDDEN;
+            g.n_rows = HIDDEN; g.batch = B;
+            LAUNCH(launch_gemv(2048, EPI_RESID, g, HIDDEN / 16, st));
 
-        // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
-        g = GemvArgs{};
-        g.seg[0] = {bf(w.wg) + (size_t)l * INTER * HIDDEN, INTER};
-        g.w2 = bf(w.wu) + (size_t)l * INTER * HIDDEN;
-        g.x = e->x; g.ldx = HIDDEN; g.gain = bf(w.ln2) + (size_t)l * HIDDEN;
-        g.out = e->hid; g.ldo = INTER; g.n_rows = INTER; g.batch = B;
-        LAUNCH(launch_gemv(1024, EPI_SILU, g, INTER / 8, st));
+            // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
+            g = GemvArgs{};
+            g.seg[0] = {bf(w.wg) + (size_t)l * INTER * HIDDEN, INTER};
+            g.w2 = bf(w.wu) + (size_t)l * INTER * HIDDEN;
+            g.x = e->x; g.ldx = HIDDEN; g.gain = bf(w.ln2) + (size_t)l * HIDDEN;
+            g.out = e->hid; g.ldo = INTER; g.n_rows = INTER; g.batch = B;
+            LAUNCH(launch_gemv(1024, EPI_SILU, g, INTER / 8, st));
 
-        // x += hid @ wd^T
-        g = GemvArgs{};
-        g.seg[0] = {bf(w.wd) + (size_t)l * HIDDEN * INTER, HIDDEN};
-        g.x = e->hid; g.ldx = INTER; g.out = e->x; g.ldo = HIDDEN; g.resid = e->x; g.ldr = HIDDEN;
-        g.n_rows = HIDDEN; g.batch = B;
-        LAUNCH(launch_gemv(3072, EPI_RESID, g, HIDDEN / 16, st));
+            // x += hid @ wd^T
+            g = GemvArgs{};
+            g.seg[0] = {bf(w.wd) + (size_t)l * HIDDEN * INTER, HIDDEN};
+            g.x = e->hid; g.ldx = INTER; g.out = e->x; g.ldo = HIDDEN; g.resid = e->x; g.ldr = HIDDEN;
+            g.n_rows = HIDDEN; g.batch = B;
+            LAUNCH(launch_gemv(3072, EPI_RESID, g, HIDDEN / 16, st));
+        }
     }
     // logits = rms(x, fnorm) @ embed^T ; next_token = argmax
-    GemvArgs g{};
-    g.seg[0] = {bf(w.embed), V};
-    g.x = e->x; g.ldx = HIDDEN; g.gain = bf(w.fnorm);
-    g.out = a->logits; g.ldo = V; g.n_rows = V; g.batch = B; g.pval = e->pval; g.pidx = e->pidx;
-    int lm_grid = (V + 15) / 16;
-    if (lm_grid > e->lm_grid) lm_grid = e->lm_grid;
-    LAUNCH(launch_gemv(1024, EPI_LOGITS, g, lm_grid, st));
-    LAUNCH(launch_argmax_final(e->pval, e->pidx, lm_grid, reinterpret_cast<long long*>(a->next_token), a->seq_len, append, B, st));
+    if (tc && !last_token_only && V % 128 == 0 && (a->logits != nullptr || e->logits_tc != nullptr)) {
+        float* logits = a->logits ? a->logits : e->logits_tc;
+        LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.fnorm), planes, prow, tc_planes, B, st));
+        LAUNCH(gemm(bf(w.embed), V, HIDDEN, logits, V, nullptr, 0));
+        LAUNCH(launch_argmax_rows(logits, V, reinterpret_cast<long long*>(a->next_token), a->seq_len, append, B, st));
+    } else {
+        // matrix-vector LM head: every sequence, or only the last token of a prompt
+        const int nb = last_token_only ? 1 : B;
+        if (nb > e->cfg.max_batch) return fail(e, Q3_ERR_INVALID, "decode: %d sequences exceed max_batch %d", nb, e->cfg.max_batch);
+        GemvArgs g{};
+        g.seg[0] = {bf(w.embed), V};
+        g.x = e->x + (last_token_only ? (size_t)(B - 1) * HIDDEN : 0); g.ldx = HIDDEN; g.gain = bf(w.fnorm);
+        g.out = a->logits; g.ldo = V; g.n_rows = V; g.batch = nb; g.pval = e->pval; g.pidx = e->pidx;
+        int lm_grid = (V + 15) / 16;
+        if (lm_grid > e->lm_grid) lm_grid = e->lm_grid;
+        LAUNCH(launch_gemv(1024, EPI_LOGITS, g, lm_grid, st));
+        LAUNCH(launch_argmax_final(e->pval, e->pidx, lm_grid, reinterpret_cast<long long*>(a->next_token), a->seq_len,
+                                   last_token_only ? 0 : append, nb, st));
+    }
 #undef LAUNCH
     return Q3_OK;
 }
@@ -273,31 +328,45 @@ extern "C" int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream) {
     return decode_layered(e, a, st);
 }
 
-// Prefill by sequential decode: position t attends the t rows already appended to the cache.
-// Exact causal attention with bf16-rounded cached rows; the tensor-core prefill replaces this loop
-// for long prompts but keeps the entry point.
-static int prefill_sequential(q3_engine* e, const q3_prefill_args* a, cudaStream_t st) {
-    struct Desc { uint64_t k, v; long long stride; int len; int pad; long long tok; } h;
-    h.k = reinterpret_cast<uint64_t>(a->kcache);
-    h.v = reinterpret_cast<uint64_t>(a->vcache);
-    h.stride = (long long)a->cache_capacity * KV_DIM;
-    h.len = 0; h.pad = 0; h.tok = 0;
-    CU(e, cudaMemcpyAsync(e->pf_desc, &h, sizeof(h), cudaMemcpyHostToDevice, st));
+// Prefill: the T prompt tokens run through the layered path as T one-token "sequences" of the same
+// cache, token t at position t.  head_prep writes every K/V row into the cache before the attention
+// kernels run, so token t attends rows [0, t) from the cache (rounded to bf16, as a later decode step
+// will see them) and its own row in fp32: causal attention, the numerics of token-by-token decode.
+// The projections are tensor-core GEMMs over two bf16 planes of the activations (relative error 2^-16).
+static int prefill_batched(q3_engine* e, const q3_prefill_args* a, cudaStream_t st) {
+    const int T = a->n_tokens;
     char* d = reinterpret_cast<char*>(e->pf_desc);
-    for (int t = 0; t < a->n_tokens; ++t) {
-        const bool last = (t == a->n_tokens - 1);
-        q3_decode_args s{};
-        s.batch = 1; s.max_len = t; s.flags = Q3_F_APPEND_KV | Q3_F_PATH_LAYERED;
-        s.token = a->ids + t;
-        s.seq_k = reinterpret_cast<const uint64_t*>(d);
-        s.seq_v = reinterpret_cast<const uint64_t*>(d + 8);
-        s.seq_layer_stride = reinterpret_cast<const int64_t*>(d + 16);
-        s.seq_len = reinterpret_cast<int32_t*>(d + 24);
-        s.logits = last ? a->last_logits : nullptr;
-        s.next_token = (last && a->next_token) ? a->next_token : reinterpret_cast<int64_t*>(d + 32);
-        int rc = decode_layered(e, &s, st);
-        if (rc != Q3_OK) return rc;
-    }
+    uint64_t* seq_k = reinterpret_cast<uint64_t*>(d + 64);
+    uint64_t* seq_v = seq_k + e->cap;
+    long long* stride = reinterpret_cast<long long*>(seq_v + e->cap);
+    int* len = reinterpret_cast<int*>(stride + e->cap);
+    cudaError_t err = launch_prefill_desc(seq_k, seq_v, stride, len, reinterpret_cast<uint64_t>(a->kcache), reinterpret_cast<uint64_t>(a->vcache),
+                                          (long long)a->cache_capacity * KV_DIM, T, st);
+    ++e->launches;
+    if (err != cudaSuccess) return fail(e, Q3_ERR_CUDA, "prefill descriptors: %s", cudaGetErrorString(err));
+    q3_decode_args s{};
+    s.batch = T; s.max_len = T - 1; s.flags = Q3_F_APPEND_KV | Q3_F_PATH_LAYERED;
+    s.token = a->ids;
+    s.seq_k = seq_k; s.seq_v = seq_v; s.seq_layer_stride = reinterpret_cast<const int64_t*>(stride); s.seq_len = len;
+    s.logits = a->last_logits;
+    s.next_token = a->next_token ? a->next_token : reinterpret_cast<int64_t*>(d + 32);
+    return decode_layered(e, &s, st, 2, true);
+}
+
+extern "C" int q3_linear_tc(const void* w, const float* x, float* out, const float* resid, int32_t n_rows, int32_t n_tok, int32_t K,
+                            int32_t nsplit, void* planes, int64_t planes_bytes, void* stream) {
+    if (!w || !x || !out || !planes) return fail(nullptr, Q3_ERR_INVALID, "q3_linear_tc: null argument");
+    if (n_rows < 128 || n_rows % 128 || K < 128 || K % 64 || n_tok < 1 || nsplit < 1 || nsplit > 3)
+        return fail(nullptr, Q3_ERR_INVALID, "q3_linear_tc: n_rows=%d (multiple of 128) n_tok=%d K=%d (multiple of 64) nsplit=%d (1..3)", n_rows, n_tok, K, nsplit);
+    const int tile = n_tok <= 32 ? 32 : (n_tok <= 64 ? 64 : 128);
+    const int plane_rows = (n_tok + tile - 1) / tile * tile;
+    const int64_t need = (int64_t)nsplit * plane_rows * K * 2;
+    if (planes_bytes < need) return fail(nullptr, Q3_ERR_INVALID, "q3_linear_tc: planes buffer holds %lld bytes, %lld needed", (long long)planes_bytes, (long long)need);
+    cudaStream_t st = (cudaStream_t)stream;
+    CU(nullptr, launch_act_split(x, K, K, nullptr, reinterpret_cast<bf16_raw*>(planes), plane_rows, nsplit, n_tok, st));
+    GemmTcCall c{w, planes, out, resid, n_rows, n_rows, n_rows, n_tok, K, nsplit, plane_rows, nullptr};
+    cudaError_t err = launch_gemm_tc(c, st);
+    if (err != cudaSuccess) return fail(nullptr, Q3_ERR_CUDA, "q3_linear_tc: %s", cudaGetErrorString(err));
     return Q3_OK;
 }
 
@@ -311,5 +380,5 @@ extern "C" int q3_prefill(q3_engine* e, const q3_prefill_args* a, void* stream) 
     if (a->n_tokens > e->rope_n) return fail(e, Q3_ERR_INVALID, "q3_prefill: RoPE table has %d rows, need %d", e->rope_n, a->n_tokens);
     if (!a->ids || !a->kcache || !a->vcache) return fail(e, Q3_ERR_INVALID, "q3_prefill: ids, kcache and vcache are required");
     CU(e, cudaSetDevice(e->device));
-    return prefill_sequential(e, a, (cudaStream_t)stream);
+    return prefill_batched(e, a, (cudaStream_t)stream);
 }

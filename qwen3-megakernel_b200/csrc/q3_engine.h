@@ -10,6 +10,7 @@
 #define Q3_STATUS_WORDS 8
 #define Q3_SYNC_WORDS 64
 #define Q3_MAX_SPLITS 64
+#define Q3_TC_MIN_BATCH 9   // from this many tokens on the projections run as tensor-core GEMMs
 
 struct q3_engine {
     int device;
@@ -31,7 +32,14 @@ struct q3_engine {
     int* pidx;      // [max_batch, lm_grid]
     uint32_t* status;
     uint32_t* sync;
-    void* pf_desc;  // 64 bytes: sequence descriptor + token slot used by q3_prefill
+    void* pf_desc;  // prefill: per-token sequence descriptors (4 arrays of `cap` entries) + a token slot
+    // tensor-core path (batches of Q3_TC_MIN_BATCH or more tokens, prefill)
+    int cap;            // tokens the scratch is sized for: max(max_batch, max_tokens)
+    int part_slots;     // (token, split) slots in `part`
+    void* planes;       // bf16 [3][cap rounded up to 128][3072] activation planes
+    float* gate;        // [cap, 3072]
+    float* up;          // [cap, 3072]
+    float* logits_tc;   // [max_batch, vocab] when the caller passes no logits buffer
     // persistent kernel geometry
     int p_grid, p_threads, p_smem;
     void* p_state;  // owned by q3_persist.cu
@@ -50,5 +58,5 @@ int persist_weights_changed(q3_engine* e);
 void persist_invalidate_weights(q3_engine* e);
 int engine_fail(q3_engine* e, int code, const char* fmt, ...);
 // the layered decode step on engine `e` (one launch per phase); `e` supplies weights, RoPE table and scratch
-int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st);
+int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes = 3, bool last_token_only = false);
 }  // namespace q3

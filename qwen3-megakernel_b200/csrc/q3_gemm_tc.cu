@@ -1,0 +1,255 @@
+// Tensor-core GEMM for prefill and large-batch decode: out[t, n] (+)= sum_k W[n, k] * X[t, k].
+//
+// Blackwell path: TMA (cp.async.bulk.tensor, 128-byte swizzle) stages W and X tiles in shared memory,
+// one elected thread issues tcgen05.mma (kind::f16, bf16 operands, fp32 accumulator in TMEM), four
+// warps read the accumulator back with tcgen05.ld and store it.  The weight matrix is the M operand
+// (128 weight rows per tile) and the tokens are the N operand, so a decode batch of 32..256 tokens is
+// one N tile and every weight byte crosses HBM once.
+//
+// Exact activations: the fp32 activations are passed as up to three bf16 planes (hi, mid, lo with
+// X = hi + mid + lo); each W tile is multiplied with every plane into the same accumulator.  With
+// three planes the result equals the fp32 product of the bf16 weights up to accumulation order;
+// large-batch decode uses that (the extra MMAs are free while the weights stream from HBM), prefill
+// uses one or two planes.
+//
+// Replaces the dense `xn @ w.T` products of the reference's PyTorch prefill (qwen3mk/prefill.py:61-80).
+#include <cuda.h>
+
+#include "q3_engine.h"
+#include "q3_gemm_tc.h"
+
+namespace q3 {
+
+constexpr int TC_THREADS = 192;    // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr int TC_BM = 128;         // weight rows per tile (UMMA M)
+constexpr int TC_BK = 64;          // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr unsigned long long TC_WAIT_NS = 200ull * 1000 * 1000;
+
+__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long tc_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+
+// bounded mbarrier wait; on timeout sets *abort_flag and returns false
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
+    unsigned it = 0;
+    unsigned long long t0 = 0;
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(tc_smem(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if ((++it & 63u) == 0) {
+            const unsigned long long t = tc_ns();
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > TC_WAIT_NS) {
+                report(status, ST_MBAR_TIMEOUT, site, parity);
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, 8-row
+// groups 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell)
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);        // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                              // leading byte offset (unused with swizzle), bits [16,30)
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset, bits [32,46)
+    d |= (uint64_t)1 << 46;                              // version
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return d;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                                const __grid_constant__ CUtensorMap tm_x, const GemmTcParams p) {
+    extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TC_BM;          // first weight row of this tile
+    const int n0 = blockIdx.y * BN;             // first token of this tile
+    const int nkb = p.K / TC_BK;
+    const int nsplit = p.nsplit;
+    const uint32_t a_bytes = TC_BM * TC_BK * 2, b_bytes = BN * TC_BK * 2;
+    const uint32_t stage_bytes = a_bytes + nsplit * b_bytes;
+    const int stages = p.stages;
+    // 1024-byte aligned base (the swizzle pattern repeats every 1024 bytes)
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&full_bar[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&empty_bar[s])) : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&acc_bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        abort_flag = 0;
+    }
+    if (warp == 1) {   // TMEM allocation: one warp, power-of-two column count >= 32
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&tmem_base_s)), "r"((uint32_t)(BN < 32 ? 32 : BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % stages;
+                if (kb >= stages && !tc_wait(&empty_bar[s], ((kb / stages) - 1) & 1, &abort_flag, p.status, 30)) break;
+                unsigned char* st = base + (size_t)s * stage_bytes;
+                asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full_bar[s])), "r"(stage_bytes) : "memory");
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(tc_smem(st)), "l"(&tm_w), "r"(kb * TC_BK), "r"(m0), "r"(tc_smem(&full_bar[s])) : "memory");
+                for (int sp = 0; sp < nsplit; ++sp)
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                 ::"r"(tc_smem(st + a_bytes + sp * b_bytes)), "l"(&tm_x), "r"(kb * TC_BK), "r"(sp * p.plane_rows + n0),
+                                   "r"(tc_smem(&full_bar[s])) : "memory");
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: D fp32, A and B bf16, both K-major, N = BN, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % stages;
+                ok = tc_wait(&full_bar[s], (kb / stages) & 1, &abort_flag, p.status, 31);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = tc_smem(base + (size_t)s * stage_bytes);
+                for (int sp = 0; sp < nsplit; ++sp) {
+                    const uint32_t sb = sa + a_bytes + sp * b_bytes;
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        const uint64_t da = tc_desc(sa + k * 32), db = tc_desc(sb + k * 32);
+                        const uint32_t accumulate = (kb | sp | k) ? 1u : 0u;
+                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                                     ::"r"(tmem_base), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+                    }
+                }
+                // the stage may be overwritten once these MMAs have read it
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&empty_bar[s])) : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&acc_bar)) : "memory");
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
+        const int quad = warp & 3;                      // TMEM lanes [32 quad, 32 quad + 32) belong to this warp
+        const bool ok = tc_wait(&acc_bar, 0, &abort_flag, p.status, 32);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const int row = m0 + quad * 32 + lane;      // weight row = output column
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                             : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < p.n_rows) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int t = n0 + c * 32 + j;
+                        if (t < p.n_tok) {
+                            float v = __uint_as_float(r[j]);
+                            float* dst = p.out + (size_t)t * p.ldo + row;
+                            if (p.epi == TC_EPI_RESID) v += p.resid[(size_t)t * p.ldr + row];
+                            *dst = v;
+                        }
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(BN < 32 ? 32 : BN)) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] row-major, box [box_rows, 64 columns], 128-byte swizzle
+static bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {TC_BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+static cudaError_t launch_bn(const CUtensorMap& tw, const CUtensorMap& tx, GemmTcParams p, int n_rows, int n_tok, cudaStream_t st) {
+    const uint32_t stage_bytes = TC_BM * TC_BK * 2 + p.nsplit * BN * TC_BK * 2;
+    int stages = (int)((200u * 1024u) / stage_bytes);
+    if (stages > 8) stages = 8;
+    if (stages > p.K / TC_BK) stages = p.K / TC_BK;
+    if (stages < 2) return cudaErrorInvalidValue;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    static size_t attr_set = 0;
+    if (smem > attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set = 224 * 1024;
+    }
+    dim3 grid((n_rows + TC_BM - 1) / TC_BM, (n_tok + BN - 1) / BN);
+    gemm_tc_kernel<BN><<<grid, TC_THREADS, smem, st>>>(tw, tx, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st) {
+    if (c.K % TC_BK || c.n_rows % TC_BM || c.nsplit < 1 || c.nsplit > 3 || c.n_tok < 1) return cudaErrorInvalidValue;
+    // token tile: the smallest of 32 / 64 / 128 that covers the batch, 128 for long prompts
+    const int bn = c.n_tok <= 32 ? 32 : (c.n_tok <= 64 ? 64 : 128);
+    if (c.plane_rows % bn) return cudaErrorInvalidValue;
+    CUtensorMap tw, tx;
+    if (!make_map(&tw, c.w, (uint64_t)c.n_rows, (uint64_t)c.K, TC_BM)) return cudaErrorUnknown;
+    if (!make_map(&tx, c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)bn)) return cudaErrorUnknown;
+    GemmTcParams p{};
+    p.out = c.out; p.resid = c.resid; p.ldo = c.ldo; p.ldr = c.ldr; p.n_rows = c.n_rows; p.n_tok = c.n_tok; p.K = c.K;
+    p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = c.resid ? TC_EPI_RESID : TC_EPI_STORE; p.status = c.status;
+    if (bn == 32) return launch_bn<32>(tw, tx, p, c.n_rows, c.n_tok, st);
+    if (bn == 64) return launch_bn<64>(tw, tx, p, c.n_rows, c.n_tok, st);
+    return launch_bn<128>(tw, tx, p, c.n_rows, c.n_tok, st);
+}
+
+}  // namespace q3

@@ -1,0 +1,38 @@
+// Tensor-core GEMM (tcgen05 + TMEM + TMA) used by prefill and large-batch decode.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace q3 {
+
+enum { TC_EPI_STORE = 0, TC_EPI_RESID = 1 };
+
+// device-side parameters
+struct GemmTcParams {
+    float* out;            // [n_tok, ldo] fp32; element (t, n) at out[t * ldo + n]
+    const float* resid;    // TC_EPI_RESID: out = resid + acc (may alias out)
+    int ldo, ldr;
+    int n_rows;            // weight rows (multiple of 128)
+    int n_tok;             // valid tokens
+    int K;                 // multiple of 64
+    int nsplit;            // activation planes (1..3)
+    int plane_rows;        // rows per plane in the activation tensor (multiple of the token tile)
+    int stages;
+    int epi;
+    uint32_t* status;
+};
+
+// host-side call
+struct GemmTcCall {
+    const void* w;         // bf16 [n_rows, K] row-major
+    const void* x_planes;  // bf16 [nsplit, plane_rows, K]: fp32 activations split as hi (+ mid (+ lo)); rows >= n_tok are zero
+    float* out;
+    const float* resid;    // nullptr: plain store
+    int ldo, ldr;
+    int n_rows, n_tok, K, nsplit, plane_rows;
+    uint32_t* status;
+};
+
+cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st);
+
+}  // namespace q3

@@ -386,6 +386,100 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
 }
 
 // ------------------------------------------------------------------------------------------------
+// act_split: fp32 activations [n_tok, K] (optionally RMS-normalised with a gain) -> bf16 planes
+// [nsplit, plane_rows, K] with x = hi (+ mid (+ lo)); the B operand of the tensor-core GEMM.
+// One block per row of the planes; rows >= n_tok (padding of the token tile) are written as zeros.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) act_split_kernel(const float* __restrict__ x, int ldx, int K, const bf16_raw* __restrict__ gain,
+                                                        bf16_raw* __restrict__ planes, int plane_rows, int nsplit, int n_tok) {
+    __shared__ float red[8];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    if (t >= n_tok) {   // padding rows of the token tile
+        for (int e = tid; e < K; e += 256)
+            for (int s = 0; s < nsplit; ++s) planes[((size_t)s * plane_rows + t) * K + e] = 0;
+        return;
+    }
+    const float* row = x + (size_t)t * ldx;
+    float r = 1.f;
+    if (gain != nullptr) {
+        float ss = 0.f;
+        for (int e = tid; e < K; e += 256) { const float v = row[e]; ss = fmaf(v, v, ss); }
+        ss = block_sum<8>(ss, red);
+        r = rsqrtf(ss / (float)K + EPS);
+    }
+    for (int e = tid; e < K; e += 256) {
+        float v = row[e];
+        if (gain != nullptr) v = (v * r) * bf_to_f(gain[e]);
+        const bf16_raw h = f_to_bf(v);
+        planes[(size_t)t * K + e] = h;
+        if (nsplit > 1) {
+            const float r1 = v - bf_to_f(h);
+            const bf16_raw m = f_to_bf(r1);
+            planes[((size_t)plane_rows + t) * K + e] = m;
+            if (nsplit > 2) planes[((size_t)2 * plane_rows + t) * K + e] = f_to_bf(r1 - bf_to_f(m));
+        }
+    }
+}
+
+// hid = silu(gate) * up, elementwise over [n_tok, n]
+__global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ h, size_t n) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) { const float a = g[i]; h[i] = (a / (1.f + expf(-a))) * u[i]; }
+}
+
+// argmax of every row of logits [n_tok, vocab]; ties -> lowest index; optional seq_len[t] += 1
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, int vocab, long long* __restrict__ next_token,
+                                                          int* seq_len, int append) {
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (size_t)t * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < vocab; i += 256) {
+        const float v = row[i];
+        if (v > bv) { bv = v; bi = i; }
+    }
+    sv[tid] = bv; si[tid] = bi;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (tid < o) {
+            const float v = sv[tid + o];
+            const int ix = si[tid + o];
+            if (v > sv[tid] || (v == sv[tid] && ix < si[tid])) { sv[tid] = v; si[tid] = ix; }
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        next_token[t] = si[0];
+        if (append) seq_len[t] += 1;
+    }
+}
+
+// prefill: token t of the prompt is treated as a one-token sequence at position t of the same cache
+__global__ void prefill_desc_kernel(uint64_t* seq_k, uint64_t* seq_v, long long* stride, int* len, uint64_t k, uint64_t v, long long s, int n) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) { seq_k[t] = k; seq_v[t] = v; stride[t] = s; len[t] = t; }
+}
+cudaError_t launch_prefill_desc(uint64_t* seq_k, uint64_t* seq_v, long long* stride, int* len, uint64_t k, uint64_t v, long long s, int n, cudaStream_t st) {
+    prefill_desc_kernel<<<(n + 255) / 256, 256, 0, st>>>(seq_k, seq_v, stride, len, k, v, s, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gain, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st) {
+    act_split_kernel<<<plane_rows, 256, 0, st>>>(x, ldx, K, gain, planes, plane_rows, nsplit, n_tok);
+    return cudaGetLastError();
+}
+cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, cudaStream_t st) {
+    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, h, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_argmax_rows(const float* logits, int vocab, long long* next_token, int* seq_len, int append, int n_tok, cudaStream_t st) {
+    argmax_rows_kernel<<<n_tok, 256, 0, st>>>(logits, vocab, next_token, seq_len, append);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
 // host-side launchers
 // ------------------------------------------------------------------------------------------------
 template <int K, int EPI>

@@ -95,8 +95,9 @@ def test_any_position(oracle, path, ctx):
 
 
 @pytest.mark.parametrize("path", ["layered", "auto"])
-@pytest.mark.parametrize("batch", [2, 5, 8])
+@pytest.mark.parametrize("batch", [2, 5, 8, 9, 33, 64])
 def test_ragged_batch(oracle, path, batch):
+    """Batches of 9 or more run their projections as tcgen05 GEMMs over three bf16 planes of the activations."""
     from qwen3mk.kernel import SeqTable
 
     shp = oracle.Shape(layers=2, vocab=2048)
