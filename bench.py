@@ -192,7 +192,7 @@ def main() -> int:
 
     import torch.distributed as dist
 
-    from qwen3mk import Megakernel
+    from qwen3mk import Megakernel, replicas
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -227,10 +227,7 @@ def main() -> int:
     mk.status()
     ms = e0.elapsed_time(e1)
     last_token = int(mk.chain_token)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
+    ms = replicas.max_over_ranks(ms, dev)          # the job is as slow as its slowest replica
     us_step = ms * 1e3 / K
 
     # ---- end to end from host memory: token H2D, step, token D2H, every step -------------------------
@@ -253,10 +250,7 @@ def main() -> int:
         torch.cuda.synchronize(dev)
         tok_host[0] = out_host[0]
     e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t[0])
+    e2e_s = replicas.max_over_ranks(e2e_s, dev)
     e2e_us = e2e_s / Ke * 1e6
 
     if rank != 0:
