@@ -189,7 +189,8 @@ static int splits_for(const q3_engine* e, int batch, int max_len) {
     return s;
 }
 
-int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes, bool last_token_only) {
+int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes, const PrefillCtx* prompt) {
+    const bool last_token_only = prompt != nullptr;
     const int B = a->batch, L = e->cfg.n_layers, V = e->cfg.vocab;
     const q3_weights& w = e->w;
     const int append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
@@ -242,8 +243,15 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         t.qkv = e->qkv; t.seq_k = a->seq_k; t.seq_v = a->seq_v;
         t.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
         t.seq_len = a->seq_len; t.part = e->part; t.layer = l; t.n_splits = ns;
-        LAUNCH(launch_attn(t, e->attn, B, st));
-        ++e->launches;  // launch_attn is two kernels
+        if (prompt != nullptr && B >= 64) {
+            // a prompt: tiled causal attention over the rows head_prep has just written into the cache
+            const bf16_raw* kc = bf(prompt->kcache) + (size_t)l * prompt->layer_stride;
+            const bf16_raw* vc = bf(prompt->vcache) + (size_t)l * prompt->layer_stride;
+            LAUNCH(launch_prefill_attn(e->qkv, kc, vc, e->attn, B, st));
+        } else {
+            LAUNCH(launch_attn(t, e->attn, B, st));
+            ++e->launches;  // launch_attn is two kernels
+        }
 
         if (tc) {
             // x += attn @ wo^T
@@ -350,7 +358,8 @@ static int prefill_batched(q3_engine* e, const q3_prefill_args* a, cudaStream_t 
     s.seq_k = seq_k; s.seq_v = seq_v; s.seq_layer_stride = reinterpret_cast<const int64_t*>(stride); s.seq_len = len;
     s.logits = a->last_logits;
     s.next_token = a->next_token ? a->next_token : reinterpret_cast<int64_t*>(d + 32);
-    return decode_layered(e, &s, st, 2, true);
+    const PrefillCtx ctx{a->kcache, a->vcache, (long long)a->cache_capacity * KV_DIM};
+    return decode_layered(e, &s, st, 2, &ctx);
 }
 
 extern "C" int q3_linear_tc(const void* w, const float* x, float* out, const float* resid, int32_t n_rows, int32_t n_tok, int32_t K,

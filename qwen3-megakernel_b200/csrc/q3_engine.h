@@ -58,5 +58,12 @@ int persist_weights_changed(q3_engine* e);
 void persist_invalidate_weights(q3_engine* e);
 int engine_fail(q3_engine* e, int code, const char* fmt, ...);
 // the layered decode step on engine `e` (one launch per phase); `e` supplies weights, RoPE table and scratch
-int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes = 3, bool last_token_only = false);
+// prompt-mode extras of the layered step: one sequence, tokens at positions 0..T-1 of this cache
+struct PrefillCtx {
+    const void* kcache;   // bf16 [L, capacity, 8, 128]
+    const void* vcache;
+    long long layer_stride;
+};
+int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes = 3, const PrefillCtx* prompt = nullptr);
+cudaError_t launch_prefill_attn(const float* qkv, const void* kcache_layer, const void* vcache_layer, float* attn, int T, cudaStream_t st);
 }  // namespace q3
