@@ -39,6 +39,7 @@ extern "C" {
 #define Q3_F_PATH_LAYERED 0x10u /* one launch per phase (debug ladder, large batches)                      */
 #define Q3_F_PATH_PERSIST 0x20u /* one persistent cooperative launch per step                              */
 #define Q3_F_PATH_MASK    0xf0u
+#define Q3_F_GRAPH        0x100u /* layered path: capture the step's launches into a CUDA graph and replay it on later calls with the same arguments */
 
 typedef struct q3_engine q3_engine; /* opaque */
 

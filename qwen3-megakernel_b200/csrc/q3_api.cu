@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "q3_engine.h"
 #include "q3_gemm_tc.h"
@@ -33,6 +34,32 @@ static int alloc(q3_engine* e, void** p, size_t bytes) {
     CU(e, cudaMalloc(p, bytes));
     CU(e, cudaMemset(*p, 0, bytes));
     return Q3_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// CUDA graphs for the layered step: a step is hundreds of small launches whose arguments all live in
+// device memory, so a call with the same argument block can replay a captured graph instead of
+// re-issuing them.  A key is seen uncaptured once (which also performs one-time function attribute
+// set-up), captured on its second use, and replayed afterwards.  Weights, RoPE table or trace changes
+// drop the cache.
+// ------------------------------------------------------------------------------------------------
+struct GraphEntry {
+    q3_decode_args key;
+    int n_splits;
+    int seen;
+    int64_t launches;      // kernels inside the graph
+    cudaGraphExec_t exec;
+};
+static std::vector<GraphEntry>* graph_cache(q3_engine* e) {
+    if (!e->graphs) e->graphs = new std::vector<GraphEntry>();
+    return static_cast<std::vector<GraphEntry>*>(e->graphs);
+}
+static void drop_graphs(q3_engine* e) {
+    if (!e->graphs) return;
+    auto* v = static_cast<std::vector<GraphEntry>*>(e->graphs);
+    for (auto& g : *v)
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+    v->clear();
 }
 
 extern "C" const char* q3_version(void) { return "q3mk-b200 0.1 sm_100a"; }
@@ -84,6 +111,15 @@ extern "C" int q3_create(int device, const q3_config* cfg, q3_engine** out) {
         q3_destroy(e);
         return rc;
     }
+    {
+        cudaStream_t cs = nullptr;
+        if (cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking) != cudaSuccess) {
+            fail(nullptr, Q3_ERR_CUDA, "q3_create: cudaStreamCreateWithFlags failed");
+            q3_destroy(e);
+            return Q3_ERR_CUDA;
+        }
+        e->capture_stream = cs;
+    }
     rc = persist_setup(e);
     if (rc != Q3_OK) {
         strncpy(g_create_error, e->err, sizeof(g_create_error) - 1);
@@ -97,6 +133,9 @@ extern "C" int q3_create(int device, const q3_config* cfg, q3_engine** out) {
 extern "C" void q3_destroy(q3_engine* e) {
     if (!e) return;
     cudaSetDevice(e->device);
+    drop_graphs(e);
+    delete static_cast<std::vector<GraphEntry>*>(e->graphs);
+    if (e->capture_stream) cudaStreamDestroy(static_cast<cudaStream_t>(e->capture_stream));
     persist_teardown(e);
     void* bufs[] = {e->x, e->qkv, e->attn, e->hid, e->part, e->pval, e->pidx, e->status, e->sync, e->pf_desc, e->planes, e->gate, e->up, e->logits_tc};
     for (void* p : bufs)
@@ -112,6 +151,7 @@ extern "C" int q3_set_weights(q3_engine* e, const q3_weights* w) {
         if (!p[i]) return fail(e, Q3_ERR_INVALID, "q3_set_weights: %s is null", names[i]);
         if (reinterpret_cast<uintptr_t>(p[i]) & 15) return fail(e, Q3_ERR_INVALID, "q3_set_weights: %s is not 16-byte aligned", names[i]);
     }
+    drop_graphs(e);
     e->w = *w;
     e->have_weights = 1;
     CU(e, cudaSetDevice(e->device));
@@ -126,6 +166,7 @@ extern "C" int q3_invalidate_weights(q3_engine* e) {
 
 extern "C" int q3_set_rope(q3_engine* e, const float* table, int32_t n_positions) {
     if (!e || !table || n_positions < 1) return fail(e, Q3_ERR_INVALID, "q3_set_rope: bad argument");
+    drop_graphs(e);
     e->rope = table;
     e->rope_n = n_positions;
     return Q3_OK;
@@ -333,7 +374,45 @@ extern "C" int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream) {
         return persist_decode(e, a, st);
     }
     if (path != Q3_F_PATH_LAYERED) return fail(e, Q3_ERR_INVALID, "q3_decode: unknown path flag 0x%x", path);
-    return decode_layered(e, a, st);
+    if (!(a->flags & Q3_F_GRAPH)) return decode_layered(e, a, st);
+
+    // graph replay: the key is the argument block with max_len replaced by what it determines (the split count)
+    q3_decode_args key = *a;
+    key.max_len = 0;
+    key.reserved = 0;
+    const int ns = splits_for(e, a->batch, a->max_len);
+    auto* cache = graph_cache(e);
+    GraphEntry* hit = nullptr;
+    for (auto& g : *cache)
+        if (g.n_splits == ns && !memcmp(&g.key, &key, sizeof(key))) { hit = &g; break; }
+    if (!hit) {
+        if (cache->size() >= 64) drop_graphs(e);
+        cache->push_back(GraphEntry{key, ns, 0, 0, nullptr});
+        hit = &cache->back();
+    }
+    if (hit->exec) {
+        CU(e, cudaGraphLaunch(hit->exec, st));
+        e->launches += hit->launches;
+        return Q3_OK;
+    }
+    if (hit->seen++ == 0) return decode_layered(e, a, st);   // first use: plain launches
+    const int64_t before = e->launches;
+    // capture on the engine's own stream (the legacy default stream cannot be captured); nothing runs during capture
+    cudaStream_t cs = static_cast<cudaStream_t>(e->capture_stream);
+    CU(e, cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
+    const int rc = decode_layered(e, a, cs);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t end = cudaStreamEndCapture(cs, &graph);
+    if (rc != Q3_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (end != cudaSuccess || !graph) return fail(e, Q3_ERR_CUDA, "q3_decode: stream capture failed: %s", cudaGetErrorString(end));
+    hit->launches = e->launches - before;
+    e->launches = before;
+    const cudaError_t inst = cudaGraphInstantiate(&hit->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (inst != cudaSuccess) { hit->exec = nullptr; return fail(e, Q3_ERR_CUDA, "q3_decode: cudaGraphInstantiate: %s", cudaGetErrorString(inst)); }
+    CU(e, cudaGraphLaunch(hit->exec, st));
+    e->launches += hit->launches;
+    return Q3_OK;
 }
 
 // Prefill: the T prompt tokens run through the layered path as T one-token "sequences" of the same

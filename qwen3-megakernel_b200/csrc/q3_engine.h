@@ -44,6 +44,8 @@ struct q3_engine {
     int p_grid, p_threads, p_smem;
     void* p_state;  // owned by q3_persist.cu
     int64_t launches;
+    void* graphs;       // cache of captured layered steps (owned by q3_api.cu)
+    void* capture_stream;  // cudaStream_t the steps are captured on
     unsigned long long* trace;  // caller-owned device buffer for phase time stamps, or nullptr
     int64_t trace_words;
     char err[512];

@@ -15,6 +15,8 @@
 // Replaces the dense `xn @ w.T` products of the reference's PyTorch prefill (qwen3mk/prefill.py:61-80).
 #include <cuda.h>
 
+#include <vector>
+
 #include "q3_engine.h"
 #include "q3_gemm_tc.h"
 
@@ -73,7 +75,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * TC_BM;          // first weight row of this tile
     const int n0 = blockIdx.y * BN;             // first token of this tile
-    const int nkb = p.K / TC_BK;
+    // split-K: grid.z slices of the k blocks; partial tiles are added into `out` with fp32 atomics
+    const int kb_begin = blockIdx.z * p.kb_per_split;
+    const int nkb = min(p.K / TC_BK - kb_begin, p.kb_per_split);
     const int nsplit = p.nsplit;
     const uint32_t a_bytes = TC_BM * TC_BK * 2, b_bytes = BN * TC_BK * 2;
     const uint32_t stage_bytes = a_bytes + nsplit * b_bytes;
@@ -108,10 +112,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                 unsigned char* st = base + (size_t)s * stage_bytes;
                 asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full_bar[s])), "r"(stage_bytes) : "memory");
                 asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(tc_smem(st)), "l"(&tm_w), "r"(kb * TC_BK), "r"(m0), "r"(tc_smem(&full_bar[s])) : "memory");
+                             ::"r"(tc_smem(st)), "l"(&tm_w), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full_bar[s])) : "memory");
                 for (int sp = 0; sp < nsplit; ++sp)
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                                 ::"r"(tc_smem(st + a_bytes + sp * b_bytes)), "l"(&tm_x), "r"(kb * TC_BK), "r"(sp * p.plane_rows + n0),
+                                 ::"r"(tc_smem(st + a_bytes + sp * b_bytes)), "l"(&tm_x), "r"((kb_begin + kb) * TC_BK), "r"(sp * p.plane_rows + n0),
                                    "r"(tc_smem(&full_bar[s])) : "memory");
             }
         }
@@ -170,8 +174,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                         if (t < p.n_tok) {
                             float v = __uint_as_float(r[j]);
                             float* dst = p.out + (size_t)t * p.ldo + row;
-                            if (p.epi == TC_EPI_RESID) v += p.resid[(size_t)t * p.ldr + row];
-                            *dst = v;
+                            if (p.epi == TC_EPI_ATOMIC) {
+                                atomicAdd(dst, v);   // split-K: `out` already holds zero or the residual
+                            } else {
+                                if (p.epi == TC_EPI_RESID) v += p.resid[(size_t)t * p.ldr + row];
+                                *dst = v;
+                            }
                         }
                     }
                 }
@@ -217,23 +225,58 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t co
 }
 
 template <int BN>
-static cudaError_t launch_bn(const CUtensorMap& tw, const CUtensorMap& tx, GemmTcParams p, int n_rows, int n_tok, cudaStream_t st) {
+static cudaError_t launch_bn(const CUtensorMap& tw, const CUtensorMap& tx, GemmTcParams p, int n_rows, int n_tok, int sm_count, cudaStream_t st) {
+    const int nkb = p.K / TC_BK;
+    const int tiles = ((n_rows + TC_BM - 1) / TC_BM) * ((n_tok + BN - 1) / BN);
+    // Few output tiles (decode batches, short prompts) cannot fill the GPU: slice K so that about one
+    // CTA per SM streams weights, at least four k blocks per slice to keep the pipeline busy.
+    int ksplit = 1;
+    if (tiles < sm_count && (p.epi == TC_EPI_STORE || p.resid == p.out)) {
+        ksplit = sm_count / tiles;
+        if (ksplit > nkb / 4) ksplit = nkb / 4;
+        if (ksplit < 1) ksplit = 1;
+    }
+    p.kb_per_split = (nkb + ksplit - 1) / ksplit;
+    ksplit = (nkb + p.kb_per_split - 1) / p.kb_per_split;
+    if (ksplit > 1) {
+        if (p.epi == TC_EPI_STORE) {   // partial sums are added onto zeros
+            cudaError_t e = cudaMemset2DAsync(p.out, (size_t)p.ldo * 4, 0, (size_t)n_rows * 4, (size_t)n_tok, st);
+            if (e != cudaSuccess) return e;
+        }
+        p.epi = TC_EPI_ATOMIC;         // in place on the residual otherwise
+    }
     const uint32_t stage_bytes = TC_BM * TC_BK * 2 + p.nsplit * BN * TC_BK * 2;
     int stages = (int)((200u * 1024u) / stage_bytes);
     if (stages > 8) stages = 8;
-    if (stages > p.K / TC_BK) stages = p.K / TC_BK;
-    if (stages < 2) return cudaErrorInvalidValue;
+    if (stages > p.kb_per_split) stages = p.kb_per_split;
+    if (stages < 1) return cudaErrorInvalidValue;
     p.stages = stages;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
-    static size_t attr_set = 0;
-    if (smem > attr_set) {
+    static bool attr_set = false;
+    if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         if (e != cudaSuccess) return e;
-        attr_set = 224 * 1024;
+        attr_set = true;
     }
-    dim3 grid((n_rows + TC_BM - 1) / TC_BM, (n_tok + BN - 1) / BN);
+    dim3 grid((n_rows + TC_BM - 1) / TC_BM, (n_tok + BN - 1) / BN, ksplit);
     gemm_tc_kernel<BN><<<grid, TC_THREADS, smem, st>>>(tw, tx, p);
     return cudaGetLastError();
+}
+
+// Encoding a tensor map costs a few microseconds of host time; a step issues hundreds of GEMMs over the
+// same few hundred (pointer, shape) pairs, so the maps are cached.
+struct MapKey { const void* p; uint64_t rows, cols; uint32_t box; };
+struct MapEntry { MapKey k; CUtensorMap m; };
+static std::vector<MapEntry>& map_cache() { static std::vector<MapEntry> c; return c; }
+static const CUtensorMap* cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    auto& c = map_cache();
+    for (auto& e : c)
+        if (e.k.p == ptr && e.k.rows == rows && e.k.cols == cols && e.k.box == box_rows) return &e.m;
+    if (c.size() > 4096) c.clear();
+    MapEntry e{{ptr, rows, cols, box_rows}, {}};
+    if (!make_map(&e.m, ptr, rows, cols, box_rows)) return nullptr;
+    c.push_back(e);
+    return &c.back().m;
 }
 
 cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st) {
@@ -241,15 +284,20 @@ cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st) {
     // token tile: the smallest of 32 / 64 / 128 that covers the batch, 128 for long prompts
     const int bn = c.n_tok <= 32 ? 32 : (c.n_tok <= 64 ? 64 : 128);
     if (c.plane_rows % bn) return cudaErrorInvalidValue;
-    CUtensorMap tw, tx;
-    if (!make_map(&tw, c.w, (uint64_t)c.n_rows, (uint64_t)c.K, TC_BM)) return cudaErrorUnknown;
-    if (!make_map(&tx, c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)bn)) return cudaErrorUnknown;
+    const CUtensorMap* pw = cached_map(c.w, (uint64_t)c.n_rows, (uint64_t)c.K, TC_BM);
+    if (!pw) return cudaErrorUnknown;
+    const CUtensorMap tw = *pw;   // copy: the cache may grow while the second map is looked up
+    const CUtensorMap* px = cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)bn);
+    if (!px) return cudaErrorUnknown;
+    const CUtensorMap tx = *px;
     GemmTcParams p{};
     p.out = c.out; p.resid = c.resid; p.ldo = c.ldo; p.ldr = c.ldr; p.n_rows = c.n_rows; p.n_tok = c.n_tok; p.K = c.K;
     p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = c.resid ? TC_EPI_RESID : TC_EPI_STORE; p.status = c.status;
-    if (bn == 32) return launch_bn<32>(tw, tx, p, c.n_rows, c.n_tok, st);
-    if (bn == 64) return launch_bn<64>(tw, tx, p, c.n_rows, c.n_tok, st);
-    return launch_bn<128>(tw, tx, p, c.n_rows, c.n_tok, st);
+    static int sm_count = 0;
+    if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+    if (bn == 32) return launch_bn<32>(tw, tx, p, c.n_rows, c.n_tok, sm_count, st);
+    if (bn == 64) return launch_bn<64>(tw, tx, p, c.n_rows, c.n_tok, sm_count, st);
+    return launch_bn<128>(tw, tx, p, c.n_rows, c.n_tok, sm_count, st);
 }
 
 }  // namespace q3

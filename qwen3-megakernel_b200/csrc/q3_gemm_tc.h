@@ -5,7 +5,7 @@
 
 namespace q3 {
 
-enum { TC_EPI_STORE = 0, TC_EPI_RESID = 1 };
+enum { TC_EPI_STORE = 0, TC_EPI_RESID = 1, TC_EPI_ATOMIC = 2 };
 
 // device-side parameters
 struct GemmTcParams {
@@ -18,6 +18,7 @@ struct GemmTcParams {
     int nsplit;            // activation planes (1..3)
     int plane_rows;        // rows per plane in the activation tensor (multiple of the token tile)
     int stages;
+    int kb_per_split;      // k blocks (of 64) each grid.z slice covers
     int epi;
     uint32_t* status;
 };

@@ -316,7 +316,8 @@ class Megakernel:
         self._bound = (weights, seqs)
         self._out = self._alloc(B)
         logits, next_token, k_write, v_write = self._out
-        flags = self._path_flag | (_cabi.F_APPEND_KV if append else 0)
+        # bound launches repeat the same argument block: let the layered path replay a CUDA graph
+        flags = self._path_flag | (_cabi.F_APPEND_KV if append else 0) | _cabi.F_GRAPH
         self._args = _cabi.DecodeArgs(B, seqs.max_len, flags, 0, tokens.data_ptr(), seqs.seq_k.data_ptr(),
                                       seqs.seq_v.data_ptr(), seqs.stride.data_ptr(), seqs.len.data_ptr(),
                                       logits.data_ptr() if want_logits else None, next_token.data_ptr(),
