@@ -49,7 +49,10 @@ constexpr int WOROW = 136;                    // the same for the 128-column Wo 
 constexpr int ATT_WARPS = 8;                  // split attention: warps that attend positions (32 positions per pass)
 constexpr int LOCAL_PASSES = 6;               // local attention: passes of 64 positions a CTA runs on its own
 constexpr int LOCAL_ATTN_MAX = 64 * LOCAL_PASSES - 1;   // up to this many cached positions every CTA attends its whole head
-constexpr int N_ACC = 2;                      // accumulators for the FFN delta (halves same-address atomics)
+#ifndef Q3_N_ACC
+#define Q3_N_ACC 2
+#endif
+constexpr int N_ACC = Q3_N_ACC;               // accumulators for the FFN delta (fewer same-address atomics each)
 constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
 constexpr int PART_STRIDE = 132;              // floats per published partial: [0] max, [1] sum, [4..132) output
 constexpr int DEFAULT_PACE = 100;             // nanoseconds the producer sleeps after each bulk copy
@@ -373,7 +376,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 
     const int n_ev = 4 + EV_PER_LAYER * L;
 #ifdef Q3_FINE
-#define Q3_FINE_T(k) do { if (p.trace != nullptr && tid == 0) p.trace[(size_t)G * n_ev + ((size_t)c * L + l) * 16 + (k)] = clock64(); } while (0)
+#define Q3_FINE_T(k) do { if (p.trace != nullptr && tid == 0) p.trace[(size_t)G * n_ev + ((size_t)c * L + l) * 32 + (k)] = clock64(); } while (0)
 #else
 #define Q3_FINE_T(k) do {} while (0)
 #endif
@@ -385,6 +388,43 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();   // the only barrier the producer warps join
+
+    // LM head rows of this CTA, four rows in flight per warp; every warp of the CTA (producers included)
+    // takes part once the layer loop is over.  Keeps the warp's best (value, row); ties -> lowest row.
+    auto lm_stream = [&](int wi, int nw, float& bestv, int& besti) {
+        const int V = p.vocab;
+        const int v0 = (int)((long long)c * V / G), v1 = (int)((long long)(c + 1) * V / G);
+        for (int base = v0 + wi * 4; base < v1; base += nw * 4) {
+            uint4 w[4][4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int row = min(base + k, v1 - 1);
+                const uint4* rp = reinterpret_cast<const uint4*>(p.embed + (size_t)row * HIDDEN);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[k][j] = ld_stream(rp + j * 32 + lane);
+            }
+            float acc[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[k] = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[k] += dot8(w[k][j], xs, j, lane);
+                acc[k] = warp_sum(acc[k]);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int row = base + k;
+                    if (row < v1) {
+                        if (p.logits) p.logits[row] = acc[k];
+                        if (acc[k] > bestv) { bestv = acc[k]; besti = row; }
+                    }
+                }
+            }
+        }
+    };
+    float* const lm_bv = q_s;                               // [CW + NPW] per-warp best values
+    int* const lm_bi = reinterpret_cast<int*>(k_s);         // [CW + NPW] and their rows
 
     // ================================================================================ producer warps
     // Weights reach shared memory through cp.async (16-byte LDGSTS copies on the load/store path),
@@ -423,6 +463,13 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // the weights are in: help with the LM head
+        asm volatile("bar.sync 2, %0;" ::"n"(PT) : "memory");    // the consumers have staged the final activations
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        lm_stream(warp, CW + NPW, bv, bi);
+        if (lane == 0) { lm_bv[warp] = bv; lm_bi[warp] = bi; }
+        asm volatile("bar.sync 3, %0;" ::"n"(PT) : "memory");
         return;
     }
 
@@ -437,8 +484,17 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     const bf16_raw* vcache = reinterpret_cast<const bf16_raw*>(p.seq_v[0]);
     const long long lstride = p.seq_layer_stride[0];
     const float* rope_row = p.rope + (size_t)len * HEAD_DIM;
-    float* dB0 = p.dB;
-    float* dB1 = p.dB + HIDDEN;
+    // x = X0 + sum of the FFN delta accumulators, two elements per thread
+    auto load_x_ffn = [&](float& x0, float& x1) {
+        float2 a = ldcg2(p.X0 + 2 * tid);
+        float2 d[N_ACC];
+#pragma unroll
+        for (int i = 0; i < N_ACC; ++i) d[i] = ldcg2(p.dB + (size_t)i * HIDDEN + 2 * tid);
+        float s0 = d[0].x, s1 = d[0].y;
+#pragma unroll
+        for (int i = 1; i < N_ACC; ++i) { s0 += d[i].x; s1 += d[i].y; }
+        x0 = a.x + s0; x1 = a.y + s1;
+    };
     float* dBmine = p.dB + (size_t)(c & (N_ACC - 1)) * HIDDEN;
 
     unsigned* bar = p.sync;
@@ -471,8 +527,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 const uint32_t e = *reinterpret_cast<const uint32_t*>(p.embed + (size_t)tok * HIDDEN + 2 * tid);
                 x0 = bf_lo(e); x1 = bf_hi(e);
             } else {
-                const float2 a = ldcg2(p.X0 + 2 * tid), d0 = ldcg2(dB0 + 2 * tid), d1 = ldcg2(dB1 + 2 * tid);
-                x0 = a.x + (d0.x + d1.x); x1 = a.y + (d0.y + d1.y);
+                load_x_ffn(x0, x1);
             }
             if (c == 0) __stcg(reinterpret_cast<float2*>(p.X1 + 2 * tid), make_float2(x0, x1));
             if (c == 1) __stcg(reinterpret_cast<float2*>(p.dA + 2 * tid), make_float2(0.f, 0.f));
@@ -627,6 +682,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 float qa[16];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) { qa[i] = q_s[fhh * 128 + sub * 8 + i]; qa[8 + i] = q_s[fhh * 128 + 64 + sub * 8 + i]; }
+                Q3_FINE_T(16);
                 float sreg[LOCAL_PASSES];
                 float tmax = -INFINITY;
 #pragma unroll
@@ -655,33 +711,40 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     if (lane == 0) misc[0] = sn_;
                     tmax = fmaxf(tmax, sn_);
                 }
+                Q3_FINE_T(17);
                 tmax = warp_max(tmax);
                 if (lane == 0) red[warp] = tmax;
                 cta_sync();
+                Q3_FINE_T(18);
                 float M = (lane < CW) ? red[lane] : -INFINITY;
                 M = warp_max(M);
+                Q3_FINE_T(19);
 
                 float lsum = 0.f, acc[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+                Q3_FINE_T(20);
                 switch (npl & 3) {   // V pass 0 sits in ring buffer npl & 3
                     case 0: local_pv<0>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
                     case 1: local_pv<1>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
                     case 2: local_pv<2>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
                     default: local_pv<3>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
                 }
+                Q3_FINE_T(21);
 #pragma unroll
                 for (int off = 8; off <= 16; off <<= 1) {
                     lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
 #pragma unroll
                     for (int i = 0; i < 16; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
                 }
+                Q3_FINE_T(22);
                 if (quarter == 0) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) { om[warp * 128 + sub * 8 + i] = acc[i]; om[warp * 128 + 64 + sub * 8 + i] = acc[8 + i]; }
                     if (sub == 0) lw[warp] = lsum;
                 }
                 cta_sync();
+                Q3_FINE_T(23);
                 Q3_TRACE(ev + 4);
                 Q3_TRACE(ev + 5);
                 if (tid < HEAD_DIM) {
@@ -696,6 +759,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     reinterpret_cast<bf16_raw*>(osp + 128)[tid] = lo_;
                 }
                 cta_sync();
+                Q3_FINE_T(24);
             } else {
             // ---- scores of this CTA's cached positions, both heads: a quarter-warp per position ----
                 float tmax0 = -INFINITY, tmax1 = -INFINITY;
@@ -831,6 +895,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 
             // ---- Wo slice on the tensor cores: warp (rt, kh) = 16 rows x 64 head dims ----
             slot_wait(&full[1], l & 1, abort_flag, p.status, 11);
+            Q3_FINE_T(25);
             {
                 const int rt = warp >> 1, kh = warp & 1;
                 float cc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -849,6 +914,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 if ((lane & 3) == 0) { wo_part[kh * 128 + 16 * rt + fr_n] = r0; wo_part[kh * 128 + 16 * rt + fr_n + 8] = r1; }
             }
             cta_sync();
+            Q3_FINE_T(26);
             if (tid < fn) out_s[tid] = wo_part[tid] + wo_part[128 + tid];
             cta_sync();
             if (tid < fn / 4) red_add_v4(p.dA + fr0 + 4 * tid, out_s[4 * tid], out_s[4 * tid + 1], out_s[4 * tid + 2], out_s[4 * tid + 3]);
@@ -998,8 +1064,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 
     // ======================================================================== LM head + argmax
     {
-        const float2 a = ldcg2(p.X0 + 2 * tid), d0 = ldcg2(dB0 + 2 * tid), d1 = ldcg2(dB1 + 2 * tid);
-        const float x0 = a.x + (d0.x + d1.x), x1 = a.y + (d0.y + d1.y);
+        float x0, x1;
+        load_x_ffn(x0, x1);
         const float ss = warp_sum(x0 * x0 + x1 * x1);
         if (lane == 0) red[warp] = ss;
         cta_sync();
@@ -1010,49 +1076,21 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         xs[act_slot(2 * tid + 1)] = (x1 * r) * bf_hi(gain2);
         cta_sync();
 
-        const int V = p.vocab;
-        const int v0 = (int)((long long)c * V / G), v1 = (int)((long long)(c + 1) * V / G);
+        asm volatile("bar.sync 2, %0;" ::"n"(PT) : "memory");    // activations staged: the producer warps join
         float bestv = -INFINITY;
         int besti = 0x7fffffff;
-        for (int base = v0 + warp * 4; base < v1; base += CW * 4) {
-            uint4 w[4][4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int row = min(base + k, v1 - 1);
-                const uint4* rp = reinterpret_cast<const uint4*>(p.embed + (size_t)row * HIDDEN);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) w[k][j] = ld_stream(rp + j * 32 + lane);
-            }
-            float acc[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                acc[k] = 0.f;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[k] += dot8(w[k][j], xs, j, lane);
-                acc[k] = warp_sum(acc[k]);
-            }
-            if (lane == 0) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int row = base + k;
-                    if (row < v1) {
-                        if (p.logits) p.logits[row] = acc[k];
-                        if (acc[k] > bestv) { bestv = acc[k]; besti = row; }
-                    }
-                }
-            }
-        }
+        lm_stream(warp, CW + NPW, bestv, besti);
         Q3_TRACE(1 + EV_PER_LAYER * L);
         // CTA argmax (ties -> lowest index), then the last CTA to finish reduces over CTAs
-        float* bv_s = q_s;                       // reuse: [16] values, [16] indices
-        int* bi_s = reinterpret_cast<int*>(k_s);
+        float* bv_s = lm_bv;
+        int* bi_s = lm_bi;
         if (lane == 0) { bv_s[warp] = bestv; bi_s[warp] = besti; }
-        cta_sync();
+        asm volatile("bar.sync 3, %0;" ::"n"(PT) : "memory");    // all 18 partials written
         int* last_flag = reinterpret_cast<int*>(v_s);
         if (tid == 0) {
             float bv = bv_s[0];
             int bi = bi_s[0];
-            for (int w = 1; w < CW; ++w)
+            for (int w = 1; w < CW + NPW; ++w)
                 if (bv_s[w] > bv || (bv_s[w] == bv && bi_s[w] < bi)) { bv = bv_s[w]; bi = bi_s[w]; }
             __stcg(p.pval + c, bv);
             __stcg(p.pidx + c, bi);
