@@ -52,6 +52,17 @@ constexpr int LOCAL_ATTN_MAX = 64 * LOCAL_PASSES - 1;   // up to this many cache
 #ifndef Q3_N_ACC
 #define Q3_N_ACC 2
 #endif
+#ifndef Q3_EXP
+#define Q3_EXP 0
+#endif
+#ifndef Q3_CP_GROUP
+#define Q3_CP_GROUP 16
+#endif
+#ifndef Q3_CP_DEPTH
+#define Q3_CP_DEPTH 8
+#endif
+constexpr int CP_GROUP = Q3_CP_GROUP;         // producer lanes: 16-byte copies per committed group
+constexpr int CP_DEPTH = Q3_CP_DEPTH;         // ... and groups in flight
 constexpr int N_ACC = Q3_N_ACC;               // accumulators for the FFN delta (fewer same-address atomics each)
 constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
 constexpr int PART_STRIDE = 132;              // floats per published partial: [0] max, [1] sum, [4..132) output
@@ -59,7 +70,7 @@ constexpr int DEFAULT_PACE = 100;             // nanoseconds the producer sleeps
 constexpr int COPY_BYTES = 16384;             // largest single bulk copy
 constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;   // patience of every device-side wait: 200 ms
 // fp32 tail of shared memory: 8 KB union | q_s[2][128] k_s v_s | o split [3][128] bf16 | hid split [3][32] bf16 | red lw misc | scores
-constexpr int FBUF_FLOATS = 2048 + 4 * 128 + 192 + 48 + 32 + 16 + 16 + 2 * SC_HALF;
+constexpr int FBUF_FLOATS = 2048 + 4 * 128 + 192 + 48 + 32 + 16 + 16 + 3 * SC_HALF;
 constexpr int TAIL_BYTES = FBUF_FLOATS * 4 + 8 * 8 + 16;
 
 struct PersistParams {
@@ -76,9 +87,10 @@ struct PersistParams {
     bf16_raw* v_write;
     float* X0;        // [1024] materialised residual read by Q
     float* X1;        // [1024] materialised residual read by GD
-    float* dA;        // [1024] attention delta
-    float* dB;        // [N_ACC][1024] FFN delta
-    float* qkv;       // [4096]
+    float* dA;        // [2][1024] attention delta of layer l in buffer l & 1
+    float* dB;        // [2][N_ACC][1024] FFN delta of layer l in buffer l & 1
+    unsigned long long* xq;   // [4096] q | k | v rows of the current layer, each a (tag << 32 | fp32 bits) word
+    const unsigned* epoch;    // launches completed on this state; gives every (launch, layer) its own tag
     float* part;      // [8 groups][18 CTAs][2 heads][PART_STRIDE] attention partials
     const float* rope;
     unsigned* sync;   // [0] grid barrier counter, [2] end-of-step ticket, [8..15] kv-group counters
@@ -92,12 +104,13 @@ struct PersistParams {
 struct PersistState {
     bf16_raw* packed;       // the layer matrices re-laid per CTA (see pack_weights_kernel)
     const void* src[7];     // the seven pointers `packed` was built from
-    float* X;               // X0 | X1 | dA | dB[N_ACC]
+    float* X;               // X0 | X1 | dA[2] | dB[2][N_ACC] | xq[4096] (64-bit words) | epoch
     int grid, smem;
 };
 
 // Which rows of which matrix CTA c of a grid of G owns, and how many elements its packed share of
 // one layer takes.  Used by the decode kernel and by the kernel that packs the weights.
+constexpr size_t X_FLOATS = (size_t)(4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM + 64;
 struct Share {
     int q0, nq, qmax;       // rows [q0, q0 + nq) of [wq; wk; wv], slot rows qmax
     int i0, ni, imax;       // FFN rows [i0, i0 + ni) of gate, up and down^T, slot rows imax
@@ -233,6 +246,13 @@ __device__ __forceinline__ void slot_wait(uint64_t* b, uint32_t parity, volatile
     __syncwarp();
 }
 
+// sum of the sixteen per-warp partial sums, read by one thread (four broadcast 16-byte loads)
+__device__ __forceinline__ float sum16(const float* red) {
+    const float4 a = *reinterpret_cast<const float4*>(red), b = *reinterpret_cast<const float4*>(red + 4);
+    const float4 c = *reinterpret_cast<const float4*>(red + 8), d = *reinterpret_cast<const float4*>(red + 12);
+    return ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w)) + (((c.x + c.y) + (c.z + c.w)) + ((d.x + d.y) + (d.z + d.w)));
+}
+
 __device__ __forceinline__ void unpack8f(const uint4& u, float* f) {
     f[0] = bf_lo(u.x); f[1] = bf_hi(u.x); f[2] = bf_lo(u.y); f[3] = bf_hi(u.y);
     f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
@@ -294,41 +314,27 @@ __device__ __forceinline__ void load_act_regs(const float* xs, int lane, float* 
     }
 }
 
-// Local attention streams its K rows and then its V rows through one ring of four register buffers:
-// item i (K pass i for i < npl, V pass i - npl after that) lives in buffer i & 3, and the load of
-// item i + 4 is issued the moment item i has been consumed, so a row has four passes to arrive.
-__device__ __forceinline__ void ring_load(uint4 (&buf)[2], int item, int npl, int len, int att_slot, int sub,
-                                          const bf16_raw* kl, const bf16_raw* vl) {
-    const bool is_v = item >= npl;
-    const int pass = is_v ? item - npl : item;
+// Local attention keeps its K rows in a ring of four register buffers (a quarter-warp per position,
+// 64 positions per pass): pass i lives in buffer i & 3 and the load of pass i + 4 is issued the moment
+// pass i has been consumed.  The V rows are read dim-major instead (one warp per position, four dims
+// per lane), so P.V needs no shuffles: the first eight positions of every warp are fetched before the
+// barrier wait, the rest inside the loop.
+__device__ __forceinline__ void ring_load(uint4 (&buf)[2], int pass, int npl, int len, int att_slot, int sub, const bf16_raw* kl) {
     const int pos = pass * 64 + att_slot;
     if (pass < npl && pos < len) {
-        const uint4* row = reinterpret_cast<const uint4*>((is_v ? vl : kl) + (size_t)pos * KV_DIM);
+        const uint4* row = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
         buf[0] = ld_stream(row + sub);
         buf[1] = ld_stream(row + 8 + sub);
     } else {
         buf[0] = buf[1] = make_uint4(0, 0, 0, 0);
     }
 }
-template <int OFF>
-__device__ __forceinline__ void local_pv(uint4 (&ring)[4][2], const float (&sreg)[LOCAL_PASSES], float M, int npl, int len,
-                                         int att_slot, int sub, const bf16_raw* kl, const bf16_raw* vl, float& lsum, float (&acc)[16]) {
-#pragma unroll
-    for (int ps = 0; ps < LOCAL_PASSES; ++ps) {
-        if (ps < npl) {
-            constexpr int dummy = 0; (void)dummy;
-            const int b = (OFF + ps) & 3;
-            const uint4 v0 = ring[b][0], v1 = ring[b][1];
-            if (ps + 4 < npl) ring_load(ring[b], npl + ps + 4, npl, len, att_slot, sub, kl, vl);
-            const float pr = __expf(sreg[ps] - M);   // exp(-inf) = 0 for the slots past the cache
-            lsum += pr;
-            float vf[16];
-            f_unpack16(v0, v1, vf);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = fmaf(pr, vf[i], acc[i]);
-        }
-    }
+__device__ __forceinline__ uint2 ld_stream8(const void* ptr) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr));
+    return v;
 }
+constexpr int LOCAL_V_PRE = 8;   // V positions per warp fetched ahead of the barrier wait
 
 // ====================================================================================================
 __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p) {
@@ -368,9 +374,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     float* red = reinterpret_cast<float*>(hsp + 48);          // [32]
     float* lw = red + 32;        // [16] per-warp probability sums, [w][head]
     float* misc = lw + 16;       // [16]: [0] score of the new row for this CTA's head
-    float* sc = misc + 16;       // [2][SC_HALF] scores of this CTA's positions
-    float* out_s = sc;           // [128] Wo slice results (the scores are dead by then)
-    uint64_t* full = reinterpret_cast<uint64_t*>(sc + 2 * SC_HALF);   // [4] slot filled
+    float* sc = misc + 16;       // split attention: [2][SC_HALF] scores of this CTA's positions; local: [3 * SC_HALF] scores of all positions
+    uint64_t* full = reinterpret_cast<uint64_t*>(sc + 3 * SC_HALF);   // [4] slot filled
     uint64_t* empty = full + 4;                                        // [4] slot released by the consumers
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + 4);
 
@@ -450,9 +455,9 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     const int pieces = bytes >> 4;
                     for (int i = pw * 32 + lane; i < pieces; i += NPW * 32) {
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 16), "l"(src + (size_t)i * 16) : "memory");
-                        if (++in_group == 16) {
+                        if (++in_group == CP_GROUP) {
                             asm volatile("cp.async.commit_group;" ::: "memory");
-                            asm volatile("cp.async.wait_group 7;" ::: "memory");
+                            asm volatile("cp.async.wait_group %0;" ::"n"(CP_DEPTH - 1) : "memory");
                             in_group = 0;
                         }
                     }
@@ -485,17 +490,18 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     const long long lstride = p.seq_layer_stride[0];
     const float* rope_row = p.rope + (size_t)len * HEAD_DIM;
     // x = X0 + sum of the FFN delta accumulators, two elements per thread
-    auto load_x_ffn = [&](float& x0, float& x1) {
+    auto load_x_ffn = [&](const float* dBl, float& x0, float& x1) {
         float2 a = ldcg2(p.X0 + 2 * tid);
         float2 d[N_ACC];
 #pragma unroll
-        for (int i = 0; i < N_ACC; ++i) d[i] = ldcg2(p.dB + (size_t)i * HIDDEN + 2 * tid);
+        for (int i = 0; i < N_ACC; ++i) d[i] = ldcg2(dBl + (size_t)i * HIDDEN + 2 * tid);
         float s0 = d[0].x, s1 = d[0].y;
 #pragma unroll
         for (int i = 1; i < N_ACC; ++i) { s0 += d[i].x; s1 += d[i].y; }
         x0 = a.x + s0; x1 = a.y + s1;
     };
-    float* dBmine = p.dB + (size_t)(c & (N_ACC - 1)) * HIDDEN;
+    // Every (launch, layer) tags its q/k/v words differently, so a reader can tell a fresh word from an old one.
+    const unsigned tag_base = __ldcg(p.epoch) * 32u;
 
     unsigned* bar = p.sync;
     unsigned* grp = p.sync + 8 + fg;
@@ -520,17 +526,25 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 
     for (int l = 0; l < L; ++l) {
         const int ev = 1 + EV_PER_LAYER * l;
+        // The two deltas alternate between two buffers: a buffer is cleared one phase after its last reader
+        // has passed a grid barrier and at least one grid barrier before its next writer starts.
+        float* dAl = p.dA + (size_t)(l & 1) * HIDDEN;
+        float* dBl = p.dB + (size_t)(l & 1) * N_ACC * HIDDEN;
+        const unsigned tag = tag_base + (unsigned)l + 1u;
         // ==================================================================== Q
         {
             float x0, x1;
+            Q3_FINE_T(27);
             if (l == 0) {
                 const uint32_t e = *reinterpret_cast<const uint32_t*>(p.embed + (size_t)tok * HIDDEN + 2 * tid);
                 x0 = bf_lo(e); x1 = bf_hi(e);
             } else {
-                load_x_ffn(x0, x1);
+                load_x_ffn(p.dB + (size_t)((l - 1) & 1) * N_ACC * HIDDEN, x0, x1);
             }
             if (c == 0) __stcg(reinterpret_cast<float2*>(p.X1 + 2 * tid), make_float2(x0, x1));
-            if (c == 1) __stcg(reinterpret_cast<float2*>(p.dA + 2 * tid), make_float2(0.f, 0.f));
+            if (c == 1 && l + 1 < L) __stcg(reinterpret_cast<float2*>(p.dA + (size_t)((l + 1) & 1) * HIDDEN + 2 * tid), make_float2(0.f, 0.f));
+            if (c == G - 1 && l == 0)
+                for (int i = tid; i < N_ACC * HIDDEN / 2; i += CT) __stcg(reinterpret_cast<float2*>(p.dB) + i, make_float2(0.f, 0.f));
             {   // stage x * gain split in three bf16 parts (the 1/rms factor is applied to the row sums)
                 bf16_raw h0, m0, l0, h1, m1, l1;
                 split3(x0 * bf_lo(gain2), h0, m0, l0);
@@ -539,14 +553,16 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 xsp[512 + tid] = (uint32_t)m0 | ((uint32_t)m1 << 16);
                 xsp[1024 + tid] = (uint32_t)l0 | ((uint32_t)l1 << 16);
             }
+            Q3_FINE_T(28);
             const float ss = warp_sum(x0 * x0 + x1 * x1);
             if (lane == 0) red[warp] = ss;
+            Q3_FINE_T(29);
             cta_sync();
             Q3_TRACE(ev + 0);
-            float tot = (lane < CW) ? red[lane] : 0.f;
-            tot = warp_sum(tot);
-            const float r = rsqrtf(tot / (float)HIDDEN + EPS);
             Q3_FINE_T(0);
+#if Q3_EXP == 2 || Q3_EXP == 3
+            const float r = rsqrtf(sum16(red) / (float)HIDDEN + EPS);
+#endif
             // warp w: k range [64 w, 64 w + 64) of both 16-row tiles of this CTA's rows
             uint32_t bq[4][2];
 #pragma unroll
@@ -587,30 +603,48 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 }
             }
             cta_sync();
-            if (tid < nq) {
-                float v = 0.f;
+            if (warp == 0) {   // nq <= 28: the row sums, the 1/rms factor and the arrival all sit in warp 0
+                if (tid < nq) {
+#if !(Q3_EXP == 2 || Q3_EXP == 3)
+                    const float r = rsqrtf(sum16(red) / (float)HIDDEN + EPS);
+#endif
+                    float v0 = 0.f, v1 = 0.f;
 #pragma unroll
-                for (int w = 0; w < CW; ++w) v += part[w * 32 + tid];
-                __stcg(p.qkv + q0 + tid, v * r);
+                    for (int w = 0; w < CW; w += 2) { v0 += part[w * 32 + tid]; v1 += part[w * 32 + 32 + tid]; }
+                    // value and tag travel in one 64-bit word: no barrier between Q and F, the readers poll the tags
+                    const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint((v0 + v1) * r);
+#if Q3_EXP == 1 || Q3_EXP == 3
+                    __stcg(p.xq + q0 + tid, word);
+#else
+                    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p.xq + q0 + tid), "l"(word) : "memory");
+#endif
+                }
+                Q3_FINE_T(3);
+                Q3_FINE_T(4);
+                Q3_TRACE(ev + 1);
             }
-            Q3_FINE_T(3);
-            cta_sync();
-            Q3_FINE_T(4);
-            Q3_TRACE(ev + 1);
-            if (tid == 0) counter_arrive(bar);
             if (tid == 32) mbar_arrive(&empty[0]);
         }
-        target += G;
 
         // ---- between arrive and wait: what the F phase needs that no other CTA produces ----
-        uint4 ring[4][2];   // local attention: the K/V ring; split attention: [0], [1] = K passes, [2], [3] = V passes
+        // fetched ahead of the barrier wait.  Split attention: [0], [1] = K passes, [2], [3] = V passes of the
+        // CTA's positions.  Local attention: [0], [1] = K passes 0, 1 (a quarter-warp per position) and
+        // [2], [3] = V[warp + 16 i][4 lane .. 4 lane + 3] for i < 8, two positions per uint4.
+        uint4 ring[4][2];
         float gq[4] = {0.f, 0.f, 0.f, 0.f}, cs[4] = {0.f, 0.f, 0.f, 0.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
         const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
         const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
         if (has_f) {
             if (local_attn) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl, vl);
+                for (int i = 0; i < 2; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl);
+#pragma unroll
+                for (int i = 0; i < LOCAL_V_PRE; ++i) {
+                    const int pos = warp + CW * i;
+                    const uint2 v = (pos < len) ? ld_stream8(vl + (size_t)pos * KV_DIM + lane * 4) : make_uint2(0, 0);
+                    uint4& dst = ring[2 + (i >> 2)][(i >> 1) & 1];
+                    if (i & 1) { dst.z = v.x; dst.w = v.y; } else { dst.x = v.x; dst.y = v.y; }
+                }
             } else if (warp < ATT_WARPS) {
 #pragma unroll
                 for (int ps = 0; ps < 2; ++ps) {
@@ -635,16 +669,36 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 sn[0] = sv.x; sn[1] = sv.y; sn[2] = sv.z; sn[3] = sv.w;
             }
         }
-        counter_wait(bar, target, abort_flag, p.status, 100 + l);
         Q3_TRACE(ev + 2);
+        Q3_FINE_T(30);
 
         // ==================================================================== F
         if (has_f) {
             // ---- q (both heads of the group), k, v of the new position: warps 8..11 ----
             if (warp >= 8 && warp < 12) {
                 const int role = warp - 8;   // 0, 1: q heads 2g, 2g+1;  2: k;  3: v
-                const float* src = p.qkv + (role < 2 ? (2 * fg + role) * HEAD_DIM : (role == 2 ? Q_DIM + fg * HEAD_DIM : Q_DIM + KV_DIM + fg * HEAD_DIM));
-                const float4 v4 = ldcg4(src + lane * 4);
+                const unsigned long long* src = p.xq + (role < 2 ? (2 * fg + role) * HEAD_DIM : (role == 2 ? Q_DIM + fg * HEAD_DIM : Q_DIM + KV_DIM + fg * HEAD_DIM)) + lane * 4;
+                unsigned long long w0, w1, w2, w3;
+                {   // bounded poll: the four words of this lane must all carry this layer's tag
+                    unsigned it = 0;
+                    unsigned long long t0 = 0;
+                    for (;;) {
+                        asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(src) : "memory");
+                        asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(w2), "=l"(w3) : "l"(src + 2) : "memory");
+                        const bool fresh = (unsigned)(w0 >> 32) == tag && (unsigned)(w1 >> 32) == tag && (unsigned)(w2 >> 32) == tag && (unsigned)(w3 >> 32) == tag;
+                        if (__all_sync(0xffffffffu, fresh)) break;
+                        if (*abort_flag) break;
+                        if ((++it & 127u) == 0) {
+                            const unsigned long long t = global_ns();
+                            if (t0 == 0) t0 = t;
+                            else if (t - t0 > WAIT_NS) {
+                                if (lane == 0) { report(p.status, ST_BARRIER_TIMEOUT, 100 + l, (uint32_t)(w0 >> 32)); *abort_flag = 1; }
+                                break;
+                            }
+                        }
+                    }
+                }
+                const float4 v4 = make_float4(__uint_as_float((unsigned)w0), __uint_as_float((unsigned)w1), __uint_as_float((unsigned)w2), __uint_as_float((unsigned)w3));
                 float v[4] = {v4.x, v4.y, v4.z, v4.w};
                 float* dst = (role < 2) ? q_s + role * 128 : (role == 2 ? k_s : v_s);
                 if (role < 3) {
@@ -674,35 +728,42 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     }
                 }
             }
+            Q3_FINE_T(31);
             cta_sync();
             Q3_TRACE(ev + 3);
 
             if (local_attn) {
-                // ---- local attention of head fh over all cached positions: scores stay in registers ----
+                // ---- local attention of head fh over all cached positions ----
                 float qa[16];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) { qa[i] = q_s[fhh * 128 + sub * 8 + i]; qa[8 + i] = q_s[fhh * 128 + 64 + sub * 8 + i]; }
                 Q3_FINE_T(16);
-                float sreg[LOCAL_PASSES];
                 float tmax = -INFINITY;
+                auto score_pass = [&](const uint4& k0, const uint4& k1, int ps) {
+                    const int pos = ps * 64 + att_slot;
+                    float kf[16];
+                    unpack8f(k0, kf); unpack8f(k1, kf + 8);
+                    float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-                for (int ps = 0; ps < LOCAL_PASSES; ++ps) {
-                    sreg[ps] = -INFINITY;
-                    if (ps < npl) {
-                        const int pos = ps * 64 + att_slot;
-                        const uint4 k0 = ring[ps & 3][0], k1 = ring[ps & 3][1];
-                        if (ps + 4 < 2 * npl) ring_load(ring[ps & 3], ps + 4, npl, len, att_slot, sub, kl, vl);
-                        float kf[16];
-                        unpack8f(k0, kf); unpack8f(k1, kf + 8);
-                        float s0 = 0.f, s1 = 0.f;
+                    for (int i = 0; i < 8; ++i) { s0 = fmaf(qa[i], kf[i], s0); s1 = fmaf(qa[8 + i], kf[8 + i], s1); }
+                    s0 += s1;
+                    s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+                    s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+                    s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
+                    if (pos < len) { tmax = fmaxf(tmax, s0); if (sub == 0) sc[pos] = s0; }
+                };
+                if (npl > 2) {   // passes 2..5 were not fetched ahead: issue them all, then score in order
+                    uint4 kx[LOCAL_PASSES - 2][2];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) { s0 = fmaf(qa[i], kf[i], s0); s1 = fmaf(qa[8 + i], kf[8 + i], s1); }
-                        s0 += s1;
-                        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-                        s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-                        s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
-                        if (pos < len) { sreg[ps] = s0; tmax = fmaxf(tmax, s0); }
-                    }
+                    for (int i = 0; i < LOCAL_PASSES - 2; ++i) ring_load(kx[i], 2 + i, npl, len, att_slot, sub, kl);
+                    score_pass(ring[0][0], ring[0][1], 0);
+                    score_pass(ring[1][0], ring[1][1], 1);
+#pragma unroll
+                    for (int i = 0; i < LOCAL_PASSES - 2; ++i)
+                        if (2 + i < npl) score_pass(kx[i][0], kx[i][1], 2 + i);
+                } else {
+                    score_pass(ring[0][0], ring[0][1], 0);
+                    score_pass(ring[1][0], ring[1][1], 1);   // all zero (and masked) when there is one pass
                 }
                 if (warp == 12) {   // the new row's score: q . k_new in fp32, unrounded
                     const float4 a = *reinterpret_cast<const float4*>(q_s + fhh * 128 + lane * 4);
@@ -720,29 +781,31 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 M = warp_max(M);
                 Q3_FINE_T(19);
 
-                float lsum = 0.f, acc[16];
+                // P.V with a warp per position and four dims per lane: every lane of the warp forms the same
+                // probability from the shared score, so nothing crosses lanes
+                float lsum = 0.f, acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-                Q3_FINE_T(20);
-                switch (npl & 3) {   // V pass 0 sits in ring buffer npl & 3
-                    case 0: local_pv<0>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
-                    case 1: local_pv<1>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
-                    case 2: local_pv<2>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
-                    default: local_pv<3>(ring, sreg, M, npl, len, att_slot, sub, kl, vl, lsum, acc); break;
+                for (int i = 0; i < LOCAL_V_PRE; ++i) {
+                    const int pos = warp + CW * i;
+                    const float pr = (pos < len) ? __expf(sc[min(pos, 3 * SC_HALF - 1)] - M) : 0.f;   // the rows past the cache were fetched as zeros
+                    lsum += pr;
+                    const uint4& src = ring[2 + (i >> 2)][(i >> 1) & 1];
+                    const uint32_t vx = (i & 1) ? src.z : src.x, vy = (i & 1) ? src.w : src.y;
+                    acc[i & 1][0] = fmaf(pr, bf_lo(vx), acc[i & 1][0]); acc[i & 1][1] = fmaf(pr, bf_hi(vx), acc[i & 1][1]);
+                    acc[i & 1][2] = fmaf(pr, bf_lo(vy), acc[i & 1][2]); acc[i & 1][3] = fmaf(pr, bf_hi(vy), acc[i & 1][3]);
+                }
+#pragma unroll 4
+                for (int pos = warp + CW * LOCAL_V_PRE; pos < len; pos += CW) {
+                    const uint2 v = ld_stream8(vl + (size_t)pos * KV_DIM + lane * 4);
+                    const float pr = __expf(sc[pos] - M);
+                    lsum += pr;
+                    acc[0][0] = fmaf(pr, bf_lo(v.x), acc[0][0]); acc[0][1] = fmaf(pr, bf_hi(v.x), acc[0][1]);
+                    acc[0][2] = fmaf(pr, bf_lo(v.y), acc[0][2]); acc[0][3] = fmaf(pr, bf_hi(v.y), acc[0][3]);
                 }
                 Q3_FINE_T(21);
-#pragma unroll
-                for (int off = 8; off <= 16; off <<= 1) {
-                    lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], off);
-                }
-                Q3_FINE_T(22);
-                if (quarter == 0) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) { om[warp * 128 + sub * 8 + i] = acc[i]; om[warp * 128 + 64 + sub * 8 + i] = acc[8 + i]; }
-                    if (sub == 0) lw[warp] = lsum;
-                }
+                *reinterpret_cast<float4*>(om + warp * 128 + lane * 4) =
+                    make_float4(acc[0][0] + acc[1][0], acc[0][1] + acc[1][1], acc[0][2] + acc[1][2], acc[0][3] + acc[1][3]);
+                if (lane == 0) lw[warp] = lsum;
                 cta_sync();
                 Q3_FINE_T(23);
                 Q3_TRACE(ev + 4);
@@ -915,14 +978,12 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             }
             cta_sync();
             Q3_FINE_T(26);
-            if (tid < fn) out_s[tid] = wo_part[tid] + wo_part[128 + tid];
-            cta_sync();
-            if (tid < fn / 4) red_add_v4(p.dA + fr0 + 4 * tid, out_s[4 * tid], out_s[4 * tid + 1], out_s[4 * tid + 2], out_s[4 * tid + 3]);
-        } else if (c == G - 1) {
-            // an idle CTA clears the FFN delta accumulators for the coming GD phase
-            for (int i = tid; i < N_ACC * HIDDEN / 2; i += CT) __stcg(reinterpret_cast<float2*>(p.dB) + i, make_float2(0.f, 0.f));
+            if (tid < fn / 4) {   // fn <= 116: warp 0 adds the slice to the attention delta
+                const float4 a = *reinterpret_cast<const float4*>(wo_part + 4 * tid), b = *reinterpret_cast<const float4*>(wo_part + 128 + 4 * tid);
+                red_add_v4(dAl + fr0 + 4 * tid, a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+            }
+            if (warp == 0) __syncwarp();
         }
-        cta_sync();
         Q3_TRACE(ev + 6);
         if (tid == 0) counter_arrive(bar);
         if (tid == 32 && has_f) mbar_arrive(&empty[1]);
@@ -933,9 +994,12 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 
         // ==================================================================== GD
         {
-            const float2 a = ldcg2(p.X1 + 2 * tid), d = ldcg2(p.dA + 2 * tid);
+            const float2 a = ldcg2(p.X1 + 2 * tid), d = ldcg2(dAl + 2 * tid);
             const float x0 = a.x + d.x, x1 = a.y + d.y;
             if (c == 0) __stcg(reinterpret_cast<float2*>(p.X0 + 2 * tid), make_float2(x0, x1));
+            if (c == G - 1 && l + 1 < L)   // the next layer's FFN delta starts from zero
+                for (int i = tid; i < N_ACC * HIDDEN / 2; i += CT)
+                    __stcg(reinterpret_cast<float2*>(p.dB + (size_t)((l + 1) & 1) * N_ACC * HIDDEN) + i, make_float2(0.f, 0.f));
             {
                 bf16_raw h0, m0, l0, h1, m1, l1;
                 split3(x0 * bf_lo(gain2), h0, m0, l0);
@@ -948,9 +1012,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             if (lane == 0) red[warp] = ss;
             cta_sync();
             Q3_TRACE(ev + 8);
-            float tot = (lane < CW) ? red[lane] : 0.f;
-            tot = warp_sum(tot);
-            const float r = rsqrtf(tot / (float)HIDDEN + EPS);
             {
                 Q3_FINE_T(5);
                 // warp (mat, ke): gate (0) or up (1) rows, k range [128 ke, 128 ke + 128), both 16-row tiles
@@ -985,6 +1046,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 if (tid < 32) {   // hid of this CTA's rows, split for the down projection; rows past the share are zero
                     float hv = 0.f;
                     if (tid < ni) {
+                        const float r = rsqrtf(sum16(red) / (float)HIDDEN + EPS);
                         float g = 0.f, u = 0.f;
 #pragma unroll
                         for (int e8 = 0; e8 < 8; ++e8) { g += part[e8 * 64 + tid]; u += part[e8 * 64 + 32 + tid]; }
@@ -1046,7 +1108,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             Q3_FINE_T(12);
             if (tid < 256) {
                 const float4 t = *reinterpret_cast<const float4*>(dout + tid * 4);
-                red_add_v4(dBmine + tid * 4, t.x, t.y, t.z, t.w);
+                red_add_v4(dBl + (size_t)(c & (N_ACC - 1)) * HIDDEN + tid * 4, t.x, t.y, t.z, t.w);
             }
             Q3_FINE_T(13);
             cta_sync();
@@ -1065,7 +1127,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     // ======================================================================== LM head + argmax
     {
         float x0, x1;
-        load_x_ffn(x0, x1);
+        load_x_ffn(p.dB + (size_t)((L - 1) & 1) * N_ACC * HIDDEN, x0, x1);
+        if (c == 1) __stcg(reinterpret_cast<float2*>(p.dA + 2 * tid), make_float2(0.f, 0.f));   // the next launch's first F phase adds into dA[0]
         const float ss = warp_sum(x0 * x0 + x1 * x1);
         if (lane == 0) red[warp] = ss;
         cta_sync();
@@ -1125,6 +1188,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 // every CTA has passed every barrier: rearm the counters for the next launch
                 p.sync[0] = 0;
                 p.sync[2] = 0;
+                *const_cast<unsigned*>(p.epoch) = tag_base / 32u + 1u;
             }
             if (tid >= 8 && tid < 16) p.sync[tid] = 0;
         }
@@ -1219,8 +1283,8 @@ int persist_setup(q3_engine* e) {
     PersistState* s = new PersistState();
     s->packed = nullptr; s->X = nullptr; s->grid = grid; s->smem = smem;
     for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
-    if (cudaMalloc(&s->X, (3 + N_ACC) * HIDDEN * sizeof(float)) != cudaSuccess ||
-        cudaMemset(s->X, 0, (3 + N_ACC) * HIDDEN * sizeof(float)) != cudaSuccess ||
+    if (cudaMalloc(&s->X, X_FLOATS * sizeof(float)) != cudaSuccess ||
+        cudaMemset(s->X, 0, X_FLOATS * sizeof(float)) != cudaSuccess ||
         cudaMalloc(&s->packed, (size_t)e->cfg.n_layers * grid * share_elems(grid) * sizeof(bf16_raw)) != cudaSuccess) {
         if (s->X) cudaFree(s->X);
         delete s;
@@ -1281,8 +1345,10 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
     p.seq_k = a->seq_k; p.seq_v = a->seq_v; p.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
     p.seq_len = a->seq_len; p.logits = a->logits; p.next_token = reinterpret_cast<long long*>(a->next_token);
     p.k_write = reinterpret_cast<bf16_raw*>(a->k_write); p.v_write = reinterpret_cast<bf16_raw*>(a->v_write);
-    p.X0 = s->X; p.X1 = s->X + HIDDEN; p.dA = s->X + 2 * HIDDEN; p.dB = s->X + 3 * HIDDEN;
-    p.qkv = e->qkv; p.part = e->part; p.rope = e->rope; p.sync = e->sync; p.status = e->status; p.pval = e->pval; p.pidx = e->pidx;
+    p.X0 = s->X; p.X1 = s->X + HIDDEN; p.dA = s->X + 2 * HIDDEN; p.dB = s->X + 4 * HIDDEN;
+    p.xq = reinterpret_cast<unsigned long long*>(s->X + (4 + 2 * N_ACC) * HIDDEN);
+    p.epoch = reinterpret_cast<const unsigned*>(s->X + (4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM);
+    p.part = e->part; p.rope = e->rope; p.sync = e->sync; p.status = e->status; p.pval = e->pval; p.pidx = e->pidx;
     p.trace = (e->trace && e->trace_words >= (int64_t)s->grid * (4 + EV_PER_LAYER * e->cfg.n_layers)) ? e->trace : nullptr;
     p.n_layers = e->cfg.n_layers; p.vocab = e->cfg.vocab; p.append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
     p.pace = e->cfg.pace_cycles;

@@ -108,7 +108,7 @@ def cmd_bench(args) -> int:
     return 0
 
 
-PHASE_EVENTS = ["Q stage", "Q done", "Q->F barrier", "F q/k/v", "F partial", "F group", "F done", "F->GD barrier",
+PHASE_EVENTS = ["Q stage", "Q done", "K/V prefetch", "F q/k/v exchange", "F partial", "F group", "F done", "F->GD barrier",
                 "GD stage", "GD hid", "GD done", "GD->Q barrier"]
 
 
@@ -137,7 +137,7 @@ def cmd_trace(args) -> int:
           f"LM head {(t[:, 1 + ev * L].max() - med[ev * L]) / 1e3:.1f} us, layer median {m.sum() / 1e3:.2f} us")
     for n, v in zip(PHASE_EVENTS, m):
         print(f"  {n:<16} {v:7.0f} ns")
-    for name, d in (("Q", 1), ("F", 6), ("GD", 10)):
+    for name, d in (("F", 6), ("GD", 10)):
         skew = np.median([t[:, 1 + ev * l + d].max() - np.median(t[:, 1 + ev * l + d]) for l in range(1, L)])
         hop = np.median([np.median(t[:, 2 + ev * l + d]) - t[:, 1 + ev * l + d].max() for l in range(1, L)])
         print(f"  barrier after {name:<3} skew {skew:6.0f} ns  hop {hop:6.0f} ns")
