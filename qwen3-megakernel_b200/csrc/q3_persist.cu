@@ -34,8 +34,11 @@ namespace q3 {
 
 constexpr int CW = 16;                        // consumer warps
 constexpr int CT = CW * 32;                   // consumer threads
-constexpr int NPW = 2;                        // producer warps
-constexpr int PT = CT + 32 * NPW;             // consumers + producers
+constexpr int PT = CT;                        // threads per CTA
+#ifndef Q3_PUMP_CHUNK
+#define Q3_PUMP_CHUNK 32768
+#endif
+constexpr int PUMP_CHUNK = Q3_PUMP_CHUNK;     // largest single bulk copy of the weight stream (a multiple of 16)
 constexpr int WO_SLICES = 9;                  // row slices of Wo; CTA c < 144 owns head c % 16, slice c / 16
 constexpr int F_CTAS = Q_HEADS * WO_SLICES;   // 144
 constexpr int GROUP_CTAS = 2 * WO_SLICES;     // CTAs sharing one kv head
@@ -47,27 +50,14 @@ constexpr int WROW = 1032;                    // elements between weight rows in
                                               // the eight row addresses of an ldmatrix fall into different banks
 constexpr int WOROW = 136;                    // the same for the 128-column Wo slice rows
 constexpr int ATT_WARPS = 8;                  // split attention: warps that attend positions (32 positions per pass)
-constexpr int LOCAL_PASSES = 6;               // local attention: passes of 64 positions a CTA runs on its own
+constexpr int LOCAL_PASSES = 3;               // local attention: passes of 64 positions a CTA runs on its own (measured: splitting wins beyond ~200 positions)
 constexpr int LOCAL_ATTN_MAX = 64 * LOCAL_PASSES - 1;   // up to this many cached positions every CTA attends its whole head
 #ifndef Q3_N_ACC
 #define Q3_N_ACC 2
 #endif
-#ifndef Q3_EXP
-#define Q3_EXP 0
-#endif
-#ifndef Q3_CP_GROUP
-#define Q3_CP_GROUP 16
-#endif
-#ifndef Q3_CP_DEPTH
-#define Q3_CP_DEPTH 8
-#endif
-constexpr int CP_GROUP = Q3_CP_GROUP;         // producer lanes: 16-byte copies per committed group
-constexpr int CP_DEPTH = Q3_CP_DEPTH;         // ... and groups in flight
 constexpr int N_ACC = Q3_N_ACC;               // accumulators for the FFN delta (fewer same-address atomics each)
 constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
 constexpr int PART_STRIDE = 132;              // floats per published partial: [0] max, [1] sum, [4..132) output
-constexpr int DEFAULT_PACE = 100;             // nanoseconds the producer sleeps after each bulk copy
-constexpr int COPY_BYTES = 16384;             // largest single bulk copy
 constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;   // patience of every device-side wait: 200 ms
 // fp32 tail of shared memory: 8 KB union | q_s[2][128] k_s v_s | o split [3][128] bf16 | hid split [3][32] bf16 | red lw misc | scores
 constexpr int FBUF_FLOATS = 2048 + 4 * 128 + 192 + 48 + 32 + 16 + 16 + 3 * SC_HALF;
@@ -98,7 +88,7 @@ struct PersistParams {
     float* pval;
     int* pidx;
     unsigned long long* trace;   // optional [grid][4 + 12 * n_layers] %globaltimer stamps of thread 0, or nullptr
-    int n_layers, vocab, append, pace;
+    int n_layers, vocab, append;
 };
 
 struct PersistState {
@@ -215,28 +205,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile
     return true;
 }
 
-// the same for a thread with nothing else to do: the hardware may suspend it up to 2 us per try
-__device__ __forceinline__ bool mbar_wait_sleepy(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
-    unsigned it = 0;
-    unsigned long long t0 = 0;
-    for (;;) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(smem_u32(b)), "r"(parity), "r"(2000u) : "memory");
-        if (ok) return true;
-        if ((++it & 15u) == 0) {
-            const unsigned long long t = global_ns();
-            if (t0 == 0) t0 = t;
-            else if (t - t0 > WAIT_NS) {
-                if ((threadIdx.x & 31) == 0) { report(status, ST_MBAR_TIMEOUT, site, parity); *abort_flag = 1; }
-                return false;
-            }
-        }
-    }
-}
-
-// consumer side: a single non-blocking test when the slot is already full (the normal case: the
-// producers run a layer ahead); a late slot is polled by one lane per warp
+// a single non-blocking test when the slot is already full (the normal case: the copies were issued a
+// phase or more ahead); a late slot is polled by one lane per warp
 __device__ __forceinline__ void slot_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -303,16 +273,6 @@ __device__ __forceinline__ void fold_cols(const float (&c)[4], float& row_lo, fl
     row_hi = (c[2] + c[3]) + l1;
 }
 
-// this lane's 32 activations of a 1024-vector staged in shared memory (lane-interleaved layout)
-__device__ __forceinline__ void load_act_regs(const float* xs, int lane, float* xr) {
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const float4 a = *reinterpret_cast<const float4*>(xs + k * 256 + lane * 4);
-        const float4 b = *reinterpret_cast<const float4*>(xs + k * 256 + 128 + lane * 4);
-        xr[k * 8 + 0] = a.x; xr[k * 8 + 1] = a.y; xr[k * 8 + 2] = a.z; xr[k * 8 + 3] = a.w;
-        xr[k * 8 + 4] = b.x; xr[k * 8 + 5] = b.y; xr[k * 8 + 6] = b.z; xr[k * 8 + 7] = b.w;
-    }
-}
 
 // Local attention keeps its K rows in a ring of four register buffers (a quarter-warp per position,
 // 64 positions per pass): pass i lives in buffer i & 3 and the load of pass i + 4 is issued the moment
@@ -376,8 +336,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     float* misc = lw + 16;       // [16]: [0] score of the new row for this CTA's head
     float* sc = misc + 16;       // split attention: [2][SC_HALF] scores of this CTA's positions; local: [3 * SC_HALF] scores of all positions
     uint64_t* full = reinterpret_cast<uint64_t*>(sc + 3 * SC_HALF);   // [4] slot filled
-    uint64_t* empty = full + 4;                                        // [4] slot released by the consumers
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(full + 8);
 
     const int n_ev = 4 + EV_PER_LAYER * L;
 #ifdef Q3_FINE
@@ -388,11 +347,11 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 #define Q3_TRACE(ev) do { if (p.trace != nullptr && tid == 0) p.trace[(size_t)c * n_ev + (ev)] = global_ns(); } while (0)
     Q3_TRACE(0);
     if (tid == 0) {
-        for (int i = 0; i < 4; ++i) { mbar_init(&full[i], 32 * NPW); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 4; ++i) mbar_init(&full[i], 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();   // the only barrier the producer warps join
+    __syncthreads();
 
     // LM head rows of this CTA, four rows in flight per warp; every warp of the CTA (producers included)
     // takes part once the layer loop is over.  Keeps the warp's best (value, row); ties -> lowest row.
@@ -431,52 +390,33 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     float* const lm_bv = q_s;                               // [CW + NPW] per-warp best values
     int* const lm_bi = reinterpret_cast<int*>(k_s);         // [CW + NPW] and their rows
 
-    // ================================================================================ producer warps
-    // Weights reach shared memory through cp.async (16-byte LDGSTS copies on the load/store path),
-    // not through the TMA unit: measured on B200, a grid barrier that runs while bulk copies stream
-    // takes 2.1 us at 2.4 TB/s of background traffic and 2.6 us at 4.7 TB/s (1.55 us idle), whereas
-    // the same traffic issued as cp.async by two warps (3.4 TB/s) leaves it at 1.66 us.  Each producer
-    // lane keeps up to 8 groups of 16 copies in flight (64 KB per warp); a lane's arrival on the
-    // slot's mbarrier is tied to the completion of its copies (cp.async.mbarrier.arrive.noinc).
-    if (warp >= CW) {
-        const int pw = warp - CW;
-        const int slot_rows[4] = {qmax, WO_ROWS_MAX, 2 * imax, imax};
-        bf16_raw* const slot_dst[4] = {sA, sB, sC, sD};
-        bool alive = true;
-        int in_group = 0;
-        for (int l = 0; l < L && alive; ++l) {
-            const unsigned char* src = reinterpret_cast<const unsigned char*>(p.packed + ((size_t)l * G + c) * share_elems(G));
-            for (int slot = 0; slot < 4 && alive; ++slot) {
-                const int bytes = slot_rows[slot] * (slot == 1 ? WOROW : WROW) * 2;
-                if (!(slot == 1 && !has_f)) {
-                    if (l > 0) alive = mbar_wait_sleepy(&empty[slot], (l - 1) & 1, abort_flag, p.status, 20 + slot);
-                    if (!alive) break;
-                    const uint32_t dst = smem_u32(slot_dst[slot]);
-                    const int pieces = bytes >> 4;
-                    for (int i = pw * 32 + lane; i < pieces; i += NPW * 32) {
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 16), "l"(src + (size_t)i * 16) : "memory");
-                        if (++in_group == CP_GROUP) {
-                            asm volatile("cp.async.commit_group;" ::: "memory");
-                            asm volatile("cp.async.wait_group %0;" ::"n"(CP_DEPTH - 1) : "memory");
-                            in_group = 0;
-                        }
-                    }
-                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[slot])) : "memory");
-                }
-                src += bytes;
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        // the weights are in: help with the LM head
-        asm volatile("bar.sync 2, %0;" ::"n"(PT) : "memory");    // the consumers have staged the final activations
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
-        lm_stream(warp, CW + NPW, bv, bi);
-        if (lane == 0) { lm_bv[warp] = bv; lm_bi[warp] = bi; }
-        asm volatile("bar.sync 3, %0;" ::"n"(PT) : "memory");
-        return;
-    }
+    // ================================================================================ weight delivery
+    // There are no producer warps.  One thread (lane 0 of warp 1) moves the CTA's packed rows into the four slots
+    // with TMA bulk copies, a whole slot at a time, at the START of a phase, so that the copies have landed before
+    // the phase ends and nothing is in flight while a grid barrier is polled: measured on B200, a barrier polled
+    // while 64 KB per SM of bulk copies are in flight takes 2.1 to 2.6 us instead of 1.55 us (the poll's answer
+    // queues behind the copies), and cp.async (LDGSTS) copies in flight slow the other warps' own accesses.
+    //   start of Q  (layer l): down rows of layer l         (43 KB, read in GD)
+    //   start of F  (layer l): gate/up rows of layer l      (87 KB, read in GD)
+    //   start of GD (layer l): q/k/v rows and Wo slice of layer l + 1   (58 + 31 KB)
+    // The first chunk of a slot arms the slot's mbarrier with the slot's byte count; the consumers wait on it.
+    const int bytesA = qmax * WROW * 2, bytesB = WO_ROWS_MAX * WOROW * 2, bytesC = 2 * imax * WROW * 2, bytesD = imax * WROW * 2;
+    const bool pumper = tid == 32;
+    int pump_armed = 0, pump_parity = 0;                // per slot: armed at all, and the parity of its last armed phase
+    auto fetch_slot = [&](int slot, int layer) {
+        if (!pumper || layer >= L || (slot == 1 && !has_f)) return;
+        const int bytes = slot == 0 ? bytesA : slot == 1 ? bytesB : slot == 2 ? bytesC : bytesD;
+        const int off = slot == 0 ? 0 : slot == 1 ? bytesA : slot == 2 ? bytesA + bytesB : bytesA + bytesB + bytesC;
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.packed + ((size_t)layer * G + c) * share_elems(G)) + off;
+        unsigned char* dst = reinterpret_cast<unsigned char*>(slot == 0 ? sA : slot == 1 ? sB : slot == 2 ? sC : sD);
+        fence_proxy_async();   // the slot's last readers used ordinary loads; they are behind a CTA barrier
+        mbar_expect_tx(&full[slot], (uint32_t)bytes);
+        pump_armed |= 1 << slot;
+        pump_parity = (pump_parity & ~(1 << slot)) | ((layer & 1) << slot);
+        for (int o = 0; o < bytes; o += PUMP_CHUNK) bulk_g2s(dst + o, src + o, (uint32_t)min(PUMP_CHUNK, bytes - o), &full[slot]);
+    };
+    fetch_slot(0, 0);
+    fetch_slot(1, 0);
 
     // ================================================================================ consumer warps
     long long tok = p.token[0];
@@ -531,6 +471,14 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         float* dAl = p.dA + (size_t)(l & 1) * HIDDEN;
         float* dBl = p.dB + (size_t)(l & 1) * N_ACC * HIDDEN;
         const unsigned tag = tag_base + (unsigned)l + 1u;
+        // K and V rows of the cached positions, fetched at the very start of the layer (they depend on nothing of this
+        // step), so that they have arrived, and the SM's input path is quiet, when the q/k/v exchange starts polling.
+        // Split attention: [0], [1] = K passes, [2], [3] = V passes of the CTA's positions.  Local attention:
+        // [0], [1] = K passes 0, 1 (a quarter-warp per position) and [2], [3] = V[warp + 16 i][4 lane .. 4 lane + 3]
+        // for i < 8, two positions per uint4.
+        uint4 ring[4][2];
+        const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
+        const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
         // ==================================================================== Q
         {
             float x0, x1;
@@ -541,6 +489,33 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             } else {
                 load_x_ffn(p.dB + (size_t)((l - 1) & 1) * N_ACC * HIDDEN, x0, x1);
             }
+            if (has_f) {
+                if (local_attn) {
+    #pragma unroll
+                    for (int i = 0; i < 2; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl);
+    #pragma unroll
+                    for (int i = 0; i < LOCAL_V_PRE; ++i) {
+                        const int pos = warp + CW * i;
+                        const uint2 v = (pos < len) ? ld_stream8(vl + (size_t)pos * KV_DIM + lane * 4) : make_uint2(0, 0);
+                        uint4& dst = ring[2 + (i >> 2)][(i >> 1) & 1];
+                        if (i & 1) { dst.z = v.x; dst.w = v.y; } else { dst.x = v.x; dst.y = v.y; }
+                    }
+                } else if (warp < ATT_WARPS) {
+    #pragma unroll
+                    for (int ps = 0; ps < 2; ++ps) {
+                        const int pos = cp0 + ps * 32 + att_slot;
+                        if (pos < cp1) {
+                            const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
+                            const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
+                            ring[ps][0] = ld_stream(kr + sub); ring[ps][1] = ld_stream(kr + 8 + sub);
+                            ring[2 + ps][0] = ld_stream(vr + sub); ring[2 + ps][1] = ld_stream(vr + 8 + sub);
+                        } else {
+                            ring[ps][0] = ring[ps][1] = ring[2 + ps][0] = ring[2 + ps][1] = make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                }
+            }
+            fetch_slot(3, l);   // down rows of this layer: landed before the q/k/v exchange starts polling
             if (c == 0) __stcg(reinterpret_cast<float2*>(p.X1 + 2 * tid), make_float2(x0, x1));
             if (c == 1 && l + 1 < L) __stcg(reinterpret_cast<float2*>(p.dA + (size_t)((l + 1) & 1) * HIDDEN + 2 * tid), make_float2(0.f, 0.f));
             if (c == G - 1 && l == 0)
@@ -560,9 +535,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             cta_sync();
             Q3_TRACE(ev + 0);
             Q3_FINE_T(0);
-#if Q3_EXP == 2 || Q3_EXP == 3
-            const float r = rsqrtf(sum16(red) / (float)HIDDEN + EPS);
-#endif
             // warp w: k range [64 w, 64 w + 64) of both 16-row tiles of this CTA's rows
             uint32_t bq[4][2];
 #pragma unroll
@@ -603,62 +575,25 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 }
             }
             cta_sync();
-            if (warp == 0) {   // nq <= 28: the row sums, the 1/rms factor and the arrival all sit in warp 0
+            if (warp == 0) {   // nq <= 28: the row sums and the 1/rms factor sit in warp 0
                 if (tid < nq) {
-#if !(Q3_EXP == 2 || Q3_EXP == 3)
                     const float r = rsqrtf(sum16(red) / (float)HIDDEN + EPS);
-#endif
                     float v0 = 0.f, v1 = 0.f;
 #pragma unroll
                     for (int w = 0; w < CW; w += 2) { v0 += part[w * 32 + tid]; v1 += part[w * 32 + 32 + tid]; }
                     // value and tag travel in one 64-bit word: no barrier between Q and F, the readers poll the tags
                     const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint((v0 + v1) * r);
-#if Q3_EXP == 1 || Q3_EXP == 3
-                    __stcg(p.xq + q0 + tid, word);
-#else
                     asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p.xq + q0 + tid), "l"(word) : "memory");
-#endif
                 }
                 Q3_FINE_T(3);
                 Q3_FINE_T(4);
                 Q3_TRACE(ev + 1);
             }
-            if (tid == 32) mbar_arrive(&empty[0]);
         }
 
-        // ---- between arrive and wait: what the F phase needs that no other CTA produces ----
-        // fetched ahead of the barrier wait.  Split attention: [0], [1] = K passes, [2], [3] = V passes of the
-        // CTA's positions.  Local attention: [0], [1] = K passes 0, 1 (a quarter-warp per position) and
-        // [2], [3] = V[warp + 16 i][4 lane .. 4 lane + 3] for i < 8, two positions per uint4.
-        uint4 ring[4][2];
+        // ---- what the F phase needs that no other CTA produces: norm gains and the RoPE row ----
         float gq[4] = {0.f, 0.f, 0.f, 0.f}, cs[4] = {0.f, 0.f, 0.f, 0.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
-        const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
-        const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
         if (has_f) {
-            if (local_attn) {
-#pragma unroll
-                for (int i = 0; i < 2; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl);
-#pragma unroll
-                for (int i = 0; i < LOCAL_V_PRE; ++i) {
-                    const int pos = warp + CW * i;
-                    const uint2 v = (pos < len) ? ld_stream8(vl + (size_t)pos * KV_DIM + lane * 4) : make_uint2(0, 0);
-                    uint4& dst = ring[2 + (i >> 2)][(i >> 1) & 1];
-                    if (i & 1) { dst.z = v.x; dst.w = v.y; } else { dst.x = v.x; dst.y = v.y; }
-                }
-            } else if (warp < ATT_WARPS) {
-#pragma unroll
-                for (int ps = 0; ps < 2; ++ps) {
-                    const int pos = cp0 + ps * 32 + att_slot;
-                    if (pos < cp1) {
-                        const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
-                        const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
-                        ring[ps][0] = ld_stream(kr + sub); ring[ps][1] = ld_stream(kr + 8 + sub);
-                        ring[2 + ps][0] = ld_stream(vr + sub); ring[2 + ps][1] = ld_stream(vr + 8 + sub);
-                    } else {
-                        ring[ps][0] = ring[ps][1] = ring[2 + ps][0] = ring[2 + ps][1] = make_uint4(0, 0, 0, 0);
-                    }
-                }
-            }
             if (warp >= 8 && warp < 11) {   // warps 8, 9 normalise the two q heads, warp 10 normalises k: dims 4*lane..
                 const bf16_raw* gsrc = (warp < 10 ? p.qn : p.kn) + (size_t)l * HEAD_DIM + lane * 4;
                 const uint2 gg = *reinterpret_cast<const uint2*>(gsrc);
@@ -669,6 +604,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 sn[0] = sv.x; sn[1] = sv.y; sn[2] = sv.z; sn[3] = sv.w;
             }
         }
+        fetch_slot(2, l);       // gate/up rows of this layer: in flight during F, landed before its barrier is polled
         Q3_TRACE(ev + 2);
         Q3_FINE_T(30);
 
@@ -986,7 +922,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         }
         Q3_TRACE(ev + 6);
         if (tid == 0) counter_arrive(bar);
-        if (tid == 32 && has_f) mbar_arrive(&empty[1]);
         target += G;
         gain2 = *reinterpret_cast<const uint32_t*>(p.ln2 + (size_t)l * HIDDEN + 2 * tid);
         counter_wait(bar, target, abort_flag, p.status, 200 + l);
@@ -996,6 +931,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         {
             const float2 a = ldcg2(p.X1 + 2 * tid), d = ldcg2(dAl + 2 * tid);
             const float x0 = a.x + d.x, x1 = a.y + d.y;
+            fetch_slot(0, l + 1);   // q/k/v rows and Wo slice of the next layer: landed before this phase's barrier is polled
+            fetch_slot(1, l + 1);
             if (c == 0) __stcg(reinterpret_cast<float2*>(p.X0 + 2 * tid), make_float2(x0, x1));
             if (c == G - 1 && l + 1 < L)   // the next layer's FFN delta starts from zero
                 for (int i = tid; i < N_ACC * HIDDEN / 2; i += CT)
@@ -1062,7 +999,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             }
             cta_sync();   // hid ready; the activations and the gate/up slot are no longer needed
             Q3_TRACE(ev + 9);
-            if (tid == 32) mbar_arrive(&empty[2]);
 
             Q3_FINE_T(9);
             slot_wait(&full[3], l & 1, abort_flag, p.status, 13);
@@ -1115,7 +1051,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             Q3_FINE_T(14);
             Q3_TRACE(ev + 10);
             if (tid == 0) counter_arrive(bar);
-            if (tid == 32) mbar_arrive(&empty[3]);
         }
         target += G;
         gain2 = (l + 1 < L) ? *reinterpret_cast<const uint32_t*>(p.ln1 + (size_t)(l + 1) * HIDDEN + 2 * tid)
@@ -1139,21 +1074,20 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         xs[act_slot(2 * tid + 1)] = (x1 * r) * bf_hi(gain2);
         cta_sync();
 
-        asm volatile("bar.sync 2, %0;" ::"n"(PT) : "memory");    // activations staged: the producer warps join
         float bestv = -INFINITY;
         int besti = 0x7fffffff;
-        lm_stream(warp, CW + NPW, bestv, besti);
+        lm_stream(warp, CW, bestv, besti);
         Q3_TRACE(1 + EV_PER_LAYER * L);
         // CTA argmax (ties -> lowest index), then the last CTA to finish reduces over CTAs
         float* bv_s = lm_bv;
         int* bi_s = lm_bi;
         if (lane == 0) { bv_s[warp] = bestv; bi_s[warp] = besti; }
-        asm volatile("bar.sync 3, %0;" ::"n"(PT) : "memory");    // all 18 partials written
+        cta_sync();
         int* last_flag = reinterpret_cast<int*>(v_s);
         if (tid == 0) {
             float bv = bv_s[0];
             int bi = bi_s[0];
-            for (int w = 1; w < CW + NPW; ++w)
+            for (int w = 1; w < CW; ++w)
                 if (bv_s[w] > bv || (bv_s[w] == bv && bi_s[w] < bi)) { bv = bv_s[w]; bi = bi_s[w]; }
             __stcg(p.pval + c, bv);
             __stcg(p.pidx + c, bi);
@@ -1193,6 +1127,12 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             if (tid >= 8 && tid < 16) p.sync[tid] = 0;
         }
         Q3_TRACE(2 + EV_PER_LAYER * L);
+    }
+    // The issuing thread makes sure (bounded) that every slot it armed has landed before the CTA gives its
+    // shared memory back; after a clean step these four tests succeed at once.
+    if (pumper) {
+        for (int slot = 0; slot < 4; ++slot)
+            if (pump_armed & (1 << slot)) mbar_wait(&full[slot], (uint32_t)((pump_parity >> slot) & 1), abort_flag, p.status, 30 + slot);
     }
 #undef Q3_TRACE
 #undef Q3_FINE_T
@@ -1351,7 +1291,6 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
     p.part = e->part; p.rope = e->rope; p.sync = e->sync; p.status = e->status; p.pval = e->pval; p.pidx = e->pidx;
     p.trace = (e->trace && e->trace_words >= (int64_t)s->grid * (4 + EV_PER_LAYER * e->cfg.n_layers)) ? e->trace : nullptr;
     p.n_layers = e->cfg.n_layers; p.vocab = e->cfg.vocab; p.append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
-    p.pace = e->cfg.pace_cycles;
     void* args[] = {&p};
     cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(q3_persist_decode), dim3(s->grid), dim3(PT), args, (size_t)s->smem, st);
     ++e->launches;
