@@ -321,7 +321,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     float* fbuf = reinterpret_cast<float*>(sD + (size_t)imax * WROW);
     // one 8 KB region with a different tenant per phase
     uint32_t* xsp = reinterpret_cast<uint32_t*>(fbuf);   // Q, GD: activations split in three bf16 parts, [3][512] pairs (6 KB)
-    float* part = fbuf + 1536;                           // Q, GD: per-warp partial row sums (2 KB)
+    float* part = fbuf + 1536;                           // Q: per-warp partial row sums [16][32] (2 KB)
+    float* gpart = fbuf + 1536;                          // GD: per-warp partial sums of the 48 gate/up tile rows [16][48] (3 KB: runs into q_s, idle in GD)
     float* om = fbuf;                                    // F: [8 warps][2 heads][128] attention partials
     float* wo_part = fbuf;                               // F: [2 k-halves][128] Wo slice partial sums (after the partials are published)
     float* dout = fbuf;                                  // GD: [1024] down-projection outputs of this CTA (after the gate/up rows)
@@ -479,21 +480,12 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         uint4 ring[4][2];
         const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
         const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
-        // ==================================================================== Q
-        {
-            float x0, x1;
-            Q3_FINE_T(27);
-            if (l == 0) {
-                const uint32_t e = *reinterpret_cast<const uint32_t*>(p.embed + (size_t)tok * HIDDEN + 2 * tid);
-                x0 = bf_lo(e); x1 = bf_hi(e);
-            } else {
-                load_x_ffn(p.dB + (size_t)((l - 1) & 1) * N_ACC * HIDDEN, x0, x1);
-            }
+        auto kv_prefetch = [&]() {
             if (has_f) {
                 if (local_attn) {
-    #pragma unroll
+#pragma unroll
                     for (int i = 0; i < 2; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl);
-    #pragma unroll
+#pragma unroll
                     for (int i = 0; i < LOCAL_V_PRE; ++i) {
                         const int pos = warp + CW * i;
                         const uint2 v = (pos < len) ? ld_stream8(vl + (size_t)pos * KV_DIM + lane * 4) : make_uint2(0, 0);
@@ -501,7 +493,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         if (i & 1) { dst.z = v.x; dst.w = v.y; } else { dst.x = v.x; dst.y = v.y; }
                     }
                 } else if (warp < ATT_WARPS) {
-    #pragma unroll
+#pragma unroll
                     for (int ps = 0; ps < 2; ++ps) {
                         const int pos = cp0 + ps * 32 + att_slot;
                         if (pos < cp1) {
@@ -515,6 +507,18 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     }
                 }
             }
+        };
+        // ==================================================================== Q
+        {
+            float x0, x1;
+            Q3_FINE_T(27);
+            if (l == 0) {
+                const uint32_t e = *reinterpret_cast<const uint32_t*>(p.embed + (size_t)tok * HIDDEN + 2 * tid);
+                x0 = bf_lo(e); x1 = bf_hi(e);
+            } else {
+                load_x_ffn(p.dB + (size_t)((l - 1) & 1) * N_ACC * HIDDEN, x0, x1);
+            }
+            if (warp >= 8 && warp < 12) kv_prefetch();   // the warps that will poll the q/k/v exchange fetch now, the others while they wait for it
             fetch_slot(3, l);   // down rows of this layer: landed before the q/k/v exchange starts polling
             if (c == 0) __stcg(reinterpret_cast<float2*>(p.X1 + 2 * tid), make_float2(x0, x1));
             if (c == 1 && l + 1 < L) __stcg(reinterpret_cast<float2*>(p.dA + (size_t)((l + 1) & 1) * HIDDEN + 2 * tid), make_float2(0.f, 0.f));
@@ -589,6 +593,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 Q3_FINE_T(4);
                 Q3_TRACE(ev + 1);
             }
+            if (warp < 8 || warp >= 12) kv_prefetch();   // after the rows are published: nothing waits for these warps now
         }
 
         // ---- what the F phase needs that no other CTA produces: norm gains and the RoPE row ----
@@ -951,32 +956,44 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             Q3_TRACE(ev + 8);
             {
                 Q3_FINE_T(5);
-                // warp (mat, ke): gate (0) or up (1) rows, k range [128 ke, 128 ke + 128), both 16-row tiles
-                const int mat = warp >> 3, ke = warp & 7;
-                uint32_t bx[8][2];
+                // The slot holds one matrix of 2 * imax = 42 rows (gate rows, then up rows): three 16-row tiles cover it
+                // (the last six rows of the third tile belong to the next slot and are never used).  Warp w takes
+                // the k range [64 w, 64 w + 64) of all three tiles.
+                uint32_t bx[4][2];
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
-                    const int kp = (128 * ke + 16 * t + fr_k) >> 1;
+                for (int t = 0; t < 4; ++t) {
+                    const int kp = (64 * warp + 16 * t + fr_k) >> 1;
                     bx[t][0] = (fr_n < 3) ? xsp[fr_n * 512 + kp] : 0u;
                     bx[t][1] = (fr_n < 3) ? xsp[fr_n * 512 + kp + 4] : 0u;
                 }
                 Q3_FINE_T(6);
                 slot_wait(&full[2], l & 1, abort_flag, p.status, 12);
                 Q3_FINE_T(7);
+                uint32_t af[3][4][4];
 #pragma unroll
-                for (int rt = 0; rt < 2; ++rt) {
-                    const uint32_t abase = smem_u32(sC + (size_t)(mat * imax + 16 * rt + lm_row) * WROW + 128 * ke + lm_k);
-                    uint32_t af[8][4];
+                for (int rt = 0; rt < 3; ++rt) {
+                    const uint32_t abase = smem_u32(sC + (size_t)(16 * rt + lm_row) * WROW + 64 * warp + lm_k);
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) ldsm_x4(af[t], abase + 32 * t);
-                    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int t = 0; t < 4; ++t) ldsm_x4(af[rt][t], abase + 32 * t);
+                }
+                float cg[3][2][4];
 #pragma unroll
-                    for (int t = 0; t < 8; t += 2) { mma_bf16(c0, af[t], bx[t][0], bx[t][1]); mma_bf16(c1, af[t + 1], bx[t + 1][0], bx[t + 1][1]); }
+                for (int rt = 0; rt < 3; ++rt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) c0[i] += c1[i];
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) cg[rt][h][i] = 0.f;
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int rt = 0; rt < 3; ++rt) mma_bf16(cg[rt][t & 1], af[rt][t], bx[t][0], bx[t][1]);
+#pragma unroll
+                for (int rt = 0; rt < 3; ++rt) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) cg[rt][0][i] += cg[rt][1][i];
                     float r0, r1;
-                    fold_cols(c0, r0, r1);
-                    if ((lane & 3) == 0) { part[ke * 64 + mat * 32 + 16 * rt + fr_n] = r0; part[ke * 64 + mat * 32 + 16 * rt + fr_n + 8] = r1; }
+                    fold_cols(cg[rt][0], r0, r1);
+                    if ((lane & 3) == 0) { gpart[warp * 48 + 16 * rt + fr_n] = r0; gpart[warp * 48 + 16 * rt + fr_n + 8] = r1; }
                 }
                 Q3_FINE_T(8);
                 cta_sync();
@@ -986,7 +1003,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         const float r = rsqrtf(sum16(red) / (float)HIDDEN + EPS);
                         float g = 0.f, u = 0.f;
 #pragma unroll
-                        for (int e8 = 0; e8 < 8; ++e8) { g += part[e8 * 64 + tid]; u += part[e8 * 64 + 32 + tid]; }
+                        for (int w = 0; w < CW; ++w) { g += gpart[w * 48 + tid]; u += gpart[w * 48 + imax + tid]; }
                         g *= r; u *= r;
                         hv = (g / (1.f + expf(-g))) * u;
                     }
@@ -1207,6 +1224,7 @@ int persist_setup(q3_engine* e) {
     int grid = e->sm_count;
     if (e->cfg.grid_limit > 0 && e->cfg.grid_limit < grid) grid = e->cfg.grid_limit;
     if (grid < MIN_GRID) return Q3_OK;   // too few CTAs for the slot sizes: the layered path serves everything
+    static_assert(2 * ((INTER + MIN_GRID - 1) / MIN_GRID) <= 48, "the gate/up rows of a CTA must fit three 16-row tiles");
     const int smem = smem_bytes_for(grid);
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, e->device) != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "cudaGetDeviceProperties failed");
