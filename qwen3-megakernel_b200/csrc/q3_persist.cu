@@ -57,7 +57,6 @@ constexpr int LOCAL_ATTN_MAX = 64 * LOCAL_PASSES - 1;   // up to this many cache
 #endif
 constexpr int N_ACC = Q3_N_ACC;               // accumulators for the FFN delta (fewer same-address atomics each)
 constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
-constexpr int PART_STRIDE = 132;              // floats per published partial: [0] max, [1] sum, [4..132) output
 constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;   // patience of every device-side wait: 200 ms
 // fp32 tail of shared memory: 8 KB union | q_s[2][128] k_s v_s | o split [3][128] bf16 | hid split [3][32] bf16 | red lw misc | scores
 constexpr int FBUF_FLOATS = 2048 + 4 * 128 + 192 + 48 + 32 + 16 + 16 + 3 * SC_HALF;
@@ -81,9 +80,9 @@ struct PersistParams {
     float* dB;        // [2][N_ACC][1024] FFN delta of layer l in buffer l & 1
     unsigned long long* xq;   // [4096] q | k | v rows of the current layer, each a (tag << 32 | fp32 bits) word
     const unsigned* epoch;    // launches completed on this state; gives every (launch, layer) its own tag
-    float* part;      // [8 groups][18 CTAs][2 heads][PART_STRIDE] attention partials
+    unsigned long long* xp;   // [8 groups][2 heads][18 CTAs][XP_STRIDE] split-attention partials (max, sum, -, -, o[128]), tagged like xq
     const float* rope;
-    unsigned* sync;   // [0] grid barrier counter, [2] end-of-step ticket, [8..15] kv-group counters
+    unsigned* sync;   // [0] grid barrier counter, [2] end-of-step ticket
     uint32_t* status;
     float* pval;
     int* pidx;
@@ -94,13 +93,15 @@ struct PersistParams {
 struct PersistState {
     bf16_raw* packed;       // the layer matrices re-laid per CTA (see pack_weights_kernel)
     const void* src[7];     // the seven pointers `packed` was built from
-    float* X;               // X0 | X1 | dA[2] | dB[2][N_ACC] | xq[4096] (64-bit words) | epoch
+    float* X;               // X0 | X1 | dA[2] | dB[2][N_ACC] | xq[4096] (64-bit words) | epoch | xp
     int grid, smem;
 };
 
 // Which rows of which matrix CTA c of a grid of G owns, and how many elements its packed share of
 // one layer takes.  Used by the decode kernel and by the kernel that packs the weights.
-constexpr size_t X_FLOATS = (size_t)(4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM + 64;
+constexpr int XP_STRIDE = 132;                // 64-bit words per published partial
+constexpr size_t XP_WORDS = (size_t)KV_HEADS * 2 * GROUP_CTAS * XP_STRIDE;
+constexpr size_t X_FLOATS = (size_t)(4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM + 64 + 2 * XP_WORDS;
 struct Share {
     int q0, nq, qmax;       // rows [q0, q0 + nq) of [wq; wk; wv], slot rows qmax
     int i0, ni, imax;       // FFN rows [i0, i0 + ni) of gate, up and down^T, slot rows imax
@@ -445,8 +446,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     const unsigned tag_base = __ldcg(p.epoch) * 32u;
 
     unsigned* bar = p.sync;
-    unsigned* grp = p.sync + 8 + fg;
-    unsigned target = 0, gtarget = 0;
+    unsigned target = 0;
     const int quarter = lane >> 3, sub = lane & 7;
     // ldmatrix.x4 row addresses of a 16 x 16 A tile: lanes 0-7 rows 0-7, 8-15 rows 8-15 (k 0-7); 16-31 the same rows at k 8-15
     const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_k = (lane >> 4) * 8;
@@ -766,6 +766,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 Q3_FINE_T(24);
             } else {
             // ---- scores of this CTA's cached positions, both heads: a quarter-warp per position ----
+                Q3_FINE_T(16);
                 float tmax0 = -INFINITY, tmax1 = -INFINITY;
                 if (warp < ATT_WARPS) {
                     float qa[2][16];
@@ -805,7 +806,9 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     const float sn_ = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
                     if (lane == 0) misc[0] = sn_;
                 }
+                Q3_FINE_T(17);
                 cta_sync();
+                Q3_FINE_T(18);
                 float M0 = (lane < ATT_WARPS) ? red[lane] : -INFINITY, M1 = (lane < ATT_WARPS) ? red[8 + lane] : -INFINITY;
                 M0 = warp_max(M0); M1 = warp_max(M1);
 
@@ -854,45 +857,110 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         if (sub == 0) { lw[warp * 2] = l0; lw[warp * 2 + 1] = l1; }
                     }
                 }
+                Q3_FINE_T(19);
                 cta_sync();
-                // ---- publish the CTA's partial of both heads: (max, sum, unnormalised output) ----
+                Q3_FINE_T(21);
+                // ---- publish the CTA's partial of both heads: (max, sum, unnormalised output), every word tagged ----
                 if (tid < 256) {
                     const int hh = tid >> 7, d = tid & 127;
                     float o = 0.f, Ls = 0.f;
 #pragma unroll
                     for (int w = 0; w < ATT_WARPS; ++w) { o += om[(w * 2 + hh) * 128 + d]; Ls += lw[w * 2 + hh]; }
-                    float* dst = p.part + ((size_t)(fg * GROUP_CTAS + fj) * 2 + hh) * PART_STRIDE;
-                    if (d == 0) { __stcg(dst, hh ? M1 : M0); __stcg(dst + 1, Ls); }
-                    __stcg(dst + 4 + d, o);
+                    unsigned long long* dst = p.xp + (size_t)((fg * 2 + hh) * GROUP_CTAS + fj) * XP_STRIDE;
+                    const unsigned long long t64 = (unsigned long long)tag << 32;
+                    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(dst + 4 + d), "l"(t64 | __float_as_uint(o)) : "memory");
+                    __syncwarp();
+                    if (d == 127) {   // the (max, sum) pair goes last: it is what the readers poll
+                        asm volatile("st.relaxed.gpu.global.v2.b64 [%0], {%1, %2};" ::"l"(dst), "l"(t64 | __float_as_uint(hh ? M1 : M0)), "l"(t64 | __float_as_uint(Ls)) : "memory");
+                    }
+                }
+                Q3_TRACE(ev + 4);
+                Q3_FINE_T(23);
+
+                // ---- merge the 18 partials of this CTA's head with the new row.  Step 1: one warp polls the 18
+                //      (max, sum) pairs, which their writers store last, so that the polling stays light; step 2:
+                //      eight warps read the outputs, half h = tid / 128 merging partials [9 h, 9 h + 9) for dim
+                //      tid % 128, and go round again in the rare case that a word does not carry the tag yet.
+                constexpr int HALF = GROUP_CTAS / 2;
+                const unsigned long long* xsrc = p.xp + (size_t)((fg * 2 + fhh) * GROUP_CTAS) * XP_STRIDE;
+                float* pm_s = misc + 8;          // [18] maxima   (misc[8..25] runs into sc, which is dead by now)
+                float* pl_s = sc + 32;           // [18] sums
+                if (warp == 0) {
+                    unsigned long long wa = (unsigned long long)tag << 32, wb = wa;
+                    unsigned it = 0;
+                    unsigned long long t0 = 0;
+                    for (;;) {
+                        if (lane < GROUP_CTAS)
+                            asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(wa), "=l"(wb) : "l"(xsrc + (size_t)lane * XP_STRIDE) : "memory");
+                        const bool fresh = (unsigned)(wa >> 32) == tag && (unsigned)(wb >> 32) == tag;
+                        if (__all_sync(0xffffffffu, fresh)) break;
+                        if (*abort_flag) break;
+                        if ((++it & 255u) == 0) {
+                            const unsigned long long t = global_ns();
+                            if (t0 == 0) t0 = t;
+                            else if (t - t0 > WAIT_NS) {
+                                if (lane == 0) { report(p.status, ST_BARRIER_TIMEOUT, 400 + l, 0); *abort_flag = 1; }
+                                break;
+                            }
+                        }
+                    }
+                    if (lane < GROUP_CTAS) { pm_s[lane] = __uint_as_float((unsigned)wa); pl_s[lane] = __uint_as_float((unsigned)wb); }
                 }
                 cta_sync();
-                Q3_TRACE(ev + 4);
-                if (tid == 0) counter_arrive(grp);
-                gtarget += GROUP_CTAS;
-                counter_wait(grp, gtarget, abort_flag, p.status, 400 + l);
-                Q3_TRACE(ev + 5);
-
-                // ---- merge the 18 partials of this CTA's head with the new row ----
-                if (tid < HEAD_DIM) {
-                    const float* src = p.part + ((size_t)fg * GROUP_CTAS * 2 + fhh) * PART_STRIDE;
-                    const float s_new = misc[0];
-                    float mj[GROUP_CTAS], M = s_new;
+                Q3_FINE_T(22);
+                if (tid < 2 * HEAD_DIM) {
+                    const int half = tid >> 7, d = tid & 127;
+                    const unsigned long long* src = xsrc + (size_t)(half * HALF) * XP_STRIDE;
+                    float M, Ls, o;
+                    unsigned it = 0;
+                    unsigned long long t0 = 0;
+                    for (;;) {
+                        unsigned long long wc[HALF];
 #pragma unroll
-                    for (int j = 0; j < GROUP_CTAS; ++j) { mj[j] = __ldcg(src + (size_t)j * 2 * PART_STRIDE); M = fmaxf(M, mj[j]); }
-                    const float pn = __expf(s_new - M);
-                    float Ls = pn, o = pn * v_s[tid];
+                        for (int j = 0; j < HALF; ++j)
+                            asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(wc[j]) : "l"(src + (size_t)j * XP_STRIDE + 4 + d) : "memory");
+                        bool fresh = true;
+                        M = -INFINITY; Ls = 0.f; o = 0.f;
 #pragma unroll
-                    for (int j = 0; j < GROUP_CTAS; ++j) {
-                        const float wgt = __expf(mj[j] - M);    // 0 for a CTA that had no positions (max = -inf)
-                        Ls = fmaf(__ldcg(src + (size_t)j * 2 * PART_STRIDE + 1), wgt, Ls);
-                        o = fmaf(__ldcg(src + (size_t)j * 2 * PART_STRIDE + 4 + tid), wgt, o);
+                        for (int j = 0; j < HALF; ++j) {
+                            fresh = fresh && (unsigned)(wc[j] >> 32) == tag;
+                            const float mj = pm_s[half * HALF + j];   // -inf for a CTA that had no positions
+                            const float Mn = fmaxf(M, mj);
+                            const float keep = (M == -INFINITY) ? 0.f : __expf(M - Mn), wgt = (mj == -INFINITY) ? 0.f : __expf(mj - Mn);
+                            Ls = fmaf(pl_s[half * HALF + j], wgt, Ls * keep);
+                            o = fmaf(__uint_as_float((unsigned)wc[j]), wgt, o * keep);
+                            M = Mn;
+                        }
+                        if (__all_sync(0xffffffffu, fresh)) break;
+                        if (*abort_flag) break;
+                        if ((++it & 63u) == 0) {
+                            const unsigned long long t = global_ns();
+                            if (t0 == 0) t0 = t;
+                            else if (t - t0 > WAIT_NS) {
+                                if (lane == 0) { report(p.status, ST_BARRIER_TIMEOUT, 450 + l, 0); *abort_flag = 1; }
+                                break;
+                            }
+                        }
                     }
+                    Q3_FINE_T(24);
+                    q_s[half * 128 + d] = o;                       // the queries are dead by now
+                    if (d == 0) { misc[4 + 2 * half] = M; misc[5 + 2 * half] = Ls; }
+                }
+                cta_sync();
+                if (tid < HEAD_DIM) {
+                    const float s_new = misc[0], m0 = misc[4], m1 = misc[6];
+                    const float M = fmaxf(s_new, fmaxf(m0, m1));
+                    const float pn = __expf(s_new - M);
+                    const float w0 = (m0 == -INFINITY) ? 0.f : __expf(m0 - M), w1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - M);
+                    const float Ls = pn + misc[5] * w0 + misc[7] * w1;
+                    const float o = pn * v_s[tid] + q_s[tid] * w0 + q_s[128 + tid] * w1;
                     bf16_raw h, m, lo_;
                     split3(o / Ls, h, m, lo_);
                     reinterpret_cast<bf16_raw*>(osp)[tid] = h;
                     reinterpret_cast<bf16_raw*>(osp + 64)[tid] = m;
                     reinterpret_cast<bf16_raw*>(osp + 128)[tid] = lo_;
                 }
+                Q3_TRACE(ev + 5);
                 cta_sync();
 
             }
@@ -1141,7 +1209,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 p.sync[2] = 0;
                 *const_cast<unsigned*>(p.epoch) = tag_base / 32u + 1u;
             }
-            if (tid >= 8 && tid < 16) p.sync[tid] = 0;
         }
         Q3_TRACE(2 + EV_PER_LAYER * L);
     }
@@ -1236,8 +1303,6 @@ int persist_setup(q3_engine* e) {
     if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: occupancy query: %s", cudaGetErrorString(err));
     if (per_sm < 1 || per_sm * e->sm_count < grid || !prop.cooperativeLaunch)
         return engine_fail(e, Q3_ERR_NOT_RESIDENT, "persist: %d CTAs of %d threads and %d B shared memory cannot be co-resident", grid, PT, smem);
-    if ((size_t)KV_HEADS * GROUP_CTAS * 2 * PART_STRIDE > (size_t)e->cfg.max_batch * Q_HEADS * e->max_splits * ATTN_PART_STRIDE)
-        return engine_fail(e, Q3_ERR_INVALID, "persist: attention partial buffer too small");
     PersistState* s = new PersistState();
     s->packed = nullptr; s->X = nullptr; s->grid = grid; s->smem = smem;
     for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
@@ -1306,7 +1371,8 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
     p.X0 = s->X; p.X1 = s->X + HIDDEN; p.dA = s->X + 2 * HIDDEN; p.dB = s->X + 4 * HIDDEN;
     p.xq = reinterpret_cast<unsigned long long*>(s->X + (4 + 2 * N_ACC) * HIDDEN);
     p.epoch = reinterpret_cast<const unsigned*>(s->X + (4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM);
-    p.part = e->part; p.rope = e->rope; p.sync = e->sync; p.status = e->status; p.pval = e->pval; p.pidx = e->pidx;
+    p.xp = reinterpret_cast<unsigned long long*>(s->X + (4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM + 64);
+    p.rope = e->rope; p.sync = e->sync; p.status = e->status; p.pval = e->pval; p.pidx = e->pidx;
     p.trace = (e->trace && e->trace_words >= (int64_t)s->grid * (4 + EV_PER_LAYER * e->cfg.n_layers)) ? e->trace : nullptr;
     p.n_layers = e->cfg.n_layers; p.vocab = e->cfg.vocab; p.append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
     void* args[] = {&p};
