@@ -280,15 +280,25 @@ __device__ __forceinline__ void fold_cols(const float (&c)[4], float& row_lo, fl
 // pass i has been consumed.  The V rows are read dim-major instead (one warp per position, four dims
 // per lane), so P.V needs no shuffles: the first eight positions of every warp are fetched before the
 // barrier wait, the rest inside the loop.
+// Prefetch loads write straight into the registers that hold the row until it is used: the zero for a row past the
+// cache and the predicated load sit in one asm statement, so that no select or move consumes the loaded value (which
+// would park the warp until the row has arrived, at the place where it was only meant to be requested).
+__device__ __forceinline__ void ld_row16(uint4& d, const void* ptr, bool live) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+                 "@p ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+                 : "=&r"(d.x), "=&r"(d.y), "=&r"(d.z), "=&r"(d.w) : "l"(ptr), "r"((int)live));
+}
+__device__ __forceinline__ void ld_row8(uint32_t& a, uint32_t& b, const void* ptr, bool live) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %3, 0;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\t"
+                 "@p ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];\n\t}"
+                 : "=&r"(a), "=&r"(b) : "l"(ptr), "r"((int)live));
+}
 __device__ __forceinline__ void ring_load(uint4 (&buf)[2], int pass, int npl, int len, int att_slot, int sub, const bf16_raw* kl) {
     const int pos = pass * 64 + att_slot;
-    if (pass < npl && pos < len) {
-        const uint4* row = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
-        buf[0] = ld_stream(row + sub);
-        buf[1] = ld_stream(row + 8 + sub);
-    } else {
-        buf[0] = buf[1] = make_uint4(0, 0, 0, 0);
-    }
+    const bool live = pass < npl && pos < len;
+    const uint4* row = reinterpret_cast<const uint4*>(kl + (size_t)(live ? pos : 0) * KV_DIM);
+    ld_row16(buf[0], row + sub, live);
+    ld_row16(buf[1], row + 8 + sub, live);
 }
 __device__ __forceinline__ uint2 ld_stream8(const void* ptr) {
     uint2 v;
@@ -478,6 +488,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         // [0], [1] = K passes 0, 1 (a quarter-warp per position) and [2], [3] = V[warp + 16 i][4 lane .. 4 lane + 3]
         // for i < 8, two positions per uint4.
         uint4 ring[4][2];
+        uint4 ring3[2];   // local attention, third pass: K row of position 128 + slot
+        uint4 vext;       // ... and V[warp + 16 i][4 lane ..] for i = 8, 9 (i = 10, 11 are loaded inside the P.V loop)
         const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
         const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
         auto kv_prefetch = [&]() {
@@ -485,25 +497,38 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 if (local_attn) {
 #pragma unroll
                     for (int i = 0; i < 2; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl);
+                    ring_load(ring3, 2, npl, len, att_slot, sub, kl);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int pos = warp + CW * (LOCAL_V_PRE + i);
+                        const bool live = pos < len;
+                        const bf16_raw* vp = vl + (size_t)(live ? pos : 0) * KV_DIM + lane * 4;
+                        if (i) ld_row8(vext.z, vext.w, vp, live); else ld_row8(vext.x, vext.y, vp, live);
+                    }
 #pragma unroll
                     for (int i = 0; i < LOCAL_V_PRE; ++i) {
                         const int pos = warp + CW * i;
-                        const uint2 v = (pos < len) ? ld_stream8(vl + (size_t)pos * KV_DIM + lane * 4) : make_uint2(0, 0);
+                        const bool live = pos < len;
+                        const bf16_raw* vp = vl + (size_t)(live ? pos : 0) * KV_DIM + lane * 4;
                         uint4& dst = ring[2 + (i >> 2)][(i >> 1) & 1];
-                        if (i & 1) { dst.z = v.x; dst.w = v.y; } else { dst.x = v.x; dst.y = v.y; }
+                        if (i & 1) ld_row8(dst.z, dst.w, vp, live); else ld_row8(dst.x, dst.y, vp, live);
                     }
                 } else if (warp < ATT_WARPS) {
 #pragma unroll
-                    for (int ps = 0; ps < 2; ++ps) {
+                    for (int ps = 0; ps < 2; ++ps) {   // K: a quarter-warp per position
                         const int pos = cp0 + ps * 32 + att_slot;
-                        if (pos < cp1) {
-                            const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)pos * KV_DIM);
-                            const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
-                            ring[ps][0] = ld_stream(kr + sub); ring[ps][1] = ld_stream(kr + 8 + sub);
-                            ring[2 + ps][0] = ld_stream(vr + sub); ring[2 + ps][1] = ld_stream(vr + 8 + sub);
-                        } else {
-                            ring[ps][0] = ring[ps][1] = ring[2 + ps][0] = ring[2 + ps][1] = make_uint4(0, 0, 0, 0);
-                        }
+                        const bool live = pos < cp1;
+                        const uint4* kr = reinterpret_cast<const uint4*>(kl + (size_t)(live ? pos : 0) * KV_DIM);
+                        ld_row16(ring[ps][0], kr + sub, live);
+                        ld_row16(ring[ps][1], kr + 8 + sub, live);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {      // V: a warp per position, four dims per lane
+                        const int pos = cp0 + warp + ATT_WARPS * i;
+                        const bool live = pos < cp1;
+                        const bf16_raw* vp = vl + (size_t)(live ? pos : 0) * KV_DIM + lane * 4;
+                        uint4& dst = ring[2 + (i >> 2)][(i >> 1) & 1];
+                        if (i & 1) ld_row8(dst.z, dst.w, vp, live); else ld_row8(dst.x, dst.y, vp, live);
                     }
                 }
             }
@@ -518,7 +543,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             } else {
                 load_x_ffn(p.dB + (size_t)((l - 1) & 1) * N_ACC * HIDDEN, x0, x1);
             }
-            if (warp >= 8 && warp < 12) kv_prefetch();   // the warps that will poll the q/k/v exchange fetch now, the others while they wait for it
             fetch_slot(3, l);   // down rows of this layer: landed before the q/k/v exchange starts polling
             if (c == 0) __stcg(reinterpret_cast<float2*>(p.X1 + 2 * tid), make_float2(x0, x1));
             if (c == 1 && l + 1 < L) __stcg(reinterpret_cast<float2*>(p.dA + (size_t)((l + 1) & 1) * HIDDEN + 2 * tid), make_float2(0.f, 0.f));
@@ -536,6 +560,9 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             const float ss = warp_sum(x0 * x0 + x1 * x1);
             if (lane == 0) red[warp] = ss;
             Q3_FINE_T(29);
+            // the warps that will poll the q/k/v exchange request their K/V rows now (x is staged: nothing queues behind
+            // these loads), the others while they wait for the exchange
+            if (warp >= 8 && warp < 12) kv_prefetch();
             cta_sync();
             Q3_TRACE(ev + 0);
             Q3_FINE_T(0);
@@ -693,19 +720,9 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     s0 += __shfl_xor_sync(0xffffffffu, s0, 4);
                     if (pos < len) { tmax = fmaxf(tmax, s0); if (sub == 0) sc[pos] = s0; }
                 };
-                if (npl > 2) {   // passes 2..5 were not fetched ahead: issue them all, then score in order
-                    uint4 kx[LOCAL_PASSES - 2][2];
-#pragma unroll
-                    for (int i = 0; i < LOCAL_PASSES - 2; ++i) ring_load(kx[i], 2 + i, npl, len, att_slot, sub, kl);
-                    score_pass(ring[0][0], ring[0][1], 0);
-                    score_pass(ring[1][0], ring[1][1], 1);
-#pragma unroll
-                    for (int i = 0; i < LOCAL_PASSES - 2; ++i)
-                        if (2 + i < npl) score_pass(kx[i][0], kx[i][1], 2 + i);
-                } else {
-                    score_pass(ring[0][0], ring[0][1], 0);
-                    score_pass(ring[1][0], ring[1][1], 1);   // all zero (and masked) when there is one pass
-                }
+                score_pass(ring[0][0], ring[0][1], 0);
+                score_pass(ring[1][0], ring[1][1], 1);   // all zero (and masked) when there is one pass
+                if (npl > 2) score_pass(ring3[0], ring3[1], 2);
                 if (warp == 12) {   // the new row's score: q . k_new in fp32, unrounded
                     const float4 a = *reinterpret_cast<const float4*>(q_s + fhh * 128 + lane * 4);
                     const float4 b = *reinterpret_cast<const float4*>(k_s + lane * 4);
@@ -735,8 +752,17 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     acc[i & 1][0] = fmaf(pr, bf_lo(vx), acc[i & 1][0]); acc[i & 1][1] = fmaf(pr, bf_hi(vx), acc[i & 1][1]);
                     acc[i & 1][2] = fmaf(pr, bf_lo(vy), acc[i & 1][2]); acc[i & 1][3] = fmaf(pr, bf_hi(vy), acc[i & 1][3]);
                 }
-#pragma unroll 4
-                for (int pos = warp + CW * LOCAL_V_PRE; pos < len; pos += CW) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int pos = warp + CW * (LOCAL_V_PRE + i);
+                    const float pr = (pos < len) ? __expf(sc[min(pos, 3 * SC_HALF - 1)] - M) : 0.f;
+                    lsum += pr;
+                    const uint32_t vx = i ? vext.z : vext.x, vy = i ? vext.w : vext.y;
+                    acc[i][0] = fmaf(pr, bf_lo(vx), acc[i][0]); acc[i][1] = fmaf(pr, bf_hi(vx), acc[i][1]);
+                    acc[i][2] = fmaf(pr, bf_lo(vy), acc[i][2]); acc[i][3] = fmaf(pr, bf_hi(vy), acc[i][3]);
+                }
+#pragma unroll 2
+                for (int pos = warp + CW * (LOCAL_V_PRE + 2); pos < len; pos += CW) {
                     const uint2 v = ld_stream8(vl + (size_t)pos * KV_DIM + lane * 4);
                     const float pr = __expf(sc[pos] - M);
                     lsum += pr;
@@ -812,50 +838,34 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 float M0 = (lane < ATT_WARPS) ? red[lane] : -INFINITY, M1 = (lane < ATT_WARPS) ? red[8 + lane] : -INFINITY;
                 M0 = warp_max(M0); M1 = warp_max(M1);
 
-                // ---- probabilities and P.V against the CTA-wide maxima: the partial sums just add ----
+                // ---- probabilities and P.V against the CTA-wide maxima: the partial sums just add.  A warp per position
+                //      and four dims per lane: every lane forms the same two probabilities, nothing crosses lanes ----
                 if (warp < ATT_WARPS) {
-                    float l0 = 0.f, l1 = 0.f, acc[2][16];
+                    float l0 = 0.f, l1 = 0.f, acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) { acc[0][i] = 0.f; acc[1][i] = 0.f; }
-                    for (int ps = 0; ps < npass; ++ps) {
-                        const int idx = ps * 32 + att_slot, pos = cp0 + idx;
-                        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
-                        if (ps == 0) { v0 = ring[2][0]; v1 = ring[2][1]; }
-                        else if (ps == 1) { v0 = ring[3][0]; v1 = ring[3][1]; }
-                        else if (pos < cp1) {
-                            const uint4* vr = reinterpret_cast<const uint4*>(vl + (size_t)pos * KV_DIM);
-                            v0 = ld_stream(vr + sub); v1 = ld_stream(vr + 8 + sub);
-                        }
-                        if (pos < cp1) {
-                            const float p0 = __expf(sc[idx] - M0), p1 = __expf(sc[SC_HALF + idx] - M1);
-                            l0 += p0; l1 += p1;
-                            float vf[16];
-                            unpack8f(v0, vf); unpack8f(v1, vf + 8);
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) { acc[0][i] = fmaf(p0, vf[i], acc[0][i]); acc[1][i] = fmaf(p1, vf[i], acc[1][i]); }
-                        }
+                    for (int i = 0; i < 8; ++i) {
+                        const int idx = warp + ATT_WARPS * i;
+                        const bool live = cp0 + idx < cp1;
+                        const float p0 = live ? __expf(sc[idx] - M0) : 0.f, p1 = live ? __expf(sc[SC_HALF + idx] - M1) : 0.f;
+                        l0 += p0; l1 += p1;
+                        const uint4& src = ring[2 + (i >> 2)][(i >> 1) & 1];
+                        const uint32_t vx = (i & 1) ? src.z : src.x, vy = (i & 1) ? src.w : src.y;
+                        const float f0 = bf_lo(vx), f1 = bf_hi(vx), f2 = bf_lo(vy), f3 = bf_hi(vy);
+                        acc[0][0] = fmaf(p0, f0, acc[0][0]); acc[0][1] = fmaf(p0, f1, acc[0][1]); acc[0][2] = fmaf(p0, f2, acc[0][2]); acc[0][3] = fmaf(p0, f3, acc[0][3]);
+                        acc[1][0] = fmaf(p1, f0, acc[1][0]); acc[1][1] = fmaf(p1, f1, acc[1][1]); acc[1][2] = fmaf(p1, f2, acc[1][2]); acc[1][3] = fmaf(p1, f3, acc[1][3]);
                     }
-                    // fold the four quarter-warp partials of the warp (lanes with equal `sub` hold the same dims)
-#pragma unroll
-                    for (int off = 8; off <= 16; off <<= 1) {
-                        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
-                        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            acc[0][i] += __shfl_xor_sync(0xffffffffu, acc[0][i], off);
-                            acc[1][i] += __shfl_xor_sync(0xffffffffu, acc[1][i], off);
-                        }
+#pragma unroll 2
+                    for (int idx = warp + ATT_WARPS * 8; cp0 + idx < cp1; idx += ATT_WARPS) {
+                        const uint2 v = ld_stream8(vl + (size_t)(cp0 + idx) * KV_DIM + lane * 4);
+                        const float p0 = __expf(sc[idx] - M0), p1 = __expf(sc[SC_HALF + idx] - M1);
+                        l0 += p0; l1 += p1;
+                        const float f0 = bf_lo(v.x), f1 = bf_hi(v.x), f2 = bf_lo(v.y), f3 = bf_hi(v.y);
+                        acc[0][0] = fmaf(p0, f0, acc[0][0]); acc[0][1] = fmaf(p0, f1, acc[0][1]); acc[0][2] = fmaf(p0, f2, acc[0][2]); acc[0][3] = fmaf(p0, f3, acc[0][3]);
+                        acc[1][0] = fmaf(p1, f0, acc[1][0]); acc[1][1] = fmaf(p1, f1, acc[1][1]); acc[1][2] = fmaf(p1, f2, acc[1][2]); acc[1][3] = fmaf(p1, f3, acc[1][3]);
                     }
-                    if (quarter == 0) {
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                om[(warp * 2 + hh) * 128 + sub * 8 + i] = acc[hh][i];
-                                om[(warp * 2 + hh) * 128 + 64 + sub * 8 + i] = acc[hh][8 + i];
-                            }
-                        if (sub == 0) { lw[warp * 2] = l0; lw[warp * 2 + 1] = l1; }
-                    }
+                    *reinterpret_cast<float4*>(om + (warp * 2) * 128 + lane * 4) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+                    *reinterpret_cast<float4*>(om + (warp * 2 + 1) * 128 + lane * 4) = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
+                    if (lane == 0) { lw[warp * 2] = l0; lw[warp * 2 + 1] = l1; }
                 }
                 Q3_FINE_T(19);
                 cta_sync();
@@ -885,7 +895,16 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 const unsigned long long* xsrc = p.xp + (size_t)((fg * 2 + fhh) * GROUP_CTAS) * XP_STRIDE;
                 float* pm_s = misc + 8;          // [18] maxima   (misc[8..25] runs into sc, which is dead by now)
                 float* pl_s = sc + 32;           // [18] sums
-                if (warp == 0) {
+                unsigned long long wc[HALF];   // warps 0..7: this thread's nine output words
+                const int mhalf = tid >> 7, md = tid & 127;
+                const unsigned long long* msrc = xsrc + (size_t)(mhalf * HALF) * XP_STRIDE + 4 + md;
+                auto load_outputs = [&]() {
+#pragma unroll
+                    for (int j = 0; j < HALF; ++j)
+                        asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(wc[j]) : "l"(msrc + (size_t)j * XP_STRIDE) : "memory");
+                };
+                if (warp < 8) load_outputs();   // speculative: usually fresh by the time the pairs are, which saves a round trip
+                if (warp == 8) {
                     unsigned long long wa = (unsigned long long)tag << 32, wb = wa;
                     unsigned it = 0;
                     unsigned long long t0 = 0;
@@ -909,16 +928,11 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 cta_sync();
                 Q3_FINE_T(22);
                 if (tid < 2 * HEAD_DIM) {
-                    const int half = tid >> 7, d = tid & 127;
-                    const unsigned long long* src = xsrc + (size_t)(half * HALF) * XP_STRIDE;
+                    const int half = mhalf, d = md;
                     float M, Ls, o;
                     unsigned it = 0;
                     unsigned long long t0 = 0;
                     for (;;) {
-                        unsigned long long wc[HALF];
-#pragma unroll
-                        for (int j = 0; j < HALF; ++j)
-                            asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(wc[j]) : "l"(src + (size_t)j * XP_STRIDE + 4 + d) : "memory");
                         bool fresh = true;
                         M = -INFINITY; Ls = 0.f; o = 0.f;
 #pragma unroll
@@ -941,6 +955,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                                 break;
                             }
                         }
+                        load_outputs();
                     }
                     Q3_FINE_T(24);
                     q_s[half * 128 + d] = o;                       // the queries are dead by now

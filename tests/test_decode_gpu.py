@@ -76,7 +76,7 @@ def test_small_model_step_vs_oracle_and_golden(oracle, small, path):
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("ctx", [0, 1, 7, 17, 19, 64, 129, 515, 577, 1500, 2286, 2400])
+@pytest.mark.parametrize("ctx", [0, 1, 7, 17, 19, 64, 128, 129, 191, 240, 241, 300, 324, 325, 515, 577, 1500, 2286, 2400])
 def test_any_position(oracle, path, ctx):
     shp = oracle.Shape(layers=2, vocab=2048)
     inp = oracle.synthetic(100 + ctx, shp, context=max(ctx, 1))
