@@ -212,6 +212,7 @@ extern "C" int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n)
     // leave the engine reusable: clear the status and the barrier words
     CU(e, cudaMemset(e->status, 0, Q3_STATUS_WORDS * 4));
     CU(e, cudaMemset(e->sync, 0, Q3_SYNC_WORDS * 4));
+    if (persist_recover(e) != Q3_OK) return Q3_ERR_CUDA;
     return fail(e, Q3_ERR_DEVICE_WAIT, "device status: code %u at site %u, CTA %u, value %u", h[0], h[1], h[2], h[3]);
 }
 

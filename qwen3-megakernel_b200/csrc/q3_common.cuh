@@ -87,7 +87,7 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 
 // ---- device status words ----------------------------------------------------------------------
 // [0] error code (0 = fine), [1] phase / site id, [2] CTA index, [3] observed value.
-enum : uint32_t { ST_OK = 0, ST_BARRIER_TIMEOUT = 1, ST_MBAR_TIMEOUT = 2, ST_BAD_TOKEN = 3, ST_PEER_TIMEOUT = 4 };
+enum : uint32_t { ST_OK = 0, ST_BARRIER_TIMEOUT = 1, ST_MBAR_TIMEOUT = 2, ST_BAD_TOKEN = 3, ST_PEER_TIMEOUT = 4, ST_BAD_LEN = 5 };
 
 __device__ __forceinline__ void report(uint32_t* status, uint32_t code, uint32_t site, uint32_t value) {
     if (atomicCAS(status, 0u, code) == 0u) {

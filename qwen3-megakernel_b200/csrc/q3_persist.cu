@@ -50,8 +50,8 @@ constexpr int WROW = 1032;                    // elements between weight rows in
                                               // the eight row addresses of an ldmatrix fall into different banks
 constexpr int WOROW = 136;                    // the same for the 128-column Wo slice rows
 constexpr int ATT_WARPS = 8;                  // split attention: warps that attend positions (32 positions per pass)
-constexpr int LOCAL_PASSES = 3;               // local attention: passes of 64 positions a CTA runs on its own (measured: splitting wins beyond ~200 positions)
-constexpr int LOCAL_ATTN_MAX = 64 * LOCAL_PASSES - 1;   // up to this many cached positions every CTA attends its whole head
+// Local attention (every CTA attends its whole head over all cached positions) serves up to 191 positions; measured,
+// splitting the positions over the 18 CTAs of a kv group wins beyond about 200.
 #ifndef Q3_N_ACC
 #define Q3_N_ACC 2
 #endif
@@ -308,11 +308,25 @@ __device__ __forceinline__ uint2 ld_stream8(const void* ptr) {
 constexpr int LOCAL_V_PRE = 8;   // V positions per warp fetched ahead of the barrier wait
 
 // ====================================================================================================
+// MODE picks the attention scheme at compile time, so that each variant carries only its own code and registers:
+//   0  local attention, up to 128 cached positions (everything prefetched into 32 registers)
+//   1  local attention, up to 191 cached positions (a third K pass and four more V rows in 16 more registers)
+//   2  local attention, up to 255 cached positions (a fourth K pass and another four V rows)
+//   3  split attention, up to PERSIST_MAX_LEN cached positions
+// (measured per step at 192 / 255 / 319 / 383 positions: local 392 / 417 / 475 / 511 us, split 450 us throughout).
+// The host picks the variant from its upper bound of the length; a cache longer than the variant serves is reported.
+constexpr int N_MODES = 4;
+__host__ __device__ constexpr int mode_max_len(int mode) { return mode == 0 ? 128 : mode < N_MODES - 1 ? 127 + 64 * mode : PERSIST_MAX_LEN; }
+template <int MODE>
 __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int c = blockIdx.x, G = gridDim.x;
     const int L = p.n_layers;
+    if (p.seq_len[0] > mode_max_len(MODE) || p.seq_len[0] < 0) {   // the same for every CTA: nothing has been started yet
+        if (tid == 0) report(p.status, ST_BAD_LEN, (uint32_t)MODE, (uint32_t)p.seq_len[0]);
+        return;
+    }
 
     // ---- static ownership ----
     const Share sh = share_of(c, G);
@@ -469,7 +483,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     const int att_slot = warp * 4 + quarter;                  // < 32 for the attending warps
     // Short caches: every CTA recomputes the attention of its own head over all positions (no exchange between
     // CTAs; the K/V rows come from L2).  Longer caches: the 18 CTAs of a kv group split the positions.
-    const bool local_attn = len <= LOCAL_ATTN_MAX;
+    constexpr bool local_attn = MODE < N_MODES - 1;
+    constexpr int XPASS = local_attn ? MODE : 0;   // K passes (and groups of four V rows) beyond the first two
     const int npl = (len + 63) >> 6;                          // local attention: passes of 64 positions (16 warps x 4 quarter-warps)
 
     // gains of the next GEMV phase, fetched ahead of the barrier wait
@@ -488,8 +503,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         // [0], [1] = K passes 0, 1 (a quarter-warp per position) and [2], [3] = V[warp + 16 i][4 lane .. 4 lane + 3]
         // for i < 8, two positions per uint4.
         uint4 ring[4][2];
-        uint4 ring3[2];   // local attention, third pass: K row of position 128 + slot
-        uint4 vext;       // ... and V[warp + 16 i][4 lane ..] for i = 8, 9 (i = 10, 11 are loaded inside the P.V loop)
+        uint4 ring3[XPASS > 0 ? XPASS : 1][2];    // passes 2..: K row of position 64 pass + slot
+        uint4 vext[XPASS > 0 ? 2 * XPASS : 1];    // ... and V[warp + 16 i][4 lane ..] for i = 8 .., two rows per uint4
         const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
         const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
         auto kv_prefetch = [&]() {
@@ -497,13 +512,17 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 if (local_attn) {
 #pragma unroll
                     for (int i = 0; i < 2; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl);
-                    ring_load(ring3, 2, npl, len, att_slot, sub, kl);
+                    if constexpr (XPASS > 0) {
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const int pos = warp + CW * (LOCAL_V_PRE + i);
-                        const bool live = pos < len;
-                        const bf16_raw* vp = vl + (size_t)(live ? pos : 0) * KV_DIM + lane * 4;
-                        if (i) ld_row8(vext.z, vext.w, vp, live); else ld_row8(vext.x, vext.y, vp, live);
+                        for (int x = 0; x < XPASS; ++x) ring_load(ring3[x], 2 + x, npl, len, att_slot, sub, kl);
+#pragma unroll
+                        for (int i = 0; i < 4 * XPASS; ++i) {
+                            const int pos = warp + CW * (LOCAL_V_PRE + i);
+                            const bool live = pos < len;
+                            const bf16_raw* vp = vl + (size_t)(live ? pos : 0) * KV_DIM + lane * 4;
+                            uint4& dst = vext[i >> 1];
+                            if (i & 1) ld_row8(dst.z, dst.w, vp, live); else ld_row8(dst.x, dst.y, vp, live);
+                        }
                     }
 #pragma unroll
                     for (int i = 0; i < LOCAL_V_PRE; ++i) {
@@ -722,7 +741,11 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 };
                 score_pass(ring[0][0], ring[0][1], 0);
                 score_pass(ring[1][0], ring[1][1], 1);   // all zero (and masked) when there is one pass
-                if (npl > 2) score_pass(ring3[0], ring3[1], 2);
+                if constexpr (XPASS > 0) {
+#pragma unroll
+                    for (int x = 0; x < XPASS; ++x)
+                        if (npl > 2 + x) score_pass(ring3[x][0], ring3[x][1], 2 + x);
+                }
                 if (warp == 12) {   // the new row's score: q . k_new in fp32, unrounded
                     const float4 a = *reinterpret_cast<const float4*>(q_s + fhh * 128 + lane * 4);
                     const float4 b = *reinterpret_cast<const float4*>(k_s + lane * 4);
@@ -752,22 +775,17 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     acc[i & 1][0] = fmaf(pr, bf_lo(vx), acc[i & 1][0]); acc[i & 1][1] = fmaf(pr, bf_hi(vx), acc[i & 1][1]);
                     acc[i & 1][2] = fmaf(pr, bf_lo(vy), acc[i & 1][2]); acc[i & 1][3] = fmaf(pr, bf_hi(vy), acc[i & 1][3]);
                 }
+                if constexpr (XPASS > 0) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int pos = warp + CW * (LOCAL_V_PRE + i);
-                    const float pr = (pos < len) ? __expf(sc[min(pos, 3 * SC_HALF - 1)] - M) : 0.f;
-                    lsum += pr;
-                    const uint32_t vx = i ? vext.z : vext.x, vy = i ? vext.w : vext.y;
-                    acc[i][0] = fmaf(pr, bf_lo(vx), acc[i][0]); acc[i][1] = fmaf(pr, bf_hi(vx), acc[i][1]);
-                    acc[i][2] = fmaf(pr, bf_lo(vy), acc[i][2]); acc[i][3] = fmaf(pr, bf_hi(vy), acc[i][3]);
-                }
-#pragma unroll 2
-                for (int pos = warp + CW * (LOCAL_V_PRE + 2); pos < len; pos += CW) {
-                    const uint2 v = ld_stream8(vl + (size_t)pos * KV_DIM + lane * 4);
-                    const float pr = __expf(sc[pos] - M);
-                    lsum += pr;
-                    acc[0][0] = fmaf(pr, bf_lo(v.x), acc[0][0]); acc[0][1] = fmaf(pr, bf_hi(v.x), acc[0][1]);
-                    acc[0][2] = fmaf(pr, bf_lo(v.y), acc[0][2]); acc[0][3] = fmaf(pr, bf_hi(v.y), acc[0][3]);
+                    for (int i = 0; i < 4 * XPASS; ++i) {
+                        const int pos = warp + CW * (LOCAL_V_PRE + i);
+                        const float pr = (pos < len) ? __expf(sc[min(pos, 3 * SC_HALF - 1)] - M) : 0.f;
+                        lsum += pr;
+                        const uint4& src = vext[i >> 1];
+                        const uint32_t vx = (i & 1) ? src.z : src.x, vy = (i & 1) ? src.w : src.y;
+                        acc[i & 1][0] = fmaf(pr, bf_lo(vx), acc[i & 1][0]); acc[i & 1][1] = fmaf(pr, bf_hi(vx), acc[i & 1][1]);
+                        acc[i & 1][2] = fmaf(pr, bf_lo(vy), acc[i & 1][2]); acc[i & 1][3] = fmaf(pr, bf_hi(vy), acc[i & 1][3]);
+                    }
                 }
                 Q3_FINE_T(21);
                 *reinterpret_cast<float4*>(om + warp * 128 + lane * 4) =
@@ -1301,6 +1319,15 @@ static int smem_bytes_for(int grid) {
     return (qmax + 3 * imax) * WROW * 2 + WO_ROWS_MAX * WOROW * 2 + TAIL_BYTES;
 }
 
+static const void* persist_kernel(int mode) {
+    switch (mode) {
+        case 0: return reinterpret_cast<const void*>(q3_persist_decode<0>);
+        case 1: return reinterpret_cast<const void*>(q3_persist_decode<1>);
+        case 2: return reinterpret_cast<const void*>(q3_persist_decode<2>);
+        default: return reinterpret_cast<const void*>(q3_persist_decode<3>);
+    }
+}
+
 int persist_setup(q3_engine* e) {
     e->p_grid = 0; e->p_threads = PT; e->p_smem = 0; e->p_state = nullptr;
     int grid = e->sm_count;
@@ -1311,13 +1338,15 @@ int persist_setup(q3_engine* e) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, e->device) != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "cudaGetDeviceProperties failed");
     if ((size_t)smem > prop.sharedMemPerBlockOptin) return Q3_OK;
-    cudaError_t err = cudaFuncSetAttribute(q3_persist_decode, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: set smem attribute (%d B): %s", smem, cudaGetErrorString(err));
-    int per_sm = 0;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, q3_persist_decode, PT, smem);
-    if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: occupancy query: %s", cudaGetErrorString(err));
-    if (per_sm < 1 || per_sm * e->sm_count < grid || !prop.cooperativeLaunch)
-        return engine_fail(e, Q3_ERR_NOT_RESIDENT, "persist: %d CTAs of %d threads and %d B shared memory cannot be co-resident", grid, PT, smem);
+    for (int mode = 0; mode < N_MODES; ++mode) {
+        cudaError_t err = cudaFuncSetAttribute(persist_kernel(mode), cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: set smem attribute (%d B): %s", smem, cudaGetErrorString(err));
+        int per_sm = 0;
+        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, persist_kernel(mode), PT, smem);
+        if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: occupancy query: %s", cudaGetErrorString(err));
+        if (per_sm < 1 || per_sm * e->sm_count < grid || !prop.cooperativeLaunch)
+            return engine_fail(e, Q3_ERR_NOT_RESIDENT, "persist: %d CTAs of %d threads and %d B shared memory cannot be co-resident", grid, PT, smem);
+    }
     PersistState* s = new PersistState();
     s->packed = nullptr; s->X = nullptr; s->grid = grid; s->smem = smem;
     for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
@@ -1367,6 +1396,14 @@ int persist_weights_changed(q3_engine* e) {
     return Q3_OK;
 }
 
+// A step that gave up half-way leaves partial sums in the delta accumulators and stale tags behind: start over.
+int persist_recover(q3_engine* e) {
+    PersistState* s = static_cast<PersistState*>(e->p_state);
+    if (!s) return Q3_OK;
+    if (cudaMemset(s->X, 0, X_FLOATS * sizeof(float)) != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: clearing the scratch state failed");
+    return Q3_OK;
+}
+
 void persist_invalidate_weights(q3_engine* e) {
     PersistState* s = static_cast<PersistState*>(e->p_state);
     if (s) for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
@@ -1391,7 +1428,9 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
     p.trace = (e->trace && e->trace_words >= (int64_t)s->grid * (4 + EV_PER_LAYER * e->cfg.n_layers)) ? e->trace : nullptr;
     p.n_layers = e->cfg.n_layers; p.vocab = e->cfg.vocab; p.append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
     void* args[] = {&p};
-    cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(q3_persist_decode), dim3(s->grid), dim3(PT), args, (size_t)s->smem, st);
+    int mode = 0;
+    while (mode + 1 < N_MODES && a->max_len > mode_max_len(mode)) ++mode;
+    cudaError_t err = cudaLaunchCooperativeKernel(persist_kernel(mode), dim3(s->grid), dim3(PT), args, (size_t)s->smem, st);
     ++e->launches;
     if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: cooperative launch failed: %s", cudaGetErrorString(err));
     return Q3_OK;
