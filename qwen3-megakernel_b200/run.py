@@ -2,7 +2,7 @@
 """Command line for the B200 Qwen3-0.6B decode engine (same sub-commands as the reference's run.py:1-158).
 
   run.py check [--weights hf|synthetic] [--seed N] [--context N]
-  run.py bench [--weights hf|synthetic] [--iters N] [--context N] [--grow]
+  run.py bench [--weights hf|synthetic] [--iters N] [--context N] [--grow] [--chains N]
   run.py trace [--context N]            per-phase timing of the persistent kernel (device time stamps)
   run.py demo --prompt "..."
 
@@ -101,7 +101,7 @@ def cmd_bench(args) -> int:
     iso = bench_mod.isolated(mk, inputs, iters=args.iters)
     print(f"isolated: median {iso['event_us_median']:.1f} us (events), {iso['wall_us_median']:.1f} us (wall); "
           f"event min {iso['event_us_min']:.1f} max {iso['event_us_max']:.1f}; iters {iso['iters']}")
-    st = bench_mod.steady(mk, inputs, grow=args.grow)
+    st = bench_mod.steady(mk, inputs, grow=args.grow, reps=args.chains)
     print(f"steady:   median {st['us_per_step_median']:.1f} us/step; min {st['us_per_step_min']:.1f} max {st['us_per_step_max']:.1f}; "
           f"{st['reps']} chains of {st['steps']} steps{' (cache grows)' if args.grow else ''}")
     mk.status()
@@ -176,6 +176,7 @@ def main(argv=None) -> int:
         if name == "bench":
             p.add_argument("--iters", type=int, default=200)
             p.add_argument("--grow", action="store_true")
+            p.add_argument("--chains", type=int, default=20, help="chains of 50 steps in the steady measurement")
     p = sub.add_parser("demo")
     p.add_argument("--prompt", default=DEFAULT_PROMPT)
     args = ap.parse_args(argv)
