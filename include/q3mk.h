@@ -49,7 +49,7 @@ typedef struct q3_config {
     int32_t max_batch;      /* largest q3_decode_args.batch the scratch is sized for (>= 1)      */
     int32_t max_tokens;     /* largest q3_prefill_args.n_tokens the scratch is sized for (0: no prefill) */
     int32_t grid_limit;     /* 0 = one CTA per SM; otherwise cap the persistent grid (tests)     */
-    int32_t pace_cycles;    /* 0 = default; nanoseconds the persistent kernel's producer warp sleeps between two <= 2 KB weight copies */
+    int32_t pace_cycles;    /* reserved, must be 0 (an earlier weight-streaming scheme was paced by it; the field keeps the struct layout) */
 } q3_config;
 
 /* The 13 weight tensors, device pointers to bf16.  Replaces slots 1..13 of the reference's
