@@ -262,9 +262,15 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         // qkv = rms(x, ln1) @ [wq; wk; wv]^T
         if (tc) {
             LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln1) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st));
-            LAUNCH(gemm(bf(w.wq) + (size_t)l * Q_DIM * HIDDEN, Q_DIM, HIDDEN, e->qkv, QKV_DIM, nullptr, 0));
-            LAUNCH(gemm(bf(w.wk) + (size_t)l * KV_DIM * HIDDEN, KV_DIM, HIDDEN, e->qkv + Q_DIM, QKV_DIM, nullptr, 0));
-            LAUNCH(gemm(bf(w.wv) + (size_t)l * KV_DIM * HIDDEN, KV_DIM, HIDDEN, e->qkv + Q_DIM + KV_DIM, QKV_DIM, nullptr, 0));
+            {   // the three projections in one launch: 32 weight tiles instead of 16 + 8 + 8
+                GemmTcGroupCall c{};
+                c.n_groups = 3;
+                c.w[0] = bf(w.wq) + (size_t)l * Q_DIM * HIDDEN; c.n_rows[0] = Q_DIM; c.out[0] = e->qkv; c.ldo[0] = QKV_DIM;
+                c.w[1] = bf(w.wk) + (size_t)l * KV_DIM * HIDDEN; c.n_rows[1] = KV_DIM; c.out[1] = e->qkv + Q_DIM; c.ldo[1] = QKV_DIM;
+                c.w[2] = bf(w.wv) + (size_t)l * KV_DIM * HIDDEN; c.n_rows[2] = KV_DIM; c.out[2] = e->qkv + Q_DIM + KV_DIM; c.ldo[2] = QKV_DIM;
+                c.x_planes = planes; c.n_tok = B; c.K = HIDDEN; c.nsplit = tc_planes; c.plane_rows = prow; c.status = e->status;
+                LAUNCH(launch_gemm_tc_group(c, st));
+            }
         } else {
             g.seg[0] = {bf(w.wq) + (size_t)l * Q_DIM * HIDDEN, Q_DIM};
             g.seg[1] = {bf(w.wk) + (size_t)l * KV_DIM * HIDDEN, KV_DIM};
@@ -301,8 +307,14 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
             LAUNCH(gemm(bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN, Q_DIM, e->x, HIDDEN, e->x, HIDDEN));
             // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
             LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st));
-            LAUNCH(gemm(bf(w.wg) + (size_t)l * INTER * HIDDEN, INTER, HIDDEN, e->gate, INTER, nullptr, 0));
-            LAUNCH(gemm(bf(w.wu) + (size_t)l * INTER * HIDDEN, INTER, HIDDEN, e->up, INTER, nullptr, 0));
+            {   // gate and up in one launch
+                GemmTcGroupCall c{};
+                c.n_groups = 2;
+                c.w[0] = bf(w.wg) + (size_t)l * INTER * HIDDEN; c.n_rows[0] = INTER; c.out[0] = e->gate; c.ldo[0] = INTER;
+                c.w[1] = bf(w.wu) + (size_t)l * INTER * HIDDEN; c.n_rows[1] = INTER; c.out[1] = e->up; c.ldo[1] = INTER;
+                c.x_planes = planes; c.n_tok = B; c.K = HIDDEN; c.nsplit = tc_planes; c.plane_rows = prow; c.status = e->status;
+                LAUNCH(launch_gemm_tc_group(c, st));
+            }
             LAUNCH(launch_silu_mul(e->gate, e->up, e->hid, (size_t)B * INTER, st));
             // x += hid @ wd^T
             LAUNCH(launch_act_split(e->hid, INTER, INTER, nullptr, planes, prow, tc_planes, B, st));

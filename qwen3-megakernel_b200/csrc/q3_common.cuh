@@ -85,6 +85,20 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
     return v;
 }
 
+// Prefetch loads write straight into the registers that hold the row until it is used: the zero for a row past the
+// cache and the predicated load sit in one asm statement, so that no select or move consumes the loaded value (which
+// would park the warp until the row has arrived, at the place where it was only meant to be requested).
+__device__ __forceinline__ void ld_row16(uint4& d, const void* ptr, bool live) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+                 "@p ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
+                 : "=&r"(d.x), "=&r"(d.y), "=&r"(d.z), "=&r"(d.w) : "l"(ptr), "r"((int)live));
+}
+__device__ __forceinline__ void ld_row8(uint32_t& a, uint32_t& b, const void* ptr, bool live) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %3, 0;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\t"
+                 "@p ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];\n\t}"
+                 : "=&r"(a), "=&r"(b) : "l"(ptr), "r"((int)live));
+}
+
 // ---- device status words ----------------------------------------------------------------------
 // [0] error code (0 = fine), [1] phase / site id, [2] CTA index, [3] observed value.
 enum : uint32_t { ST_OK = 0, ST_BARRIER_TIMEOUT = 1, ST_MBAR_TIMEOUT = 2, ST_BAD_TOKEN = 3, ST_PEER_TIMEOUT = 4, ST_BAD_LEN = 5 };

@@ -65,7 +65,9 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
 }
 
 template <int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
+                                                                const __grid_constant__ CUtensorMap tm_w1,
+                                                                const __grid_constant__ CUtensorMap tm_w2,
                                                                 const __grid_constant__ CUtensorMap tm_x, const GemmTcParams p) {
     extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_bar;
@@ -73,7 +75,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __shared__ volatile int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * TC_BM;          // first weight row of this tile
+    // which weight matrix this tile belongs to (grouped launches), and its first row inside that matrix
+    int grp = 0, tile = blockIdx.x;
+    if (p.n_groups > 1) {
+        if (tile >= p.g_tiles[0]) { tile -= p.g_tiles[0]; grp = 1; }
+        if (grp == 1 && p.n_groups > 2 && tile >= p.g_tiles[1]) { tile -= p.g_tiles[1]; grp = 2; }
+    }
+    const CUtensorMap* tm_w = grp == 0 ? &tm_w0 : (grp == 1 ? &tm_w1 : &tm_w2);
+    float* const out = p.n_groups > 1 ? (grp == 0 ? p.g_out[0] : grp == 1 ? p.g_out[1] : p.g_out[2]) : p.out;
+    const int ldo = p.n_groups > 1 ? (grp == 0 ? p.g_ldo[0] : grp == 1 ? p.g_ldo[1] : p.g_ldo[2]) : p.ldo;
+    const int n_rows = p.n_groups > 1 ? (grp == 0 ? p.g_tiles[0] : grp == 1 ? p.g_tiles[1] : p.g_tiles[2]) * TC_BM : p.n_rows;
+    const int m0 = tile * TC_BM;                // first weight row of this tile
     const int n0 = blockIdx.y * BN;             // first token of this tile
     // split-K: grid.z slices of the k blocks; partial tiles are added into `out` with fp32 atomics
     const int kb_begin = blockIdx.z * p.kb_per_split;
@@ -112,7 +124,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                 unsigned char* st = base + (size_t)s * stage_bytes;
                 asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full_bar[s])), "r"(stage_bytes) : "memory");
                 asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(tc_smem(st)), "l"(&tm_w), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full_bar[s])) : "memory");
+                             ::"r"(tc_smem(st)), "l"(tm_w), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full_bar[s])) : "memory");
                 for (int sp = 0; sp < nsplit; ++sp)
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                                  ::"r"(tc_smem(st + a_bytes + sp * b_bytes)), "l"(&tm_x), "r"((kb_begin + kb) * TC_BK), "r"(sp * p.plane_rows + n0),
@@ -167,13 +179,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                                "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                              : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < p.n_rows) {
+                if (row < n_rows) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int t = n0 + c * 32 + j;
                         if (t < p.n_tok) {
                             float v = __uint_as_float(r[j]);
-                            float* dst = p.out + (size_t)t * p.ldo + row;
+                            float* dst = out + (size_t)t * ldo + row;
                             if (p.epi == TC_EPI_ATOMIC) {
                                 atomicAdd(dst, v);   // split-K: `out` already holds zero or the residual
                             } else {
@@ -225,7 +237,8 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t co
 }
 
 template <int BN>
-static cudaError_t launch_bn(const CUtensorMap& tw, const CUtensorMap& tx, GemmTcParams p, int n_rows, int n_tok, int sm_count, cudaStream_t st) {
+static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmTcParams p, int n_rows, int n_tok, int sm_count, cudaStream_t st) {
+    // n_rows: all weight rows of the launch (the sum over the groups); tw: three maps (unused ones repeat the first)
     const int nkb = p.K / TC_BK;
     const int tiles = ((n_rows + TC_BM - 1) / TC_BM) * ((n_tok + BN - 1) / BN);
     // Few output tiles (decode batches, short prompts) cannot fill the GPU: slice K so that about one
@@ -240,8 +253,17 @@ static cudaError_t launch_bn(const CUtensorMap& tw, const CUtensorMap& tx, GemmT
     ksplit = (nkb + p.kb_per_split - 1) / p.kb_per_split;
     if (ksplit > 1) {
         if (p.epi == TC_EPI_STORE) {   // partial sums are added onto zeros
-            cudaError_t e = cudaMemset2DAsync(p.out, (size_t)p.ldo * 4, 0, (size_t)n_rows * 4, (size_t)n_tok, st);
-            if (e != cudaSuccess) return e;
+            const int ng = p.n_groups > 1 ? p.n_groups : 1;
+            for (int g = 0; g < ng; ++g) {
+                float* o = p.n_groups > 1 ? p.g_out[g] : p.out;
+                const int ld = p.n_groups > 1 ? p.g_ldo[g] : p.ldo, rows = p.n_groups > 1 ? p.g_tiles[g] * TC_BM : n_rows;
+                // adjacent groups of one row-major buffer (q | k | v) are cleared by the first group's call
+                if (g > 0 && p.g_out[g] == p.g_out[g - 1] + p.g_tiles[g - 1] * TC_BM && p.g_ldo[g] == p.g_ldo[g - 1]) continue;
+                int span = rows;
+                for (int h = g + 1; h < ng && p.g_out[h] == o + span && p.g_ldo[h] == ld; ++h) span += p.g_tiles[h] * TC_BM;
+                cudaError_t e = cudaMemset2DAsync(o, (size_t)ld * 4, 0, (size_t)span * 4, (size_t)n_tok, st);
+                if (e != cudaSuccess) return e;
+            }
         }
         p.epi = TC_EPI_ATOMIC;         // in place on the residual otherwise
     }
@@ -259,7 +281,7 @@ static cudaError_t launch_bn(const CUtensorMap& tw, const CUtensorMap& tx, GemmT
         attr_set = true;
     }
     dim3 grid((n_rows + TC_BM - 1) / TC_BM, (n_tok + BN - 1) / BN, ksplit);
-    gemm_tc_kernel<BN><<<grid, TC_THREADS, smem, st>>>(tw, tx, p);
+    gemm_tc_kernel<BN><<<grid, TC_THREADS, smem, st>>>(tw[0], tw[1], tw[2], tx, p);
     return cudaGetLastError();
 }
 
@@ -295,9 +317,38 @@ cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st) {
     p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = c.resid ? TC_EPI_RESID : TC_EPI_STORE; p.status = c.status;
     static int sm_count = 0;
     if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
-    if (bn == 32) return launch_bn<32>(tw, tx, p, c.n_rows, c.n_tok, sm_count, st);
-    if (bn == 64) return launch_bn<64>(tw, tx, p, c.n_rows, c.n_tok, sm_count, st);
-    return launch_bn<128>(tw, tx, p, c.n_rows, c.n_tok, sm_count, st);
+    const CUtensorMap maps[3] = {tw, tw, tw};
+    if (bn == 32) return launch_bn<32>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st);
+    if (bn == 64) return launch_bn<64>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st);
+    return launch_bn<128>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st);
+}
+
+cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st) {
+    if (c.n_groups < 1 || c.n_groups > 3 || c.K % TC_BK || c.nsplit < 1 || c.nsplit > 3 || c.n_tok < 1) return cudaErrorInvalidValue;
+    const int bn = c.n_tok <= 32 ? 32 : (c.n_tok <= 64 ? 64 : 128);
+    if (c.plane_rows % bn) return cudaErrorInvalidValue;
+    CUtensorMap maps[3];
+    GemmTcParams p{};
+    int rows = 0;
+    for (int g = 0; g < c.n_groups; ++g) {
+        if (c.n_rows[g] % TC_BM || c.n_rows[g] < TC_BM) return cudaErrorInvalidValue;
+        const CUtensorMap* pw = cached_map(c.w[g], (uint64_t)c.n_rows[g], (uint64_t)c.K, TC_BM);
+        if (!pw) return cudaErrorUnknown;
+        maps[g] = *pw;
+        p.g_tiles[g] = c.n_rows[g] / TC_BM; p.g_out[g] = c.out[g]; p.g_ldo[g] = c.ldo[g];
+        rows += c.n_rows[g];
+    }
+    for (int g = c.n_groups; g < 3; ++g) maps[g] = maps[0];
+    const CUtensorMap* px = cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)bn);
+    if (!px) return cudaErrorUnknown;
+    const CUtensorMap tx = *px;
+    p.n_groups = c.n_groups; p.out = c.out[0]; p.resid = nullptr; p.ldo = c.ldo[0]; p.ldr = 0; p.n_rows = rows; p.n_tok = c.n_tok; p.K = c.K;
+    p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = TC_EPI_STORE; p.status = c.status;
+    static int sm_count = 0;
+    if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+    if (bn == 32) return launch_bn<32>(maps, tx, p, rows, c.n_tok, sm_count, st);
+    if (bn == 64) return launch_bn<64>(maps, tx, p, rows, c.n_tok, sm_count, st);
+    return launch_bn<128>(maps, tx, p, rows, c.n_tok, sm_count, st);
 }
 
 }  // namespace q3

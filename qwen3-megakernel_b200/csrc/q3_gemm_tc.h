@@ -21,6 +21,11 @@ struct GemmTcParams {
     int kb_per_split;      // k blocks (of 64) each grid.z slice covers
     int epi;
     uint32_t* status;
+    // grouped launches: grid.x tiles [0, g_tiles[0]) belong to matrix 0, the next g_tiles[1] to matrix 1, ...
+    int n_groups;          // 0 or 1: a single matrix (tm_w0, `out`, `ldo`)
+    int g_tiles[3];
+    float* g_out[3];
+    int g_ldo[3];
 };
 
 // host-side call
@@ -35,5 +40,19 @@ struct GemmTcCall {
 };
 
 cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st);
+
+// Up to three weight matrices with the same K against the same activation planes in ONE launch (q/k/v, gate/up):
+// group g writes out[g][t * ldo[g] + n] for its own rows n.  Plain stores or split-K atomics onto zeros; no residual.
+struct GemmTcGroupCall {
+    int n_groups;          // 1..3
+    const void* w[3];      // bf16 [n_rows[g], K] row-major
+    int n_rows[3];         // multiples of 128
+    float* out[3];
+    int ldo[3];
+    const void* x_planes;
+    int n_tok, K, nsplit, plane_rows;
+    uint32_t* status;
+};
+cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st);
 
 }  // namespace q3

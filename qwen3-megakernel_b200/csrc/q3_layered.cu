@@ -258,7 +258,7 @@ __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
     f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
 }
 
-__global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
     __shared__ float s_m[32][2], s_l[32][2];
     __shared__ __align__(16) float s_o[32][2][HEAD_DIM];  // 32 KB
 
@@ -291,18 +291,25 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc[hh][i] = 0.f;
 
+    // The rows of the next iteration are requested before the current ones are used (two iterations of K/V rows in
+    // flight per thread: the kernel is bound by HBM latency x bytes in flight, not by arithmetic).
+    auto request = [&](int pb, uint4& k0, uint4& k1, uint4& v0, uint4& v1) {
+        const int p = pb + quarter;
+        const bool live = p < p1 && p < len;
+        const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)(live ? p : 0) * KV_DIM);
+        const uint4* vr = reinterpret_cast<const uint4*>(vbase + (size_t)(live ? p : 0) * KV_DIM);
+        ld_row16(k0, kr + sub, live); ld_row16(k1, kr + 8 + sub, live);
+        ld_row16(v0, vr + sub, live); ld_row16(v1, vr + 8 + sub, live);
+    };
+    uint4 ck0, ck1, cv0, cv1;
+    request(p0 + warp * 4, ck0, ck1, cv0, cv1);
     for (int pb = p0 + warp * 4; pb < p1; pb += 32) {   // warp-uniform loop
+        uint4 nk0, nk1, nv0, nv1;
+        request(pb + 32, nk0, nk1, nv0, nv1);            // past p1: predicated off
         const int p = pb + quarter;
         const bool valid = p < p1;
         float kf[16], vf[16];
-        if (valid && p < len) {
-            const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)p * KV_DIM);
-            const uint4* vr = reinterpret_cast<const uint4*>(vbase + (size_t)p * KV_DIM);
-            const uint4 k0 = ld_stream(kr + sub), k1 = ld_stream(kr + 8 + sub);
-            const uint4 v0 = ld_stream(vr + sub), v1 = ld_stream(vr + 8 + sub);
-            unpack8(k0, kf); unpack8(k1, kf + 8);
-            unpack8(v0, vf); unpack8(v1, vf + 8);
-        } else if (valid) {   // the new token's own row
+        if (valid && p >= len) {   // the new token's own row
             const float* kn = qkv + Q_DIM + g * HEAD_DIM;
             const float* vn = qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
 #pragma unroll
@@ -310,9 +317,9 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
                 kf[i] = kn[sub * 8 + i]; kf[8 + i] = kn[64 + sub * 8 + i];
                 vf[i] = vn[sub * 8 + i]; vf[8 + i] = vn[64 + sub * 8 + i];
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+        } else {                   // a cached row, or zeros past the chunk
+            unpack8(ck0, kf); unpack8(ck1, kf + 8);
+            unpack8(cv0, vf); unpack8(cv1, vf + 8);
         }
         float s[2];
 #pragma unroll
@@ -337,6 +344,7 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const AttnArgs a) {
                 m[hh] = mn;
             }
         }
+        ck0 = nk0; ck1 = nk1; cv0 = nv0; cv1 = nv1;
     }
 
     // merge the 32 (warp, quarter) states of the block

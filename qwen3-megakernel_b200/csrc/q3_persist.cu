@@ -284,19 +284,6 @@ __device__ __forceinline__ void fold_cols(const float (&c)[4], float& row_lo, fl
 // pass i has been consumed.  The V rows are read dim-major instead (one warp per position, four dims
 // per lane), so P.V needs no shuffles: the first eight positions of every warp are fetched before the
 // barrier wait, the rest inside the loop.
-// Prefetch loads write straight into the registers that hold the row until it is used: the zero for a row past the
-// cache and the predicated load sit in one asm statement, so that no select or move consumes the loaded value (which
-// would park the warp until the row has arrived, at the place where it was only meant to be requested).
-__device__ __forceinline__ void ld_row16(uint4& d, const void* ptr, bool live) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
-                 "@p ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n\t}"
-                 : "=&r"(d.x), "=&r"(d.y), "=&r"(d.z), "=&r"(d.w) : "l"(ptr), "r"((int)live));
-}
-__device__ __forceinline__ void ld_row8(uint32_t& a, uint32_t& b, const void* ptr, bool live) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %3, 0;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\t"
-                 "@p ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];\n\t}"
-                 : "=&r"(a), "=&r"(b) : "l"(ptr), "r"((int)live));
-}
 __device__ __forceinline__ void ring_load(uint4 (&buf)[2], int pass, int npl, int len, int att_slot, int sub, const bf16_raw* kl) {
     const int pos = pass * 64 + att_slot;
     const bool live = pass < npl && pos < len;

@@ -302,11 +302,12 @@ class Megakernel:
         return dict(zip(self._out_specs, self._out))
 
     def bind_sequences(self, weights: dict, tokens: torch.Tensor, seqs: SeqTable, *, append: bool = False,
-                       chained: bool = False, want_logits: bool = True) -> dict:
+                       chained: bool = False, want_logits: bool = True, graph: bool = True) -> dict:
         """Batched form of `bind`: `tokens` int64 [B] on the device, `seqs` a SeqTable of B sequences.
         Returns outputs with a leading batch axis.  With append=True each launch writes the new K/V rows
         into the caches and advances the device-side lengths (capacity is the caller's responsibility:
-        at most capacity_b - len_b launches)."""
+        at most capacity_b - len_b launches).  graph=False keeps the layered path on plain launches
+        (one per kernel), which is what a profiler wants to see."""
         B = seqs.batch
         if tokens.dtype != torch.int64 or tokens.numel() != B or not tokens.is_cuda or not tokens.is_contiguous():
             raise ValueError(f"tokens: expected a contiguous CUDA int64 tensor of {B} elements")
@@ -317,7 +318,7 @@ class Megakernel:
         self._out = self._alloc(B)
         logits, next_token, k_write, v_write = self._out
         # bound launches repeat the same argument block: let the layered path replay a CUDA graph
-        flags = self._path_flag | (_cabi.F_APPEND_KV if append else 0) | _cabi.F_GRAPH
+        flags = self._path_flag | (_cabi.F_APPEND_KV if append else 0) | (_cabi.F_GRAPH if graph else 0)
         self._args = _cabi.DecodeArgs(B, seqs.max_len, flags, 0, tokens.data_ptr(), seqs.seq_k.data_ptr(),
                                       seqs.seq_v.data_ptr(), seqs.stride.data_ptr(), seqs.len.data_ptr(),
                                       logits.data_ptr() if want_logits else None, next_token.data_ptr(),

@@ -4,6 +4,7 @@
   run.py check [--weights hf|synthetic] [--seed N] [--context N]
   run.py bench [--weights hf|synthetic] [--iters N] [--context N] [--grow] [--chains N]
   run.py trace [--context N]            per-phase timing of the persistent kernel (device time stamps)
+  run.py batch [--batch B] [--context N] [--steps K] [--plain]   one batched decode step of the layered path
   run.py demo --prompt "..."
 
 `check` verifies what can be verified without a second implementation: the persistent kernel and the
@@ -144,6 +145,39 @@ def cmd_trace(args) -> int:
     return 0
 
 
+def cmd_batch(args) -> int:
+    """One batched decode step (layered tensor-core path): `--batch` sequences of `--context` cached positions."""
+    from qwen3mk.kernel import SeqTable, LAYERS, KV_HEADS, HEAD_DIM, VOCAB
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    B, ctx = args.batch, args.context
+    w = weights.baseline_init(args.seed, dev)
+    g = torch.Generator(device=dev).manual_seed(args.seed)
+    mk_cache = lambda: (torch.randn(LAYERS, ctx, KV_HEADS, HEAD_DIM, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+    kcs, vcs = [mk_cache() for _ in range(B)], [mk_cache() for _ in range(B)]
+    mk = Megakernel(dev, max_batch=B)
+    seqs = SeqTable(kcs, vcs)
+    toks = torch.randint(0, VOCAB, (B,), device=dev, generator=g)
+    mk.bind_sequences(w, toks, seqs, graph=not args.plain)
+    for _ in range(3):
+        mk.launch()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = mk.launch_count
+    e0.record()
+    for _ in range(args.steps):
+        mk.launch()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    mk.status()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    nbytes = 1_192_099_840 + B * (114_688 * ctx + 724_480)   # weights + gains + per-sequence K/V and activations
+    print(f"batch {B} x {ctx} cached positions: {us:.1f} us/step, {B * 1e6 / us:.0f} tokens/s, "
+          f"{nbytes / us / 1e6:.2f} TB/s of algorithmic bytes, {(mk.launch_count - n0) / args.steps:.0f} kernels per step"
+          f"{' (plain launches)' if args.plain else ' (graph replay)'}")
+    return 0
+
+
 def cmd_demo(args) -> int:
     try:
         tok = prefill_mod.load_tokenizer()
@@ -177,10 +211,16 @@ def main(argv=None) -> int:
             p.add_argument("--iters", type=int, default=200)
             p.add_argument("--grow", action="store_true")
             p.add_argument("--chains", type=int, default=20, help="chains of 50 steps in the steady measurement")
+    p = sub.add_parser("batch")
+    p.add_argument("--batch", type=int, default=64)
+    p.add_argument("--context", type=int, default=1024)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--plain", action="store_true", help="plain launches instead of CUDA-graph replay")
     p = sub.add_parser("demo")
     p.add_argument("--prompt", default=DEFAULT_PROMPT)
     args = ap.parse_args(argv)
-    return {"check": cmd_check, "bench": cmd_bench, "trace": cmd_trace, "demo": cmd_demo}[args.cmd](args)
+    return {"check": cmd_check, "bench": cmd_bench, "trace": cmd_trace, "batch": cmd_batch, "demo": cmd_demo}[args.cmd](args)
 
 
 if __name__ == "__main__":

@@ -76,7 +76,7 @@ def test_small_model_step_vs_oracle_and_golden(oracle, small, path):
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("ctx", [0, 1, 7, 17, 19, 64, 128, 129, 191, 240, 241, 300, 324, 325, 515, 577, 1500, 2286, 2400])
+@pytest.mark.parametrize("ctx", [0, 1, 7, 17, 19, 64, 128, 129, 191, 192, 240, 255, 256, 300, 515, 577, 1500, 2286, 2400])
 def test_any_position(oracle, path, ctx):
     shp = oracle.Shape(layers=2, vocab=2048)
     inp = oracle.synthetic(100 + ctx, shp, context=max(ctx, 1))
@@ -92,6 +92,26 @@ def test_any_position(oracle, path, ctx):
     mk.status()
     ref = oracle.decode_step(oracle.to_fp32(inp), inp["token"], inp["kcache"], inp["vcache"])
     gate_step(oracle, out, ref, f"{path} ctx {ctx}")
+
+
+def test_persist_reports_a_cache_longer_than_the_host_said(oracle):
+    """The host's length bound picks the kernel variant; a longer cache on the device is reported, not served."""
+    from qwen3mk.kernel import SeqTable
+
+    shp = oracle.Shape(layers=2, vocab=2048)
+    inp = oracle.synthetic(5, shp, context=300)
+    dev = to_dev(inp)
+    mk = engine("persist", layers=2, vocab=2048)
+    seqs = SeqTable([dev["kcache"]], [dev["vcache"]], lens=[100])      # host bound: 100 positions
+    mk.bind_sequences({k: dev[k] for k in oracle.WEIGHT_NAMES}, dev["token"].reshape(1), seqs)
+    seqs.len.fill_(300)                                                # the device says 300
+    mk.launch()
+    with pytest.raises(RuntimeError, match="device status"):
+        mk.status()
+    # the engine stays usable
+    seqs.len.fill_(100)
+    mk.launch()
+    mk.status()
 
 
 @pytest.mark.parametrize("path", ["layered", "auto"])
