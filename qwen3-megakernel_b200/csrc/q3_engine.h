@@ -10,7 +10,9 @@
 #define Q3_STATUS_WORDS 8
 #define Q3_SYNC_WORDS 64
 #define Q3_MAX_SPLITS 64
-#define Q3_TC_MIN_BATCH 9   // from this many tokens on the projections run as tensor-core GEMMs
+#ifndef Q3_TC_MIN_BATCH
+#define Q3_TC_MIN_BATCH 4   // from this many tokens on the projections run as tensor-core GEMMs (measured at 1024 cached positions: batch 4 1804 vs 1882 us, batch 8 1959 vs 2420 us, batch 2 1740 vs 1598 us)
+#endif
 
 struct q3_engine {
     int device;
