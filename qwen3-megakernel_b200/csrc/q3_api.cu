@@ -222,9 +222,16 @@ extern "C" int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n)
 static int splits_for(const q3_engine* e, int batch, int max_len) {
     const int n = max_len + 1;
     int by_len = (n + 31) / 32;                                   // at least 32 positions per split
-    int by_fill = (2 * e->sm_count + KV_HEADS * batch - 1) / (KV_HEADS * batch);  // ~2 blocks per SM
+    // three blocks of the split kernel fit an SM; about three waves of them even out the last, partly filled one
+    // (measured, batch 64 x 1024 positions: 1 / 2 / 3 / 6 / 7 splits 3690 / 3437 / 3439 / 3551 / 3713 us per step)
+    int by_fill = (9 * e->sm_count + KV_HEADS * batch - 1) / (KV_HEADS * batch);
     int s = by_len < by_fill ? by_len : by_fill;
     if (s < 1) s = 1;
+#ifdef Q3_SPLITS_ENV
+    { static int forced = -1; if (forced < 0) { const char* v = getenv("Q3_ATTN_SPLITS"); forced = v ? atoi(v) : 0; } if (forced > 0) s = forced; }
+#endif
+    const int by_chunk = (n + ATTN_CHUNK_MAX - 1) / ATTN_CHUNK_MAX;   // a block's scores must fit its shared memory
+    if (s < by_chunk) s = by_chunk;
     if (s > e->max_splits) s = e->max_splits;
     if (e->part_slots > 0 && s * batch > e->part_slots) s = e->part_slots / batch;
     if (s < 1) s = 1;
@@ -291,11 +298,16 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         t.qkv = e->qkv; t.seq_k = a->seq_k; t.seq_v = a->seq_v;
         t.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
         t.seq_len = a->seq_len; t.part = e->part; t.layer = l; t.n_splits = ns;
+        t.chunk_pad = (((a->max_len + 1 + ns - 1) / ns) + 31) / 32 * 32;
         if (prompt != nullptr && B >= 64) {
             // a prompt: tiled causal attention over the rows head_prep has just written into the cache
             const bf16_raw* kc = bf(prompt->kcache) + (size_t)l * prompt->layer_stride;
             const bf16_raw* vc = bf(prompt->vcache) + (size_t)l * prompt->layer_stride;
             LAUNCH(launch_prefill_attn(e->qkv, kc, vc, e->attn, B, st));
+            if (tc) LAUNCH(launch_act_split(e->attn, Q_DIM, Q_DIM, nullptr, planes, prow, tc_planes, B, st));
+        } else if (tc) {
+            LAUNCH(launch_attn_planes(t, planes, prow, tc_planes, B, st));   // the merge writes the Wo GEMM's input planes
+            ++e->launches;  // two kernels
         } else {
             LAUNCH(launch_attn(t, e->attn, B, st));
             ++e->launches;  // launch_attn is two kernels
@@ -303,7 +315,6 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
 
         if (tc) {
             // x += attn @ wo^T
-            LAUNCH(launch_act_split(e->attn, Q_DIM, Q_DIM, nullptr, planes, prow, tc_planes, B, st));
             LAUNCH(gemm(bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN, Q_DIM, e->x, HIDDEN, e->x, HIDDEN));
             // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
             LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st));
@@ -315,9 +326,8 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
                 c.x_planes = planes; c.n_tok = B; c.K = HIDDEN; c.nsplit = tc_planes; c.plane_rows = prow; c.status = e->status;
                 LAUNCH(launch_gemm_tc_group(c, st));
             }
-            LAUNCH(launch_silu_mul(e->gate, e->up, e->hid, (size_t)B * INTER, st));
-            // x += hid @ wd^T
-            LAUNCH(launch_act_split(e->hid, INTER, INTER, nullptr, planes, prow, tc_planes, B, st));
+            // x += (silu(gate) * up) @ wd^T
+            LAUNCH(launch_silu_planes(e->gate, e->up, planes, prow, tc_planes, B, st));
             LAUNCH(gemm(bf(w.wd) + (size_t)l * HIDDEN * INTER, HIDDEN, INTER, e->x, HIDDEN, e->x, HIDDEN));
         } else {
             // x += attn @ wo^T

@@ -258,9 +258,18 @@ __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
     f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
 }
 
-__global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
-    __shared__ float s_m[32][2], s_l[32][2];
-    __shared__ __align__(16) float s_o[32][2][HEAD_DIM];  // 32 KB
+// Two passes over the block's chunk of positions, both bound by bytes in flight rather than arithmetic, so both keep
+// several rows per thread requested ahead of their use and the kernel keeps its registers low enough for three
+// blocks per SM:
+//   1. scores: a quarter-warp per position (K row = 2 x 16 bytes a lane), both GQA heads against the same row;
+//      scores go to shared memory, the maxima are reduced over the block;
+//   2. P.V: a warp per position, four dims a lane (V row = 8 bytes a lane): every lane forms the same two
+//      probabilities from the shared scores, so nothing crosses lanes; eight per-warp sums are added at the end.
+// The new token's own K/V rows are fp32 in `qkv` (not yet rounded into the cache) and are handled by warp 0.
+__global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
+    extern __shared__ __align__(16) float attn_sc[];          // [2][chunk_pad] scores of the chunk
+    __shared__ float s_red[2][8], s_l[8][2];
+    __shared__ __align__(16) float s_o[8][2][HEAD_DIM];       // 8 KB
 
     const int sp = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -268,111 +277,146 @@ __global__ void __launch_bounds__(256, 2) attn_split_kernel(const AttnArgs a) {
     const int len = a.seq_len[b];
     const int n = len + 1;
     const int chunk = (n + a.n_splits - 1) / a.n_splits;
-    const int p0 = sp * chunk, p1 = min(p0 + chunk, n);
+    const int p0 = sp * chunk, p1 = min(min(p0 + chunk, n), p0 + a.chunk_pad);
+    const int pc = min(p1, len);                              // cached positions of the chunk: [p0, pc)
+    const bool has_new = p0 <= len && len < p1;               // the new token's row belongs to this chunk
+    float* sc0 = attn_sc;
+    float* sc1 = attn_sc + a.chunk_pad;
 
     const float* qkv = a.qkv + (size_t)b * QKV_DIM;
-    float q[2][16];
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-        const float* qp = qkv + (2 * g + hh) * HEAD_DIM;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            q[hh][i] = qp[sub * 8 + i] * ATTN_SCALE;
-            q[hh][8 + i] = qp[64 + sub * 8 + i] * ATTN_SCALE;
-        }
-    }
     const bf16_raw* kbase = reinterpret_cast<const bf16_raw*>(a.seq_k[b]) + (size_t)a.layer * a.seq_layer_stride[b] + g * HEAD_DIM;
     const bf16_raw* vbase = reinterpret_cast<const bf16_raw*>(a.seq_v[b]) + (size_t)a.layer * a.seq_layer_stride[b] + g * HEAD_DIM;
 
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float acc[2][16];
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[hh][i] = 0.f;
-
-    // The rows of the next iteration are requested before the current ones are used (two iterations of K/V rows in
-    // flight per thread: the kernel is bound by HBM latency x bytes in flight, not by arithmetic).
-    auto request = [&](int pb, uint4& k0, uint4& k1, uint4& v0, uint4& v1) {
-        const int p = pb + quarter;
-        const bool live = p < p1 && p < len;
-        const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)(live ? p : 0) * KV_DIM);
-        const uint4* vr = reinterpret_cast<const uint4*>(vbase + (size_t)(live ? p : 0) * KV_DIM);
-        ld_row16(k0, kr + sub, live); ld_row16(k1, kr + 8 + sub, live);
-        ld_row16(v0, vr + sub, live); ld_row16(v1, vr + 8 + sub, live);
-    };
-    uint4 ck0, ck1, cv0, cv1;
-    request(p0 + warp * 4, ck0, ck1, cv0, cv1);
-    for (int pb = p0 + warp * 4; pb < p1; pb += 32) {   // warp-uniform loop
-        uint4 nk0, nk1, nv0, nv1;
-        request(pb + 32, nk0, nk1, nv0, nv1);            // past p1: predicated off
-        const int p = pb + quarter;
-        const bool valid = p < p1;
-        float kf[16], vf[16];
-        if (valid && p >= len) {   // the new token's own row
-            const float* kn = qkv + Q_DIM + g * HEAD_DIM;
-            const float* vn = qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                kf[i] = kn[sub * 8 + i]; kf[8 + i] = kn[64 + sub * 8 + i];
-                vf[i] = vn[sub * 8 + i]; vf[8 + i] = vn[64 + sub * 8 + i];
-            }
-        } else {                   // a cached row, or zeros past the chunk
-            unpack8(ck0, kf); unpack8(ck1, kf + 8);
-            unpack8(cv0, vf); unpack8(cv1, vf + 8);
-        }
-        float s[2];
+    // ---------------------------------------------------------------- pass 1: scores
+    float tmax0 = -INFINITY, tmax1 = -INFINITY;
+    {
+        float q[2][16];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-            float t = 0.f;
+            const float* qp = qkv + (2 * g + hh) * HEAD_DIM;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) t = fmaf(q[hh][i], kf[i], t);
-            t += __shfl_xor_sync(0xffffffffu, t, 1);
-            t += __shfl_xor_sync(0xffffffffu, t, 2);
-            t += __shfl_xor_sync(0xffffffffu, t, 4);
-            s[hh] = t;
-        }
-        if (valid) {
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const float mn = fmaxf(m[hh], s[hh]);
-                const float corr = expf(m[hh] - mn);   // exp(-inf) = 0 on the first row
-                const float pe = expf(s[hh] - mn);
-                l[hh] = l[hh] * corr + pe;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) acc[hh][i] = fmaf(pe, vf[i], acc[hh][i] * corr);
-                m[hh] = mn;
+            for (int i = 0; i < 8; ++i) {
+                q[hh][i] = qp[sub * 8 + i] * ATTN_SCALE;
+                q[hh][8 + i] = qp[64 + sub * 8 + i] * ATTN_SCALE;
             }
         }
-        ck0 = nk0; ck1 = nk1; cv0 = nv0; cv1 = nv1;
-    }
-
-    // merge the 32 (warp, quarter) states of the block
-    const int st = warp * 4 + quarter;
+        // position of this quarter-warp in iteration `it`: p0 + 32 it + 4 warp + quarter
+        auto request = [&](int it, uint4& k0, uint4& k1) {
+            const int p = p0 + 32 * it + 4 * warp + quarter;
+            const bool live = p < pc;
+            const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)(live ? p : 0) * KV_DIM);
+            ld_row16(k0, kr + sub, live); ld_row16(k1, kr + 8 + sub, live);
+        };
+        auto score = [&](int it, const uint4& k0, const uint4& k1) {
+            const int p = p0 + 32 * it + 4 * warp + quarter;
+            float kf[16];
+            unpack8(k0, kf); unpack8(k1, kf + 8);
+            float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-        if (sub == 0) { s_m[st][hh] = m[hh]; s_l[st][hh] = l[hh]; }
+            for (int i = 0; i < 16; ++i) { s0 = fmaf(q[0][i], kf[i], s0); s1 = fmaf(q[1][i], kf[i], s1); }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            s_o[st][hh][sub * 8 + i] = acc[hh][i];
-            s_o[st][hh][64 + sub * 8 + i] = acc[hh][8 + i];
+            for (int o = 1; o <= 4; o <<= 1) {
+                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            }
+            if (p < pc) {
+                tmax0 = fmaxf(tmax0, s0); tmax1 = fmaxf(tmax1, s1);
+                if (sub == 0) { sc0[p - p0] = s0; sc1[p - p0] = s1; }
+            }
+        };
+        const int iters = (pc - p0 + 31) / 32;                // block-uniform
+        uint4 ka0, ka1, kb0, kb1, kc0, kc1;                   // three iterations of rows in flight
+        request(0, ka0, ka1);
+        request(1, kb0, kb1);
+        for (int it = 0; it < iters; it += 3) {
+            request(it + 2, kc0, kc1);
+            score(it, ka0, ka1);
+            if (it + 1 >= iters) break;
+            request(it + 3, ka0, ka1);
+            score(it + 1, kb0, kb1);
+            if (it + 2 >= iters) break;
+            request(it + 4, kb0, kb1);
+            score(it + 2, kc0, kc1);
+        }
+        if (has_new && warp == 0) {   // q . k_new in fp32, four dims a lane
+            const float4 kn = *reinterpret_cast<const float4*>(qkv + Q_DIM + g * HEAD_DIM + lane * 4);
+            const float4 q0 = *reinterpret_cast<const float4*>(qkv + (2 * g) * HEAD_DIM + lane * 4);
+            const float4 q1 = *reinterpret_cast<const float4*>(qkv + (2 * g + 1) * HEAD_DIM + lane * 4);
+            float s0 = (q0.x * kn.x + q0.y * kn.y + q0.z * kn.z + q0.w * kn.w) * ATTN_SCALE;
+            float s1 = (q1.x * kn.x + q1.y * kn.y + q1.z * kn.z + q1.w * kn.w) * ATTN_SCALE;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            }
+            tmax0 = fmaxf(tmax0, s0); tmax1 = fmaxf(tmax1, s1);
+            if (lane == 0) { sc0[len - p0] = s0; sc1[len - p0] = s1; }
         }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, o));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, o));
+    }
+    if (lane == 0) { s_red[0][warp] = tmax0; s_red[1][warp] = tmax1; }
+    __syncthreads();
+    float M0 = -INFINITY, M1 = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { M0 = fmaxf(M0, s_red[0][w]); M1 = fmaxf(M1, s_red[1][w]); }
+
+    // ---------------------------------------------------------------- pass 2: P.V
+    float l0 = 0.f, l1 = 0.f, acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+        // position of this warp's row j of batch `bt`: p0 + 64 bt + 8 j + warp
+        auto request = [&](int bt, uint2 (&v)[8]) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int p = p0 + 64 * bt + 8 * j + warp;
+                const bool live = p < pc;
+                ld_row8(v[j].x, v[j].y, vbase + (size_t)(live ? p : 0) * KV_DIM + lane * 4, live);
+            }
+        };
+        auto accumulate = [&](int bt, const uint2 (&v)[8]) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = 64 * bt + 8 * j + warp;
+                const bool live = p0 + i < pc;
+                const float pr0 = live ? __expf(sc0[i] - M0) : 0.f, pr1 = live ? __expf(sc1[i] - M1) : 0.f;
+                l0 += pr0; l1 += pr1;
+                const float f0 = bf_lo(v[j].x), f1 = bf_hi(v[j].x), f2 = bf_lo(v[j].y), f3 = bf_hi(v[j].y);
+                acc[0][0] = fmaf(pr0, f0, acc[0][0]); acc[0][1] = fmaf(pr0, f1, acc[0][1]); acc[0][2] = fmaf(pr0, f2, acc[0][2]); acc[0][3] = fmaf(pr0, f3, acc[0][3]);
+                acc[1][0] = fmaf(pr1, f0, acc[1][0]); acc[1][1] = fmaf(pr1, f1, acc[1][1]); acc[1][2] = fmaf(pr1, f2, acc[1][2]); acc[1][3] = fmaf(pr1, f3, acc[1][3]);
+            }
+        };
+        const int batches = (pc - p0 + 63) / 64;              // block-uniform
+        uint2 va[8], vb[8];                                   // two batches of eight rows in flight per warp
+        request(0, va);
+        for (int bt = 0; bt < batches; bt += 2) {
+            request(bt + 1, vb);
+            accumulate(bt, va);
+            if (bt + 1 >= batches) break;
+            request(bt + 2, va);
+            accumulate(bt + 1, vb);
+        }
+        if (has_new && warp == 0) {   // the new token's V row in fp32
+            const float4 vn = *reinterpret_cast<const float4*>(qkv + Q_DIM + KV_DIM + g * HEAD_DIM + lane * 4);
+            const float pr0 = __expf(sc0[len - p0] - M0), pr1 = __expf(sc1[len - p0] - M1);
+            l0 += pr0; l1 += pr1;
+            acc[0][0] = fmaf(pr0, vn.x, acc[0][0]); acc[0][1] = fmaf(pr0, vn.y, acc[0][1]); acc[0][2] = fmaf(pr0, vn.z, acc[0][2]); acc[0][3] = fmaf(pr0, vn.w, acc[0][3]);
+            acc[1][0] = fmaf(pr1, vn.x, acc[1][0]); acc[1][1] = fmaf(pr1, vn.y, acc[1][1]); acc[1][2] = fmaf(pr1, vn.z, acc[1][2]); acc[1][3] = fmaf(pr1, vn.w, acc[1][3]);
+        }
+    }
+    *reinterpret_cast<float4*>(&s_o[warp][0][lane * 4]) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+    *reinterpret_cast<float4*>(&s_o[warp][1][lane * 4]) = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
+    if (lane == 0) { s_l[warp][0] = l0; s_l[warp][1] = l1; }
     __syncthreads();
     {
         const int hh = tid >> 7, d = tid & 127;
-        float M = -INFINITY;
-        for (int i = 0; i < 32; ++i) M = fmaxf(M, s_m[i][hh]);
         float L = 0.f, o = 0.f;
-        if (M > -INFINITY) {
-            for (int i = 0; i < 32; ++i) {
-                const float w = expf(s_m[i][hh] - M);   // 0 for empty states
-                L = fmaf(s_l[i][hh], w, L);
-                o = fmaf(s_o[i][hh][d], w, o);
-            }
-        }
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { L += s_l[w][hh]; o += s_o[w][hh][d]; }
         float* out = a.part + (((size_t)b * Q_HEADS + 2 * g + hh) * a.n_splits + sp) * ATTN_PART_STRIDE;
-        if (d == 0) { out[0] = M; out[1] = L; }
+        if (d == 0) { out[0] = hh ? M1 : M0; out[1] = L; }   // an empty chunk publishes (-inf, 0, 0)
         out[4 + d] = o;
     }
 }
@@ -391,6 +435,50 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
         o = fmaf(p[s * ATTN_PART_STRIDE + 4 + d], w, o);
     }
     attn[(size_t)b * Q_DIM + h * HEAD_DIM + d] = o / L;
+}
+
+// three-way bf16 split of one fp32 value into the planes of row t, element e
+__device__ __forceinline__ void store_planes(bf16_raw* __restrict__ planes, int plane_rows, int nsplit, int K, int t, int e, float v) {
+    const bf16_raw h = f_to_bf(v);
+    planes[(size_t)t * K + e] = h;
+    if (nsplit > 1) {
+        const float r1 = v - bf_to_f(h);
+        const bf16_raw m = f_to_bf(r1);
+        planes[((size_t)plane_rows + t) * K + e] = m;
+        if (nsplit > 2) planes[((size_t)2 * plane_rows + t) * K + e] = f_to_bf(r1 - bf_to_f(m));
+    }
+}
+
+// attn_merge fused with the split into planes (the input of the Wo GEMM): block (head, plane row)
+__global__ void __launch_bounds__(128) attn_merge_planes_kernel(const float* __restrict__ part, int n_splits, bf16_raw* __restrict__ planes,
+                                                                int plane_rows, int nsplit, int n_tok) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    float v = 0.f;   // padding rows of the token tile are zeros
+    if (b < n_tok) {
+        const float* p = part + ((size_t)b * Q_HEADS + h) * n_splits * ATTN_PART_STRIDE;
+        float M = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * ATTN_PART_STRIDE]);
+        float L = 0.f, o = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = p[s * ATTN_PART_STRIDE];
+            const float w = (ms > -INFINITY) ? expf(ms - M) : 0.f;
+            L = fmaf(p[s * ATTN_PART_STRIDE + 1], w, L);
+            o = fmaf(p[s * ATTN_PART_STRIDE + 4 + d], w, o);
+        }
+        v = o / L;
+    }
+    store_planes(planes, plane_rows, nsplit, Q_DIM, b, h * HEAD_DIM + d, v);
+}
+
+// silu(gate) * up fused with the split into planes (the input of the down GEMM): one block per plane row
+__global__ void __launch_bounds__(256) silu_planes_kernel(const float* __restrict__ g, const float* __restrict__ u, bf16_raw* __restrict__ planes,
+                                                          int plane_rows, int nsplit, int n_tok) {
+    const int t = blockIdx.x;
+    for (int e = threadIdx.x; e < INTER; e += 256) {
+        float v = 0.f;
+        if (t < n_tok) { const float a = g[(size_t)t * INTER + e]; v = (a / (1.f + expf(-a))) * u[(size_t)t * INTER + e]; }
+        store_planes(planes, plane_rows, nsplit, INTER, t, e, v);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -478,6 +566,10 @@ cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gai
     act_split_kernel<<<plane_rows, 256, 0, st>>>(x, ldx, K, gain, planes, plane_rows, nsplit, n_tok);
     return cudaGetLastError();
 }
+cudaError_t launch_silu_planes(const float* g, const float* u, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st) {
+    silu_planes_kernel<<<plane_rows, 256, 0, st>>>(g, u, planes, plane_rows, nsplit, n_tok);
+    return cudaGetLastError();
+}
 cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, cudaStream_t st) {
     silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, h, n);
     return cudaGetLastError();
@@ -534,8 +626,19 @@ cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st) 
     return cudaGetLastError();
 }
 
+// split attention whose merge writes the bf16 planes of the Wo GEMM's input directly
+cudaError_t launch_attn_planes(const AttnArgs& a, bf16_raw* planes, int plane_rows, int nsplit, int batch, cudaStream_t st) {
+    if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.chunk_pad > ATTN_CHUNK_MAX) return cudaErrorInvalidValue;
+    attn_split_kernel<<<dim3(a.n_splits, KV_HEADS, batch), 256, (size_t)2 * a.chunk_pad * sizeof(float), st>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    attn_merge_planes_kernel<<<dim3(Q_HEADS, plane_rows), 128, 0, st>>>(a.part, a.n_splits, planes, plane_rows, nsplit, batch);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st) {
-    attn_split_kernel<<<dim3(a.n_splits, KV_HEADS, batch), 256, 0, st>>>(a);
+    if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.chunk_pad > ATTN_CHUNK_MAX) return cudaErrorInvalidValue;
+    attn_split_kernel<<<dim3(a.n_splits, KV_HEADS, batch), 256, (size_t)2 * a.chunk_pad * sizeof(float), st>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     attn_merge_kernel<<<dim3(Q_HEADS, batch), 128, 0, st>>>(a.part, a.n_splits, attn_out);

@@ -11,6 +11,7 @@ enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU = 2, EPI_LOGITS = 3 };
 
 // floats per (sequence, head, split) attention partial: [0] max, [1] sum, [4..132) unnormalised output
 constexpr int ATTN_PART_STRIDE = 132;
+constexpr int ATTN_CHUNK_MAX = 4096;          // positions one block of the split-attention kernel takes (its scores live in shared memory)
 
 struct GemvSeg {
     const bf16_raw* w;  // [rows, K] row-major bf16
@@ -55,6 +56,7 @@ struct AttnArgs {
     const int* seq_len;
     float* part;                      // [batch, 16, n_splits, ATTN_PART_STRIDE]
     int layer, n_splits;
+    int chunk_pad;                    // positions per split, rounded up to 32: what the host's length bound allows (<= ATTN_CHUNK_MAX)
 };
 
 cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStream_t st);
@@ -62,6 +64,8 @@ cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int voca
 cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st);
 cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st);
 cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st);
+cudaError_t launch_attn_planes(const AttnArgs& a, bf16_raw* planes, int plane_rows, int nsplit, int batch, cudaStream_t st);
+cudaError_t launch_silu_planes(const float* g, const float* u, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st);
 cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gain, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st);
 cudaError_t launch_prefill_desc(uint64_t* seq_k, uint64_t* seq_v, long long* stride, int* len, uint64_t k, uint64_t v, long long s, int n, cudaStream_t st);
 cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, cudaStream_t st);

@@ -1,30 +1,31 @@
 // Persistent cooperative decode kernel: one launch runs a whole batch-1 decode step.
 //
-// One CTA per SM: 16 consumer warps and two producer warps.  The schedule is static (every CTA owns
-// fixed weight rows) and a layer costs three grid barriers:
+// One CTA of 16 warps per SM.  The schedule is static (every CTA owns fixed weight rows, all of them resident
+// in its 227 KB of shared memory for the layer at hand) and a layer costs TWO grid barriers:
 //
-//   Q   x = X0 + dB;  qkv rows = rms(x, ln1) . [wq;wk;wv] rows                 -> qkv (global fp32)
-//   F   the 18 CTAs of a kv-head group (2 query heads x 9 Wo row slices) each attend 1/18 of the
-//       cached positions for both heads, publish (max, sum, output) partials, meet at a group
-//       counter, merge their own head with the new row, then Wo[slice rows, head columns] . o_h is
-//       added into dA                                                           (red.global.add)
+//   Q   x = X0 + dB;  qkv rows = rms(x, ln1) . [wq;wk;wv] rows, published as tagged 64-bit words
+//       (tag << 32 | fp32 bits, one tag per launch and layer): no barrier follows, the readers poll the tags
+//   F   four warps of every CTA poll the q/k/v rows of their kv group, normalise and rotate them; then either
+//       every CTA attends its whole head over all cached positions from registers (up to 255 positions), or the
+//       18 CTAs of a kv-head group (2 query heads x 9 Wo row slices) each attend 1/18 of the positions for both
+//       heads and exchange (max, sum, output) partials as tagged words; Wo[slice rows, head columns] . o_h is
+//       added into dA                                                           (red.global.add)   | barrier
 //   GD  x = X1 + dA;  hid rows = silu(gate) * up for this CTA's FFN rows, kept in shared memory,
-//       then the matching rows of the transposed down matrix scatter hid into dB (red.global.add)
+//       then the matching rows of the transposed down matrix scatter hid into dB (red.global.add)   | barrier
 //
-// The residual stream lives as "materialised vector + pending delta": every consumer adds the two
-// on load, one CTA writes the sum back for the phase after next.
+// The residual stream lives as "materialised vector + pending delta": every CTA adds the two on load, one CTA
+// writes the sum back for the phase after next; the deltas alternate between two buffers per layer parity.
 //
-// Weights never wait for a barrier.  Each CTA's rows of the seven matrices of a layer are packed
-// once (pack_weights_kernel) in the order and with the row padding of four shared-memory slots; two
-// producer warps refill a slot for the next layer as soon as the consumers release it, as a steady
-// stream of 16-byte cp.async copies with a bounded number in flight.  The matrix-vector products run
-// on the tensor cores (mma.sync m16n8k16) with the fp32 activation vector split into three bf16
+// Weights never wait for a barrier, and a barrier never waits behind weights.  Each CTA's rows of the seven
+// matrices of a layer are packed once (pack_weights_kernel) in the order and with the row padding of four
+// shared-memory slots; one thread fetches a whole slot with TMA bulk copies at the START of the phase before the
+// one that reads it, so that the copies have landed when the phase's barrier is polled.  The matrix-vector
+// products run on the tensor cores (mma.sync m16n8k16) with the fp32 activation vector split into three bf16
 // columns, which is exact to fp32 and needs no warp-shuffle reductions.
 //
-// A grid barrier is an arrive (red.release) and a later bounded wait (relaxed poll + acquire
-// fence); loads that do not depend on other CTAs (cached K/V rows, norm gains) sit between the two.
-// Every wait is bounded: a wait that gives up records a status word and turns the remaining
-// barriers of the CTA into no-ops, so a launch always terminates and the host reads the error.
+// A grid barrier is an arrive (red.release) and a later bounded wait (relaxed poll + acquire fence).  Every wait
+// is bounded: a wait that gives up records a status word and turns the remaining waits of the CTA into no-ops,
+// so a launch always terminates and the host reads the error.
 //
 // What the reference does for the same step: csrc/qwen3_step.cu:382-818 (four barriers per layer,
 // attention recomputed by every slice CTA, fixed position 128).
@@ -32,8 +33,8 @@
 
 namespace q3 {
 
-constexpr int CW = 16;                        // consumer warps
-constexpr int CT = CW * 32;                   // consumer threads
+constexpr int CW = 16;                        // warps per CTA
+constexpr int CT = CW * 32;                   // threads per CTA
 constexpr int PT = CT;                        // threads per CTA
 #ifndef Q3_LM_KEEP_PCT
 #define Q3_LM_KEEP_PCT 15
@@ -54,8 +55,8 @@ constexpr int WROW = 1032;                    // elements between weight rows in
                                               // the eight row addresses of an ldmatrix fall into different banks
 constexpr int WOROW = 136;                    // the same for the 128-column Wo slice rows
 constexpr int ATT_WARPS = 8;                  // split attention: warps that attend positions (32 positions per pass)
-// Local attention (every CTA attends its whole head over all cached positions) serves up to 191 positions; measured,
-// splitting the positions over the 18 CTAs of a kv group wins beyond about 200.
+// Local attention (every CTA attends its whole head over all cached positions) serves up to 255 positions; measured,
+// splitting the positions over the 18 CTAs of a kv group wins beyond that.
 #ifndef Q3_N_ACC
 #define Q3_N_ACC 2
 #endif
@@ -136,19 +137,11 @@ __device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
-    asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
-}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
     return ok != 0;
-}
-// global -> shared bulk copy (TMA, no tensor map, no multicast); bytes and both addresses multiples of 16
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* b) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(b)) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -161,15 +154,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 __device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
-__device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
-// barrier among the consumer warps only (the producer warp runs free)
+// barrier of the whole CTA (512 threads)
 __device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
 // ---- counters in global memory: arrive and bounded wait ---------------------------------------------
 __device__ __forceinline__ void counter_arrive(unsigned* cnt) {   // one thread, after a cta_sync
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
 }
-// thread 0 polls until *cnt has reached `target` (wrap-safe), then every consumer passes a cta_sync
+// thread 0 polls until *cnt has reached `target` (wrap-safe), then every thread passes a cta_sync
 __device__ __forceinline__ void counter_wait(const unsigned* cnt, unsigned target, volatile int* abort_flag,
                                              uint32_t* status, uint32_t site) {
     if (threadIdx.x == 0 && !*abort_flag) {
@@ -231,19 +223,6 @@ __device__ __forceinline__ float sum16(const float* red) {
 __device__ __forceinline__ void unpack8f(const uint4& u, float* f) {
     f[0] = bf_lo(u.x); f[1] = bf_hi(u.x); f[2] = bf_lo(u.y); f[3] = bf_hi(u.y);
     f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
-}
-__device__ __forceinline__ void f_unpack16(const uint4& a, const uint4& b, float* f) { unpack8f(a, f); unpack8f(b, f + 8); }
-// dot of one 16-byte weight unit with eight activations held in registers
-__device__ __forceinline__ float dot8r(const uint4& w, const float* x) {
-    float s = bf_lo(w.x) * x[0];
-    s = fmaf(bf_hi(w.x), x[1], s);
-    s = fmaf(bf_lo(w.y), x[2], s);
-    s = fmaf(bf_hi(w.y), x[3], s);
-    s = fmaf(bf_lo(w.z), x[4], s);
-    s = fmaf(bf_hi(w.z), x[5], s);
-    s = fmaf(bf_lo(w.w), x[6], s);
-    s = fmaf(bf_hi(w.w), x[7], s);
-    return s;
 }
 // ---- tensor-core GEMV pieces ------------------------------------------------------------------------
 // y = W x with bf16 W and fp32 x runs on mma.sync.m16n8k16: W tiles are the A operand (ldmatrix from
@@ -426,7 +405,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     //   start of Q  (layer l): down rows of layer l         (43 KB, read in GD)
     //   start of F  (layer l): gate/up rows of layer l      (87 KB, read in GD)
     //   start of GD (layer l): q/k/v rows and Wo slice of layer l + 1   (58 + 31 KB)
-    // The first chunk of a slot arms the slot's mbarrier with the slot's byte count; the consumers wait on it.
+    // The first chunk of a slot arms the slot's mbarrier with the slot's byte count; every warp waits on it before it reads the slot.
     const int bytesA = qmax * WROW * 2, bytesB = WO_ROWS_MAX * WOROW * 2, bytesC = 2 * imax * WROW * 2, bytesD = imax * WROW * 2;
     const bool pumper = tid == 32;
     int pump_armed = 0, pump_parity = 0;                // per slot: armed at all, and the parity of its last armed phase
@@ -447,7 +426,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     fetch_slot(0, 0);
     fetch_slot(1, 0);
 
-    // ================================================================================ consumer warps
+    // ================================================================================ the step
     long long tok = p.token[0];
     if (tok < 0 || tok >= p.vocab) {
         if (tid == 0) report(p.status, ST_BAD_TOKEN, 0, (uint32_t)tok);
