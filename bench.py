@@ -166,7 +166,10 @@ def run_reference_arm(args, rank: int, world: int) -> None:
     line = {"impl": "reference", "metric": "us_per_step_qwen3_0.6b_bs1_ctx128", "value": us, "unit": "us/step",
             "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": us / 1e3,
             "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "bs1 greedy decode from position 128, cache grows on the host", "steps_sampled": steps},
+            "config": {"workload": f"Qwen3-0.6B bs1 greedy decode, {args.steps} consecutive steps from position {CTX0} "
+                                   f"(cache {CTX0 + 1}->{CTX0 + args.steps} positions)",
+                       "sample": f"the first {steps} of those steps on the host cores (fp32 restatement of the reference's CPU path)",
+                       "weights": "bf16 N(0,0.02), RMSNorm gains 1, seed 0"},
             "cpu_baseline": {"value": us, "unit": "us/step", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
                              "kind": "port", "sample": f"{steps} greedy steps from position {CTX0}"},
             "e2e": {"value": us, "unit": "us/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

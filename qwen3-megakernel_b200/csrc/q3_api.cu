@@ -222,14 +222,14 @@ extern "C" int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n)
 static int splits_for(const q3_engine* e, int batch, int max_len) {
     const int n = max_len + 1;
     int by_len = (n + 31) / 32;                                   // at least 32 positions per split
-    // three blocks of the split kernel fit an SM; about three waves of them even out the last, partly filled one
-    // (measured, batch 64 x 1024 positions: 1 / 2 / 3 / 6 / 7 splits 3690 / 3437 / 3439 / 3551 / 3713 us per step)
-    int by_fill = (9 * e->sm_count + KV_HEADS * batch - 1) / (KV_HEADS * batch);
+    // Small batches: about two blocks per SM (more splits only add merge work: batch 8 x 1024 positions, 5 / 10 / 21
+    // splits 1879 / 1918 / 2048 us per step).  Batches that fill the GPU on their own: three blocks of the split kernel
+    // fit an SM, and about three waves of them even out the last, partly filled one (batch 64 x 1024 positions,
+    // 1 / 2 / 3 / 6 / 7 splits: 3690 / 3437 / 3439 / 3551 / 3713 us per step).
+    const int fill_blocks = (KV_HEADS * batch >= e->sm_count ? 9 : 2) * e->sm_count;
+    int by_fill = (fill_blocks + KV_HEADS * batch - 1) / (KV_HEADS * batch);
     int s = by_len < by_fill ? by_len : by_fill;
     if (s < 1) s = 1;
-#ifdef Q3_SPLITS_ENV
-    { static int forced = -1; if (forced < 0) { const char* v = getenv("Q3_ATTN_SPLITS"); forced = v ? atoi(v) : 0; } if (forced > 0) s = forced; }
-#endif
     const int by_chunk = (n + ATTN_CHUNK_MAX - 1) / ATTN_CHUNK_MAX;   // a block's scores must fit its shared memory
     if (s < by_chunk) s = by_chunk;
     if (s > e->max_splits) s = e->max_splits;

@@ -876,8 +876,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     float o = 0.f, Ls = 0.f;
 #pragma unroll
                     for (int w = 0; w < ATT_WARPS; ++w) { o += om[(w * 2 + hh) * 128 + d]; Ls += lw[w * 2 + hh]; }
-                    unsigned long long* dst = p.xp + (size_t)((fg * 2 + hh) * GROUP_CTAS + fj) * XP_STRIDE;
                     const unsigned long long t64 = (unsigned long long)tag << 32;
+                    unsigned long long* dst = p.xp + (size_t)((fg * 2 + hh) * GROUP_CTAS + fj) * XP_STRIDE;
                     asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(dst + 4 + d), "l"(t64 | __float_as_uint(o)) : "memory");
                     __syncwarp();
                     if (d == 127) {   // the (max, sum) pair goes last: it is what the readers poll
