@@ -5,6 +5,7 @@
   run.py bench [--weights hf|synthetic] [--iters N] [--context N] [--grow] [--chains N]
   run.py trace [--context N]            per-phase timing of the persistent kernel (device time stamps)
   run.py batch [--batch B] [--context N] [--steps K] [--plain]   one batched decode step of the layered path
+  run.py prefill [--tokens T] [--reps N]                         causal forward over T random ids
   run.py demo --prompt "..."
 
 `check` verifies what can be verified without a second implementation: the persistent kernel and the
@@ -178,6 +179,33 @@ def cmd_batch(args) -> int:
     return 0
 
 
+def cmd_prefill(args) -> int:
+    """Causal forward over `--tokens` uniform-random ids (tcgen05 GEMMs + tiled attention), timed with CUDA events."""
+    from qwen3mk.kernel import VOCAB
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T = args.tokens
+    w = weights.baseline_init(args.seed, dev)
+    g = torch.Generator().manual_seed(args.seed)
+    ids = torch.randint(0, VOCAB, (T,), generator=g)
+    mk = Megakernel(dev, max_tokens=T, max_positions=max(T + 1, 256))
+    times = []
+    for i in range(args.reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        prefill_mod.prefill(w, ids, dev, engine=mk)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        if i:   # the first call packs the weights and builds the tensor maps
+            times.append(e0.elapsed_time(e1))
+    mk.status()
+    ms = sorted(times)[len(times) // 2]
+    flop = 2.0 * T * 15_728_640 * 28 + 4.0 * 28 * 16 * 128 * (T * (T + 1) / 2)   # projections + causal QK^T and PV
+    print(f"prefill of {T} tokens: {ms:.2f} ms (median of {len(times)}; includes the cache allocation and one synchronisation), "
+          f"{T / ms:.0f} tokens/ms, {flop / ms / 1e9:.0f} TFLOP/s of algorithmic flops")
+    return 0
+
+
 def cmd_demo(args) -> int:
     try:
         tok = prefill_mod.load_tokenizer()
@@ -217,10 +245,14 @@ def main(argv=None) -> int:
     p.add_argument("--steps", type=int, default=20)
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--plain", action="store_true", help="plain launches instead of CUDA-graph replay")
+    p = sub.add_parser("prefill")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--reps", type=int, default=5)
+    p.add_argument("--seed", type=int, default=0)
     p = sub.add_parser("demo")
     p.add_argument("--prompt", default=DEFAULT_PROMPT)
     args = ap.parse_args(argv)
-    return {"check": cmd_check, "bench": cmd_bench, "trace": cmd_trace, "batch": cmd_batch, "demo": cmd_demo}[args.cmd](args)
+    return {"check": cmd_check, "bench": cmd_bench, "trace": cmd_trace, "batch": cmd_batch, "prefill": cmd_prefill, "demo": cmd_demo}[args.cmd](args)
 
 
 if __name__ == "__main__":
