@@ -99,6 +99,35 @@ __device__ __forceinline__ void ld_row8(uint32_t& a, uint32_t& b, const void* pt
                  : "=&r"(a), "=&r"(b) : "l"(ptr), "r"((int)live));
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// The layered path is a chain of short kernels.  Each one lets its successor start launching at once
+// (`pdl_launch`) and itself waits for its predecessor's results only after its own set-up (`pdl_wait`, which
+// returns immediately for a kernel that was launched without the attribute), so that launch latency and
+// prologues overlap the tail of the kernel before.
+#ifndef Q3_PDL
+#define Q3_PDL 1
+#endif
+__device__ __forceinline__ void pdl_launch() {
+#if Q3_PDL
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void pdl_wait() {
+#if Q3_PDL
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = Q3_PDL;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- device status words ----------------------------------------------------------------------
 // [0] error code (0 = fine), [1] phase / site id, [2] CTA index, [3] observed value.
 enum : uint32_t { ST_OK = 0, ST_BARRIER_TIMEOUT = 1, ST_MBAR_TIMEOUT = 2, ST_BAD_TOKEN = 3, ST_PEER_TIMEOUT = 4, ST_BAD_LEN = 5 };

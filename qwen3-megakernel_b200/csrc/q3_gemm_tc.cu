@@ -114,6 +114,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
+    // barriers and the accumulator are set up: from here on the kernel touches what its predecessor produced
+    pdl_launch();
+    pdl_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -281,8 +284,7 @@ static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmT
         attr_set = true;
     }
     dim3 grid((n_rows + TC_BM - 1) / TC_BM, (n_tok + BN - 1) / BN, ksplit);
-    gemm_tc_kernel<BN><<<grid, TC_THREADS, smem, st>>>(tw[0], tw[1], tw[2], tx, p);
-    return cudaGetLastError();
+    return launch_chain(gemm_tc_kernel<BN>, grid, dim3(TC_THREADS), smem, st, tw[0], tw[1], tw[2], tx, p);
 }
 
 // Encoding a tensor map costs a few microseconds of host time; a step issues hundreds of GEMMs over the

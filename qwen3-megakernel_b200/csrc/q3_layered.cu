@@ -25,6 +25,8 @@ namespace q3 {
 __global__ void __launch_bounds__(256) embed_kernel(const long long* __restrict__ token,
                                                     const bf16_raw* __restrict__ embed, int vocab,
                                                     float* __restrict__ x, uint32_t* status) {
+    pdl_launch();
+    pdl_wait();
     const int b = blockIdx.x;
     long long t = token[b];
     if (t < 0 || t >= vocab) {
@@ -213,6 +215,8 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restri
 // (csrc/qwen3_step.cu:597-629; qwen3mk/reference.py:66-75)
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) head_prep_kernel(const HeadPrepArgs a) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float red[4];
     __shared__ float nv[HEAD_DIM];
     const int hb = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
@@ -267,6 +271,8 @@ __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
 //      probabilities from the shared scores, so nothing crosses lanes; eight per-warp sums are added at the end.
 // The new token's own K/V rows are fp32 in `qkv` (not yet rounded into the cache) and are handled by warp 0.
 __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
+    pdl_launch();
+    pdl_wait();
     extern __shared__ __align__(16) float attn_sc[];          // [2][chunk_pad] scores of the chunk
     __shared__ float s_red[2][8], s_l[8][2];
     __shared__ __align__(16) float s_o[8][2][HEAD_DIM];       // 8 KB
@@ -452,6 +458,8 @@ __device__ __forceinline__ void store_planes(bf16_raw* __restrict__ planes, int 
 // attn_merge fused with the split into planes (the input of the Wo GEMM): block (head, plane row)
 __global__ void __launch_bounds__(128) attn_merge_planes_kernel(const float* __restrict__ part, int n_splits, bf16_raw* __restrict__ planes,
                                                                 int plane_rows, int nsplit, int n_tok) {
+    pdl_launch();
+    pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     float v = 0.f;   // padding rows of the token tile are zeros
     if (b < n_tok) {
@@ -473,6 +481,8 @@ __global__ void __launch_bounds__(128) attn_merge_planes_kernel(const float* __r
 // silu(gate) * up fused with the split into planes (the input of the down GEMM): one block per plane row
 __global__ void __launch_bounds__(256) silu_planes_kernel(const float* __restrict__ g, const float* __restrict__ u, bf16_raw* __restrict__ planes,
                                                           int plane_rows, int nsplit, int n_tok) {
+    pdl_launch();
+    pdl_wait();
     const int t = blockIdx.x;
     for (int e = threadIdx.x; e < INTER; e += 256) {
         float v = 0.f;
@@ -488,6 +498,8 @@ __global__ void __launch_bounds__(256) silu_planes_kernel(const float* __restric
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) act_split_kernel(const float* __restrict__ x, int ldx, int K, const bf16_raw* __restrict__ gain,
                                                         bf16_raw* __restrict__ planes, int plane_rows, int nsplit, int n_tok) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float red[8];
     const int t = blockIdx.x, tid = threadIdx.x;
     if (t >= n_tok) {   // padding rows of the token tile
@@ -526,6 +538,8 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
 // argmax of every row of logits [n_tok, vocab]; ties -> lowest index; optional seq_len[t] += 1
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, int vocab, long long* __restrict__ next_token,
                                                           int* seq_len, int append) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float sv[256];
     __shared__ int si[256];
     const int t = blockIdx.x, tid = threadIdx.x;
@@ -563,20 +577,17 @@ cudaError_t launch_prefill_desc(uint64_t* seq_k, uint64_t* seq_v, long long* str
 }
 
 cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gain, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st) {
-    act_split_kernel<<<plane_rows, 256, 0, st>>>(x, ldx, K, gain, planes, plane_rows, nsplit, n_tok);
-    return cudaGetLastError();
+    return launch_chain(act_split_kernel, dim3(plane_rows), dim3(256), 0, st, x, ldx, K, gain, planes, plane_rows, nsplit, n_tok);
 }
 cudaError_t launch_silu_planes(const float* g, const float* u, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st) {
-    silu_planes_kernel<<<plane_rows, 256, 0, st>>>(g, u, planes, plane_rows, nsplit, n_tok);
-    return cudaGetLastError();
+    return launch_chain(silu_planes_kernel, dim3(plane_rows), dim3(256), 0, st, g, u, planes, plane_rows, nsplit, n_tok);
 }
 cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, cudaStream_t st) {
     silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, h, n);
     return cudaGetLastError();
 }
 cudaError_t launch_argmax_rows(const float* logits, int vocab, long long* next_token, int* seq_len, int append, int n_tok, cudaStream_t st) {
-    argmax_rows_kernel<<<n_tok, 256, 0, st>>>(logits, vocab, next_token, seq_len, append);
-    return cudaGetLastError();
+    return launch_chain(argmax_rows_kernel, dim3(n_tok), dim3(256), 0, st, logits, vocab, next_token, seq_len, append);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -612,8 +623,7 @@ cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStrea
 }
 
 cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st) {
-    embed_kernel<<<batch, 256, 0, st>>>(token, embed, vocab, x, status);
-    return cudaGetLastError();
+    return launch_chain(embed_kernel, dim3(batch), dim3(256), 0, st, token, embed, vocab, x, status);
 }
 
 cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st) {
@@ -622,24 +632,20 @@ cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, lo
 }
 
 cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st) {
-    head_prep_kernel<<<dim3(Q_HEADS + KV_HEADS, batch), 128, 0, st>>>(a);
-    return cudaGetLastError();
+    return launch_chain(head_prep_kernel, dim3(Q_HEADS + KV_HEADS, batch), dim3(128), 0, st, a);
 }
 
 // split attention whose merge writes the bf16 planes of the Wo GEMM's input directly
 cudaError_t launch_attn_planes(const AttnArgs& a, bf16_raw* planes, int plane_rows, int nsplit, int batch, cudaStream_t st) {
     if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.chunk_pad > ATTN_CHUNK_MAX) return cudaErrorInvalidValue;
-    attn_split_kernel<<<dim3(a.n_splits, KV_HEADS, batch), 256, (size_t)2 * a.chunk_pad * sizeof(float), st>>>(a);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_chain(attn_split_kernel, dim3(a.n_splits, KV_HEADS, batch), dim3(256), (size_t)2 * a.chunk_pad * sizeof(float), st, a);
     if (e != cudaSuccess) return e;
-    attn_merge_planes_kernel<<<dim3(Q_HEADS, plane_rows), 128, 0, st>>>(a.part, a.n_splits, planes, plane_rows, nsplit, batch);
-    return cudaGetLastError();
+    return launch_chain(attn_merge_planes_kernel, dim3(Q_HEADS, plane_rows), dim3(128), 0, st, a.part, a.n_splits, planes, plane_rows, nsplit, batch);
 }
 
 cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st) {
     if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.chunk_pad > ATTN_CHUNK_MAX) return cudaErrorInvalidValue;
-    attn_split_kernel<<<dim3(a.n_splits, KV_HEADS, batch), 256, (size_t)2 * a.chunk_pad * sizeof(float), st>>>(a);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_chain(attn_split_kernel, dim3(a.n_splits, KV_HEADS, batch), dim3(256), (size_t)2 * a.chunk_pad * sizeof(float), st, a);
     if (e != cudaSuccess) return e;
     attn_merge_kernel<<<dim3(Q_HEADS, batch), 128, 0, st>>>(a.part, a.n_splits, attn_out);
     return cudaGetLastError();
