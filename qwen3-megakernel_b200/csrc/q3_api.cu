@@ -268,7 +268,8 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         GemvArgs g{};
         // qkv = rms(x, ln1) @ [wq; wk; wv]^T
         if (tc) {
-            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln1) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st));
+            const ZeroRows zq{{e->qkv, nullptr}, {QKV_DIM, 0}, {QKV_DIM, 0}};
+            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln1) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st, &zq));
             {   // the three projections in one launch: 32 weight tiles instead of 16 + 8 + 8
                 GemmTcGroupCall c{};
                 c.n_groups = 3;
@@ -276,6 +277,7 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
                 c.w[1] = bf(w.wk) + (size_t)l * KV_DIM * HIDDEN; c.n_rows[1] = KV_DIM; c.out[1] = e->qkv + Q_DIM; c.ldo[1] = QKV_DIM;
                 c.w[2] = bf(w.wv) + (size_t)l * KV_DIM * HIDDEN; c.n_rows[2] = KV_DIM; c.out[2] = e->qkv + Q_DIM + KV_DIM; c.ldo[2] = QKV_DIM;
                 c.x_planes = planes; c.n_tok = B; c.K = HIDDEN; c.nsplit = tc_planes; c.plane_rows = prow; c.status = e->status;
+                c.out_is_zero = 1;   // act_split has cleared the rows
                 LAUNCH(launch_gemm_tc_group(c, st));
             }
         } else {
@@ -317,13 +319,15 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
             // x += attn @ wo^T
             LAUNCH(gemm(bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN, Q_DIM, e->x, HIDDEN, e->x, HIDDEN));
             // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
-            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st));
+            const ZeroRows zf{{e->gate, e->up}, {INTER, INTER}, {INTER, INTER}};
+            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st, &zf));
             {   // gate and up in one launch
                 GemmTcGroupCall c{};
                 c.n_groups = 2;
                 c.w[0] = bf(w.wg) + (size_t)l * INTER * HIDDEN; c.n_rows[0] = INTER; c.out[0] = e->gate; c.ldo[0] = INTER;
                 c.w[1] = bf(w.wu) + (size_t)l * INTER * HIDDEN; c.n_rows[1] = INTER; c.out[1] = e->up; c.ldo[1] = INTER;
                 c.x_planes = planes; c.n_tok = B; c.K = HIDDEN; c.nsplit = tc_planes; c.plane_rows = prow; c.status = e->status;
+                c.out_is_zero = 1;   // act_split has cleared the rows
                 LAUNCH(launch_gemm_tc_group(c, st));
             }
             // x += (silu(gate) * up) @ wd^T

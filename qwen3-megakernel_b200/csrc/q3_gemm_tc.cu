@@ -255,7 +255,7 @@ static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmT
     p.kb_per_split = (nkb + ksplit - 1) / ksplit;
     ksplit = (nkb + p.kb_per_split - 1) / p.kb_per_split;
     if (ksplit > 1) {
-        if (p.epi == TC_EPI_STORE) {   // partial sums are added onto zeros
+        if (p.epi == TC_EPI_STORE && !p.out_is_zero) {   // partial sums are added onto zeros
             const int ng = p.n_groups > 1 ? p.n_groups : 1;
             for (int g = 0; g < ng; ++g) {
                 float* o = p.n_groups > 1 ? p.g_out[g] : p.out;
@@ -345,7 +345,7 @@ cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st) {
     if (!px) return cudaErrorUnknown;
     const CUtensorMap tx = *px;
     p.n_groups = c.n_groups; p.out = c.out[0]; p.resid = nullptr; p.ldo = c.ldo[0]; p.ldr = 0; p.n_rows = rows; p.n_tok = c.n_tok; p.K = c.K;
-    p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = TC_EPI_STORE; p.status = c.status;
+    p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = TC_EPI_STORE; p.status = c.status; p.out_is_zero = c.out_is_zero;
     static int sm_count = 0;
     if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
     if (bn == 32) return launch_bn<32>(maps, tx, p, rows, c.n_tok, sm_count, st);

@@ -22,6 +22,7 @@ struct GemmTcParams {
     int epi;
     uint32_t* status;
     // grouped launches: grid.x tiles [0, g_tiles[0]) belong to matrix 0, the next g_tiles[1] to matrix 1, ...
+    int out_is_zero;       // host side only: skip the memset before a split-K launch
     int n_groups;          // 0 or 1: a single matrix (tm_w0, `out`, `ldo`)
     int g_tiles[3];
     float* g_out[3];
@@ -52,6 +53,7 @@ struct GemmTcGroupCall {
     const void* x_planes;
     int n_tok, K, nsplit, plane_rows;
     uint32_t* status;
+    int out_is_zero;       // the caller has cleared the outputs: a split-K launch adds into them without a memset
 };
 cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st);
 

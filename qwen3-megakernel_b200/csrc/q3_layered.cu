@@ -497,11 +497,17 @@ __global__ void __launch_bounds__(256) silu_planes_kernel(const float* __restric
 // One block per row of the planes; rows >= n_tok (padding of the token tile) are written as zeros.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) act_split_kernel(const float* __restrict__ x, int ldx, int K, const bf16_raw* __restrict__ gain,
-                                                        bf16_raw* __restrict__ planes, int plane_rows, int nsplit, int n_tok) {
+                                                        bf16_raw* __restrict__ planes, int plane_rows, int nsplit, int n_tok, const ZeroRows z) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[8];
     const int t = blockIdx.x, tid = threadIdx.x;
+    // side job: clear token row t of the buffers the split-K GEMM that consumes these planes will add into
+    if (t < n_tok) {
+        for (int i = 0; i < 2; ++i)
+            if (z.ptr[i] != nullptr)
+                for (int e = tid; e < z.cols[i]; e += 256) z.ptr[i][(size_t)t * z.ld[i] + e] = 0.f;
+    }
     if (t >= n_tok) {   // padding rows of the token tile
         for (int e = tid; e < K; e += 256)
             for (int s = 0; s < nsplit; ++s) planes[((size_t)s * plane_rows + t) * K + e] = 0;
@@ -576,8 +582,10 @@ cudaError_t launch_prefill_desc(uint64_t* seq_k, uint64_t* seq_v, long long* str
     return cudaGetLastError();
 }
 
-cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gain, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st) {
-    return launch_chain(act_split_kernel, dim3(plane_rows), dim3(256), 0, st, x, ldx, K, gain, planes, plane_rows, nsplit, n_tok);
+cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gain, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st,
+                             const ZeroRows* zero) {
+    const ZeroRows z = zero ? *zero : ZeroRows{};
+    return launch_chain(act_split_kernel, dim3(plane_rows), dim3(256), 0, st, x, ldx, K, gain, planes, plane_rows, nsplit, n_tok, z);
 }
 cudaError_t launch_silu_planes(const float* g, const float* u, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st) {
     return launch_chain(silu_planes_kernel, dim3(plane_rows), dim3(256), 0, st, g, u, planes, plane_rows, nsplit, n_tok);

@@ -66,7 +66,13 @@ cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st);
 cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st);
 cudaError_t launch_attn_planes(const AttnArgs& a, bf16_raw* planes, int plane_rows, int nsplit, int batch, cudaStream_t st);
 cudaError_t launch_silu_planes(const float* g, const float* u, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st);
-cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gain, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st);
+// up to two fp32 buffers whose first n_tok rows act_split clears on the side (the outputs of the split-K GEMM that follows)
+struct ZeroRows {
+    float* ptr[2];
+    int ld[2], cols[2];
+};
+cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gain, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st,
+                             const ZeroRows* zero = nullptr);
 cudaError_t launch_prefill_desc(uint64_t* seq_k, uint64_t* seq_v, long long* stride, int* len, uint64_t k, uint64_t v, long long s, int n, cudaStream_t st);
 cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, cudaStream_t st);
 cudaError_t launch_argmax_rows(const float* logits, int vocab, long long* next_token, int* seq_len, int append, int n_tok, cudaStream_t st);
