@@ -114,20 +114,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
-    // barriers and the accumulator are set up: from here on the kernel touches what its predecessor produced
+    // Barriers and the accumulator are set up.  The successor may start its own set-up now; this kernel waits for its
+    // predecessor only where it first touches what that one produced: the weights are nobody's output, so their tiles
+    // are requested BEFORE the wait (their HBM latency overlaps the predecessor's tail), the activation planes and
+    // the output stores come after it.
     pdl_launch();
-    pdl_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            const int ahead = min(nkb, stages);   // the first ring of stages: weight tiles before the wait
+            for (int kb = 0; kb < ahead; ++kb) {
+                unsigned char* st = base + (size_t)kb * stage_bytes;
+                asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full_bar[kb])), "r"(stage_bytes) : "memory");
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(tc_smem(st)), "l"(tm_w), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full_bar[kb])) : "memory");
+            }
+            pdl_wait();
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % stages;
                 if (kb >= stages && !tc_wait(&empty_bar[s], ((kb / stages) - 1) & 1, &abort_flag, p.status, 30)) break;
                 unsigned char* st = base + (size_t)s * stage_bytes;
-                asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full_bar[s])), "r"(stage_bytes) : "memory");
-                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(tc_smem(st)), "l"(tm_w), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full_bar[s])) : "memory");
+                if (kb >= ahead) {
+                    asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full_bar[s])), "r"(stage_bytes) : "memory");
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                 ::"r"(tc_smem(st)), "l"(tm_w), "r"((kb_begin + kb) * TC_BK), "r"(m0), "r"(tc_smem(&full_bar[s])) : "memory");
+                }
                 for (int sp = 0; sp < nsplit; ++sp)
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                                  ::"r"(tc_smem(st + a_bytes + sp * b_bytes)), "l"(&tm_x), "r"((kb_begin + kb) * TC_BK), "r"(sp * p.plane_rows + n0),
@@ -167,6 +179,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         const int quad = warp & 3;                      // TMEM lanes [32 quad, 32 quad + 32) belong to this warp
         const bool ok = tc_wait(&acc_bar, 0, &abort_flag, p.status, 32);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        pdl_wait();   // before the first store (the output may be something the predecessor still reads)
         if (ok) {
             const int row = m0 + quad * 32 + lane;      // weight row = output column
 #pragma unroll 1
