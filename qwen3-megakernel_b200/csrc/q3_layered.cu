@@ -478,13 +478,16 @@ __global__ void __launch_bounds__(128) attn_merge_planes_kernel(const float* __r
     store_planes(planes, plane_rows, nsplit, Q_DIM, b, h * HEAD_DIM + d, v);
 }
 
+constexpr int SILU_SLICES = 6;
+static_assert(INTER % SILU_SLICES == 0, "the FFN width must divide into the slices");
 // silu(gate) * up fused with the split into planes (the input of the down GEMM): one block per plane row
 __global__ void __launch_bounds__(256) silu_planes_kernel(const float* __restrict__ g, const float* __restrict__ u, bf16_raw* __restrict__ planes,
                                                           int plane_rows, int nsplit, int n_tok) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
-    for (int e = threadIdx.x; e < INTER; e += 256) {
+    constexpr int SLICE = INTER / SILU_SLICES;   // columns per block: a row is cut into slices so that small batches still fill the GPU
+    for (int e = blockIdx.y * SLICE + threadIdx.x; e < (blockIdx.y + 1) * SLICE; e += 256) {
         float v = 0.f;
         if (t < n_tok) { const float a = g[(size_t)t * INTER + e]; v = (a / (1.f + expf(-a))) * u[(size_t)t * INTER + e]; }
         store_planes(planes, plane_rows, nsplit, INTER, t, e, v);
@@ -588,7 +591,7 @@ cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gai
     return launch_chain(act_split_kernel, dim3(plane_rows), dim3(256), 0, st, x, ldx, K, gain, planes, plane_rows, nsplit, n_tok, z);
 }
 cudaError_t launch_silu_planes(const float* g, const float* u, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st) {
-    return launch_chain(silu_planes_kernel, dim3(plane_rows), dim3(256), 0, st, g, u, planes, plane_rows, nsplit, n_tok);
+    return launch_chain(silu_planes_kernel, dim3(plane_rows, SILU_SLICES), dim3(256), 0, st, g, u, planes, plane_rows, nsplit, n_tok);
 }
 cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, cudaStream_t st) {
     silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, h, n);
