@@ -263,7 +263,13 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         return launch_gemm_tc(c, st);
     };
 
-    LAUNCH(launch_embed(reinterpret_cast<const long long*>(a->token), bf(w.embed), V, e->x, e->status, B, st));
+    // the row argmax of the tensor-core LM head meets in e->pval (64-bit keys) and e->pidx (tickets): both are scratch
+    // of the matrix-vector LM head otherwise, and at least 8 bytes a sequence
+    // (only a decode step of at most max_batch sequences uses them: a prompt's tokens would overrun the buffers)
+    const bool row_argmax = !last_token_only && B <= e->cfg.max_batch;
+    unsigned long long* arg_keys = row_argmax ? reinterpret_cast<unsigned long long*>(e->pval) : nullptr;
+    unsigned* arg_tickets = row_argmax ? reinterpret_cast<unsigned*>(e->pidx) : nullptr;
+    LAUNCH(launch_embed(reinterpret_cast<const long long*>(a->token), bf(w.embed), V, e->x, e->status, B, st, arg_keys, arg_tickets));
     for (int l = 0; l < L; ++l) {
         GemvArgs g{};
         // qkv = rms(x, ln1) @ [wq; wk; wv]^T
@@ -358,11 +364,11 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         }
     }
     // logits = rms(x, fnorm) @ embed^T ; next_token = argmax
-    if (tc && !last_token_only && V % 128 == 0 && (a->logits != nullptr || e->logits_tc != nullptr)) {
+    if (tc && row_argmax && V % 128 == 0 && (a->logits != nullptr || e->logits_tc != nullptr)) {
         float* logits = a->logits ? a->logits : e->logits_tc;
         LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.fnorm), planes, prow, tc_planes, B, st));
         LAUNCH(gemm(bf(w.embed), V, HIDDEN, logits, V, nullptr, 0));
-        LAUNCH(launch_argmax_rows(logits, V, reinterpret_cast<long long*>(a->next_token), a->seq_len, append, B, st));
+        LAUNCH(launch_argmax_rows(logits, V, reinterpret_cast<long long*>(a->next_token), a->seq_len, append, B, st, arg_keys, arg_tickets));
     } else {
         // matrix-vector LM head: every sequence, or only the last token of a prompt
         const int nb = last_token_only ? 1 : B;

@@ -258,11 +258,15 @@ static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmT
     const int nkb = p.K / TC_BK;
     const int tiles = ((n_rows + TC_BM - 1) / TC_BM) * ((n_tok + BN - 1) / BN);
     // Few output tiles (decode batches, short prompts) cannot fill the GPU: slice K so that about one
-    // CTA per SM streams weights, at least four k blocks per slice to keep the pipeline busy.
+    // CTA per SM streams weights, at least two k blocks per slice.
     int ksplit = 1;
     if (tiles < sm_count && (p.epi == TC_EPI_STORE || p.resid == p.out)) {
         ksplit = sm_count / tiles;
-        if (ksplit > nkb / 4) ksplit = nkb / 4;
+        int min_kb = 2;   // k blocks per slice at least (measured, batch 64 / batch 8 steps: 2 -> 3077 / 1433 us, 4 -> 3121 / 1477, 8 -> 3366 / 1760)
+#ifdef Q3_KSPLIT_ENV
+        { static int v = -1; if (v < 0) { const char* t = getenv("Q3_MIN_KB"); v = t ? atoi(t) : 4; } min_kb = v; }
+#endif
+        if (ksplit > nkb / min_kb) ksplit = nkb / min_kb;
         if (ksplit < 1) ksplit = 1;
     }
     p.kb_per_split = (nkb + ksplit - 1) / ksplit;

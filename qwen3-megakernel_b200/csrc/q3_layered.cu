@@ -24,10 +24,12 @@ namespace q3 {
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) embed_kernel(const long long* __restrict__ token,
                                                     const bf16_raw* __restrict__ embed, int vocab,
-                                                    float* __restrict__ x, uint32_t* status) {
+                                                    float* __restrict__ x, uint32_t* status,
+                                                    unsigned long long* argmax_keys, unsigned* argmax_tickets) {
     pdl_launch();
     pdl_wait();
     const int b = blockIdx.x;
+    if (threadIdx.x == 0 && argmax_keys != nullptr) { argmax_keys[b] = 0ull; argmax_tickets[b] = 0u; }   // for the step's row argmax
     long long t = token[b];
     if (t < 0 || t >= vocab) {
         if (threadIdx.x == 0) report(status, ST_BAD_TOKEN, 0, (uint32_t)t);
@@ -545,17 +547,23 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const float* __restrict__
 }
 
 // argmax of every row of logits [n_tok, vocab]; ties -> lowest index; optional seq_len[t] += 1
+// Block (row t, slice y) scans its slice of the row; the slices meet in a 64-bit key per row that orders by value,
+// then by lowest index (atomicMax), and the last slice of a row to finish writes the token.  `keys` and `tickets`
+// are cleared by the step's first kernel (embed_kernel).
+constexpr int ARGMAX_SLICES = 16;
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restrict__ logits, int vocab, long long* __restrict__ next_token,
-                                                          int* seq_len, int append) {
+                                                          int* seq_len, int append, unsigned long long* keys, unsigned* tickets) {
     pdl_launch();
     pdl_wait();
     __shared__ float sv[256];
     __shared__ int si[256];
     const int t = blockIdx.x, tid = threadIdx.x;
+    const int chunk = (vocab + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+    const int i0 = blockIdx.y * chunk, i1 = min(vocab, i0 + chunk);
     const float* row = logits + (size_t)t * vocab;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < vocab; i += 256) {
+    for (int i = i0 + tid; i < i1; i += 256) {
         const float v = row[i];
         if (v > bv) { bv = v; bi = i; }
     }
@@ -570,8 +578,18 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const float* __restric
         __syncthreads();
     }
     if (tid == 0) {
-        next_token[t] = si[0];
-        if (append) seq_len[t] += 1;
+        if (si[0] != 0x7fffffff) {
+            const unsigned bits = __float_as_uint(sv[0]);
+            const unsigned ord = bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);   // monotonic in the float's value
+            atomicMax(&keys[t], ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (unsigned)si[0]));
+        }
+        __threadfence();
+        if (atomicAdd(&tickets[t], 1u) == ARGMAX_SLICES - 1) {
+            __threadfence();
+            const unsigned long long k = atomicMax(&keys[t], 0ull);
+            next_token[t] = (long long)(0xffffffffu - (unsigned)(k & 0xffffffffull));
+            if (append) seq_len[t] += 1;
+        }
     }
 }
 
@@ -597,8 +615,9 @@ cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, 
     silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, h, n);
     return cudaGetLastError();
 }
-cudaError_t launch_argmax_rows(const float* logits, int vocab, long long* next_token, int* seq_len, int append, int n_tok, cudaStream_t st) {
-    return launch_chain(argmax_rows_kernel, dim3(n_tok), dim3(256), 0, st, logits, vocab, next_token, seq_len, append);
+cudaError_t launch_argmax_rows(const float* logits, int vocab, long long* next_token, int* seq_len, int append, int n_tok, cudaStream_t st,
+                               unsigned long long* keys, unsigned* tickets) {
+    return launch_chain(argmax_rows_kernel, dim3(n_tok, ARGMAX_SLICES), dim3(256), 0, st, logits, vocab, next_token, seq_len, append, keys, tickets);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -633,8 +652,9 @@ cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStrea
     return cudaErrorInvalidValue;
 }
 
-cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st) {
-    return launch_chain(embed_kernel, dim3(batch), dim3(256), 0, st, token, embed, vocab, x, status);
+cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st,
+                         unsigned long long* argmax_keys, unsigned* argmax_tickets) {
+    return launch_chain(embed_kernel, dim3(batch), dim3(256), 0, st, token, embed, vocab, x, status, argmax_keys, argmax_tickets);
 }
 
 cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st) {

@@ -60,7 +60,8 @@ struct AttnArgs {
 };
 
 cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStream_t st);
-cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st);
+cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st,
+                         unsigned long long* argmax_keys = nullptr, unsigned* argmax_tickets = nullptr);
 cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st);
 cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st);
 cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st);
@@ -75,6 +76,7 @@ cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gai
                              const ZeroRows* zero = nullptr);
 cudaError_t launch_prefill_desc(uint64_t* seq_k, uint64_t* seq_v, long long* stride, int* len, uint64_t k, uint64_t v, long long s, int n, cudaStream_t st);
 cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, cudaStream_t st);
-cudaError_t launch_argmax_rows(const float* logits, int vocab, long long* next_token, int* seq_len, int append, int n_tok, cudaStream_t st);
+cudaError_t launch_argmax_rows(const float* logits, int vocab, long long* next_token, int* seq_len, int append, int n_tok, cudaStream_t st,
+                               unsigned long long* keys, unsigned* tickets);
 
 }  // namespace q3

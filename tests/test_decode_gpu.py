@@ -180,7 +180,7 @@ def test_rebound_launches_are_stable(oracle, small, path):
     assert 0 <= int(mk.chain_token) < 4096
 
 
-@pytest.mark.parametrize("T", [5, 37, 64, 200])
+@pytest.mark.parametrize("T", [5, 37, 64, 200, 700])
 def test_prefill_matches_oracle(oracle, small, T):
     """T < 9: matrix-vector kernels; T >= 9: tcgen05 GEMMs; T >= 64: the tiled causal attention kernel."""
     from qwen3mk import prefill
