@@ -300,13 +300,18 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         h.k_write = reinterpret_cast<bf16_raw*>(a->k_write); h.v_write = reinterpret_cast<bf16_raw*>(a->v_write);
         h.seq_k = a->seq_k; h.seq_v = a->seq_v; h.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
         h.layer = l; h.n_layers = L; h.append = append;
-        LAUNCH(launch_head_prep(h, B, st));
+        // A prompt's tokens attend rows that earlier tokens of the same launch append: those need the separate kernel.
+        // A decode step prepares the heads inside the attention kernel (one launch less per layer).
+        const bool fused_prep = prompt == nullptr;
+        if (!fused_prep) LAUNCH(launch_head_prep(h, B, st));
 
         AttnArgs t{};
         t.qkv = e->qkv; t.seq_k = a->seq_k; t.seq_v = a->seq_v;
         t.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
         t.seq_len = a->seq_len; t.part = e->part; t.layer = l; t.n_splits = ns;
         t.chunk_pad = (((a->max_len + 1 + ns - 1) / ns) + 31) / 32 * 32;
+        t.fused_prep = fused_prep ? 1 : 0; t.qn = h.qn; t.kn = h.kn; t.rope = h.rope; t.k_write = h.k_write; t.v_write = h.v_write;
+        t.n_layers = L; t.append = append;
         if (prompt != nullptr && B >= 64) {
             // a prompt: tiled causal attention over the rows head_prep has just written into the cache
             const bf16_raw* kc = bf(prompt->kcache) + (size_t)l * prompt->layer_stride;

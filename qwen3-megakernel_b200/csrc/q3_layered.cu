@@ -294,6 +294,50 @@ __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
     const float* qkv = a.qkv + (size_t)b * QKV_DIM;
     const bf16_raw* kbase = reinterpret_cast<const bf16_raw*>(a.seq_k[b]) + (size_t)a.layer * a.seq_layer_stride[b] + g * HEAD_DIM;
     const bf16_raw* vbase = reinterpret_cast<const bf16_raw*>(a.seq_v[b]) + (size_t)a.layer * a.seq_layer_stride[b] + g * HEAD_DIM;
+    // the two q heads, the k row and the v row of the new token: as prepared by head_prep_kernel, or prepared here
+    __shared__ __align__(16) float s_new[4][HEAD_DIM];
+    const float* q0p = qkv + (2 * g) * HEAD_DIM;
+    const float* q1p = qkv + (2 * g + 1) * HEAD_DIM;
+    const float* knp = qkv + Q_DIM + g * HEAD_DIM;
+    const float* vnp = qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
+    if (a.fused_prep) {
+        if (warp < 4) {   // warp r: q head 2g, q head 2g + 1, k, v; four dims a lane
+            const float* src = warp == 0 ? q0p : warp == 1 ? q1p : warp == 2 ? knp : vnp;
+            const float4 v4 = *reinterpret_cast<const float4*>(src + lane * 4);
+            float v[4] = {v4.x, v4.y, v4.z, v4.w};
+            if (warp < 3) {
+                float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float r = rsqrtf(ss / (float)HEAD_DIM + EPS);
+                const bf16_raw* gain = (warp < 2 ? a.qn : a.kn) + (size_t)a.layer * HEAD_DIM + lane * 4;
+                const float* tab = a.rope + (size_t)len * HEAD_DIM;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float nrm = (v[i] * r) * bf_to_f(gain[i]);
+                    const float partner = __shfl_xor_sync(0xffffffffu, nrm, 16);   // dim d +- 64 sits 16 lanes away
+                    const float rot = (lane < 16) ? -partner : partner;
+                    const int d = (lane * 4 + i) & 63;
+                    v[i] = nrm * tab[d] + rot * tab[64 + d];
+                }
+            }
+            *reinterpret_cast<float4*>(&s_new[warp][lane * 4]) = make_float4(v[0], v[1], v[2], v[3]);
+            if (warp >= 2 && sp == 0) {   // one block per (sequence, kv head) stores the new rows, rounded to bf16
+                bf16_raw* wr = warp == 2 ? a.k_write : a.v_write;
+                const size_t wofs = (((size_t)b * a.n_layers + a.layer) * KV_HEADS + g) * HEAD_DIM + lane * 4;
+                uint2 pk;
+                pk.x = (uint32_t)f_to_bf(v[0]) | ((uint32_t)f_to_bf(v[1]) << 16);
+                pk.y = (uint32_t)f_to_bf(v[2]) | ((uint32_t)f_to_bf(v[3]) << 16);
+                if (wr) *reinterpret_cast<uint2*>(wr + wofs) = pk;
+                if (a.append) {
+                    bf16_raw* cache = reinterpret_cast<bf16_raw*>(warp == 2 ? a.seq_k[b] : a.seq_v[b]);
+                    *reinterpret_cast<uint2*>(cache + (size_t)a.layer * a.seq_layer_stride[b] + (size_t)len * KV_DIM + g * HEAD_DIM + lane * 4) = pk;
+                }
+            }
+        }
+        __syncthreads();
+        q0p = s_new[0]; q1p = s_new[1]; knp = s_new[2]; vnp = s_new[3];
+    }
 
     // ---------------------------------------------------------------- pass 1: scores
     float tmax0 = -INFINITY, tmax1 = -INFINITY;
@@ -301,7 +345,7 @@ __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
         float q[2][16];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-            const float* qp = qkv + (2 * g + hh) * HEAD_DIM;
+            const float* qp = hh ? q1p : q0p;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 q[hh][i] = qp[sub * 8 + i] * ATTN_SCALE;
@@ -347,9 +391,9 @@ __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
             score(it + 2, kc0, kc1);
         }
         if (has_new && warp == 0) {   // q . k_new in fp32, four dims a lane
-            const float4 kn = *reinterpret_cast<const float4*>(qkv + Q_DIM + g * HEAD_DIM + lane * 4);
-            const float4 q0 = *reinterpret_cast<const float4*>(qkv + (2 * g) * HEAD_DIM + lane * 4);
-            const float4 q1 = *reinterpret_cast<const float4*>(qkv + (2 * g + 1) * HEAD_DIM + lane * 4);
+            const float4 kn = *reinterpret_cast<const float4*>(knp + lane * 4);
+            const float4 q0 = *reinterpret_cast<const float4*>(q0p + lane * 4);
+            const float4 q1 = *reinterpret_cast<const float4*>(q1p + lane * 4);
             float s0 = (q0.x * kn.x + q0.y * kn.y + q0.z * kn.z + q0.w * kn.w) * ATTN_SCALE;
             float s1 = (q1.x * kn.x + q1.y * kn.y + q1.z * kn.z + q1.w * kn.w) * ATTN_SCALE;
 #pragma unroll
@@ -407,7 +451,7 @@ __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
             accumulate(bt + 1, vb);
         }
         if (has_new && warp == 0) {   // the new token's V row in fp32
-            const float4 vn = *reinterpret_cast<const float4*>(qkv + Q_DIM + KV_DIM + g * HEAD_DIM + lane * 4);
+            const float4 vn = *reinterpret_cast<const float4*>(vnp + lane * 4);
             const float pr0 = __expf(sc0[len - p0] - M0), pr1 = __expf(sc1[len - p0] - M1);
             l0 += pr0; l1 += pr1;
             acc[0][0] = fmaf(pr0, vn.x, acc[0][0]); acc[0][1] = fmaf(pr0, vn.y, acc[0][1]); acc[0][2] = fmaf(pr0, vn.z, acc[0][2]); acc[0][3] = fmaf(pr0, vn.w, acc[0][3]);

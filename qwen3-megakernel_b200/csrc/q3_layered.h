@@ -57,6 +57,15 @@ struct AttnArgs {
     float* part;                      // [batch, 16, n_splits, ATTN_PART_STRIDE]
     int layer, n_splits;
     int chunk_pad;                    // positions per split, rounded up to 32: what the host's length bound allows (<= ATTN_CHUNK_MAX)
+    // fused head preparation (decode steps): `qkv` holds the raw projections and every block normalises and rotates the
+    // q heads and the k row of its (sequence, kv head) itself; the block of split 0 stores the new K/V rows
+    int fused_prep;                   // 0: qkv was prepared by head_prep_kernel
+    const bf16_raw* qn;
+    const bf16_raw* kn;
+    const float* rope;
+    bf16_raw* k_write;
+    bf16_raw* v_write;
+    int n_layers, append;
 };
 
 cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStream_t st);
