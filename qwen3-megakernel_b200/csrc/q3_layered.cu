@@ -377,18 +377,22 @@ __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
             }
         };
         const int iters = (pc - p0 + 31) / 32;                // block-uniform
-        uint4 ka0, ka1, kb0, kb1, kc0, kc1;                   // three iterations of rows in flight
+        uint4 ka0, ka1, kb0, kb1, kc0, kc1, kd0, kd1;         // four iterations of rows in flight
         request(0, ka0, ka1);
         request(1, kb0, kb1);
-        for (int it = 0; it < iters; it += 3) {
-            request(it + 2, kc0, kc1);
+        request(2, kc0, kc1);
+        for (int it = 0; it < iters; it += 4) {
+            request(it + 3, kd0, kd1);
             score(it, ka0, ka1);
             if (it + 1 >= iters) break;
-            request(it + 3, ka0, ka1);
+            request(it + 4, ka0, ka1);
             score(it + 1, kb0, kb1);
             if (it + 2 >= iters) break;
-            request(it + 4, kb0, kb1);
+            request(it + 5, kb0, kb1);
             score(it + 2, kc0, kc1);
+            if (it + 3 >= iters) break;
+            request(it + 6, kc0, kc1);
+            score(it + 3, kd0, kd1);
         }
         if (has_new && warp == 0) {   // q . k_new in fp32, four dims a lane
             const float4 kn = *reinterpret_cast<const float4*>(knp + lane * 4);
