@@ -291,6 +291,9 @@ static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmT
     int stages = (int)((200u * 1024u) / stage_bytes);
     if (stages > 8) stages = 8;
     if (stages > p.kb_per_split) stages = p.kb_per_split;
+    // Grids of more than two tiles per SM (prompts): two stages, so that two CTAs share an SM and the epilogue of one
+    // overlaps the MMAs of the other (measured, prefill of 2048 tokens: 14.0 ms against 15.6 ms with four stages).
+    if (tiles * ksplit > 2 * sm_count && stages > 2) stages = 2;
     if (stages < 1) return cudaErrorInvalidValue;
     p.stages = stages;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
