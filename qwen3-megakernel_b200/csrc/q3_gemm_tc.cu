@@ -260,12 +260,14 @@ static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmT
     // Few output tiles (decode batches, short prompts) cannot fill the GPU: slice K so that about one
     // CTA per SM streams weights, at least two k blocks per slice.
     int ksplit = 1;
-    if (tiles < sm_count && (p.epi == TC_EPI_STORE || p.resid == p.out)) {
-        ksplit = sm_count / tiles;
+    // CTAs per SM the split aims at.  Measured with 1 / 2 / 3: prefill of 2048 tokens 13.9 / 11.2 / 10.9 ms (the Wo and
+    // down launches have 128 tiles of long K: one wave of long serial CTAs unless K is cut), batch-8 decode step
+    // 1322 / 1250 / 1249 us, batch 64 3017 / 3031 / 3000 us; a prompt of 128 tokens (one 128-token tile) is the
+    // exception: 1.70 / 1.86 / 1.82 ms.
+    const int fill = (n_tok > 64 && n_tok < 256) ? 1 : 3;
+    if (tiles < fill * sm_count && (p.epi == TC_EPI_STORE || p.resid == p.out)) {
+        ksplit = fill * sm_count / tiles;
         int min_kb = 2;   // k blocks per slice at least (measured, batch 64 / batch 8 steps: 2 -> 3077 / 1433 us, 4 -> 3121 / 1477, 8 -> 3366 / 1760)
-#ifdef Q3_KSPLIT_ENV
-        { static int v = -1; if (v < 0) { const char* t = getenv("Q3_MIN_KB"); v = t ? atoi(t) : 4; } min_kb = v; }
-#endif
         if (ksplit > nkb / min_kb) ksplit = nkb / min_kb;
         if (ksplit < 1) ksplit = 1;
     }
