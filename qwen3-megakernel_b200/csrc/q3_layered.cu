@@ -216,37 +216,46 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float* __restri
 // grid (24, B): blocks 0..15 = q heads, 16..23 = kv heads.  128 threads = head dims.
 // (csrc/qwen3_step.cu:597-629; qwen3mk/reference.py:66-75)
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) head_prep_kernel(const HeadPrepArgs a) {
+// A warp per 128-dim vector (16 q heads, then 8 k heads, of one token), four dims a lane: RMSNorm with the head gain,
+// RoPE (dim d pairs with d +- 64, i.e. the lane 16 away), in place; the k-head warps also store the new K and V rows.
+__global__ void __launch_bounds__(256) head_prep_kernel(const HeadPrepArgs a) {
     pdl_launch();
     pdl_wait();
-    __shared__ float red[4];
-    __shared__ float nv[HEAD_DIM];
-    const int hb = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int hb = blockIdx.x * 8 + (threadIdx.x >> 5), b = blockIdx.y;   // 3 blocks of 8 warps cover the 24 vectors
     const bool is_q = hb < Q_HEADS;
     const int g = hb - Q_HEADS;
-    float* src = a.qkv + (size_t)b * QKV_DIM + (is_q ? hb * HEAD_DIM : Q_DIM + g * HEAD_DIM);
-    const bf16_raw* gain = (is_q ? a.qn : a.kn) + (size_t)a.layer * HEAD_DIM;
+    float* src = a.qkv + (size_t)b * QKV_DIM + (is_q ? hb * HEAD_DIM : Q_DIM + g * HEAD_DIM) + lane * 4;
+    const bf16_raw* gain = (is_q ? a.qn : a.kn) + (size_t)a.layer * HEAD_DIM + lane * 4;
     const int pos = a.seq_len[b];
-    const float v = src[d];
-    const float ss = block_sum<4>(v * v, red);
-    const float n = (v * rsqrtf(ss / (float)HEAD_DIM + EPS)) * bf_to_f(gain[d]);
-    nv[d] = n;
-    __syncthreads();
+    const float4 v4 = *reinterpret_cast<const float4*>(src);
+    float v[4] = {v4.x, v4.y, v4.z, v4.w};
+    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float r = rsqrtf(ss / (float)HEAD_DIM + EPS);
     const float* tab = a.rope + (size_t)pos * HEAD_DIM;
-    const float c = tab[d & 63], s = tab[64 + (d & 63)];
-    const float rot = (d < 64) ? -nv[d + 64] : nv[d - 64];
-    const float o = n * c + rot * s;
-    src[d] = o;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float n = (v[i] * r) * bf_to_f(gain[i]);
+        const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
+        const float rot = (lane < 16) ? -partner : partner;
+        const int d = (lane * 4 + i) & 63;
+        v[i] = n * tab[d] + rot * tab[64 + d];
+    }
+    *reinterpret_cast<float4*>(src) = make_float4(v[0], v[1], v[2], v[3]);
     if (!is_q) {
-        const float vv = a.qkv[(size_t)b * QKV_DIM + Q_DIM + KV_DIM + g * HEAD_DIM + d];
-        const bf16_raw kb = f_to_bf(o), vb = f_to_bf(vv);
-        const size_t wofs = (((size_t)b * a.n_layers + a.layer) * KV_HEADS + g) * HEAD_DIM + d;
-        if (a.k_write) a.k_write[wofs] = kb;
-        if (a.v_write) a.v_write[wofs] = vb;
+        const float4 vv = *reinterpret_cast<const float4*>(a.qkv + (size_t)b * QKV_DIM + Q_DIM + KV_DIM + g * HEAD_DIM + lane * 4);
+        uint2 kb, vb;
+        kb.x = (uint32_t)f_to_bf(v[0]) | ((uint32_t)f_to_bf(v[1]) << 16); kb.y = (uint32_t)f_to_bf(v[2]) | ((uint32_t)f_to_bf(v[3]) << 16);
+        vb.x = (uint32_t)f_to_bf(vv.x) | ((uint32_t)f_to_bf(vv.y) << 16); vb.y = (uint32_t)f_to_bf(vv.z) | ((uint32_t)f_to_bf(vv.w) << 16);
+        const size_t wofs = (((size_t)b * a.n_layers + a.layer) * KV_HEADS + g) * HEAD_DIM + lane * 4;
+        if (a.k_write) *reinterpret_cast<uint2*>(a.k_write + wofs) = kb;
+        if (a.v_write) *reinterpret_cast<uint2*>(a.v_write + wofs) = vb;
         if (a.append) {
-            const size_t cofs = (size_t)a.layer * a.seq_layer_stride[b] + (size_t)pos * KV_DIM + g * HEAD_DIM + d;
-            reinterpret_cast<bf16_raw*>(a.seq_k[b])[cofs] = kb;
-            reinterpret_cast<bf16_raw*>(a.seq_v[b])[cofs] = vb;
+            const size_t cofs = (size_t)a.layer * a.seq_layer_stride[b] + (size_t)pos * KV_DIM + g * HEAD_DIM + lane * 4;
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16_raw*>(a.seq_k[b]) + cofs) = kb;
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16_raw*>(a.seq_v[b]) + cofs) = vb;
         }
     }
 }
@@ -711,7 +720,8 @@ cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, lo
 }
 
 cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st) {
-    return launch_chain(head_prep_kernel, dim3(Q_HEADS + KV_HEADS, batch), dim3(128), 0, st, a);
+    static_assert((Q_HEADS + KV_HEADS) % 8 == 0, "a block takes eight of the head vectors");
+    return launch_chain(head_prep_kernel, dim3((Q_HEADS + KV_HEADS) / 8, batch), dim3(256), 0, st, a);
 }
 
 // split attention whose merge writes the bf16 planes of the Wo GEMM's input directly
