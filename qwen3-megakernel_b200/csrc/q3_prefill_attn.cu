@@ -31,14 +31,21 @@ struct PrefillAttnArgs {
     const bf16_raw* vcache;
     float* attn;             // [T, 2048]
     int T;
+    int paired;              // the grid has half as many blocks as query tiles (long prompts)
 };
 
 __global__ void __launch_bounds__(128) prefill_attn_kernel(const PrefillAttnArgs a) {
     __shared__ __align__(16) bf16_raw sK[64 * PA_ROW];
     __shared__ __align__(16) bf16_raw sV[64 * PA_ROW];
-    const int qt = blockIdx.x, h = blockIdx.y, kvh = h >> 1;
+    const int h = blockIdx.y, kvh = h >> 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, q4 = lane & 3;
+    // Causal work grows with the query tile's index: a block takes tile i and then tile n - 1 - i, so that every block
+    // walks n + 1 key tiles and the grid is one even wave instead of two ragged ones.
+    const int n_qt = (a.T + 63) / 64;
+    for (int pass = 0; pass < 2; ++pass) {
+    const int qt = pass ? n_qt - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    if (pass && (!a.paired || qt <= (int)blockIdx.x)) break;   // unpaired grid; or the middle tile of an odd count, done in pass 0
     const int row0 = qt * 64 + warp * 16 + g, row1 = row0 + 8;   // this thread's two query rows
 
     // ---- Q fragments, scaled, as hi + lo bf16 ----
@@ -147,11 +154,14 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(const PrefillAttnArgs
         if (row0 < a.T) *reinterpret_cast<float2*>(a.attn + (size_t)row0 * Q_DIM + h * HEAD_DIM + 8 * n + 2 * q4) = make_float2(o[n][0] * i0, o[n][1] * i0);
         if (row1 < a.T) *reinterpret_cast<float2*>(a.attn + (size_t)row1 * Q_DIM + h * HEAD_DIM + 8 * n + 2 * q4) = make_float2(o[n][2] * i1, o[n][3] * i1);
     }
+    }   // pass
 }
 
 cudaError_t launch_prefill_attn(const float* qkv, const void* kcache_layer, const void* vcache_layer, float* attn, int T, cudaStream_t st) {
-    PrefillAttnArgs a{qkv, reinterpret_cast<const bf16_raw*>(kcache_layer), reinterpret_cast<const bf16_raw*>(vcache_layer), attn, T};
-    prefill_attn_kernel<<<dim3((T + 63) / 64, Q_HEADS), 128, 0, st>>>(a);
+    const int n_qt = (T + 63) / 64;
+    const int paired = n_qt >= 16 ? 1 : 0;   // short prompts need every tile as a block of its own to fill the GPU
+    PrefillAttnArgs a{qkv, reinterpret_cast<const bf16_raw*>(kcache_layer), reinterpret_cast<const bf16_raw*>(vcache_layer), attn, T, paired};
+    prefill_attn_kernel<<<dim3(paired ? (n_qt + 1) / 2 : n_qt, Q_HEADS), 128, 0, st>>>(a);
     return cudaGetLastError();
 }
 
