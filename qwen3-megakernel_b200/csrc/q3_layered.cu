@@ -514,6 +514,20 @@ __device__ __forceinline__ void store_planes(bf16_raw* __restrict__ planes, int 
     }
 }
 
+// the same for two neighbouring elements (e even): one 32-bit store per plane
+__device__ __forceinline__ void store_planes2(bf16_raw* __restrict__ planes, int plane_rows, int nsplit, int K, int t, int e, float v0, float v1) {
+    const bf16_raw h0 = f_to_bf(v0), h1 = f_to_bf(v1);
+    *reinterpret_cast<uint32_t*>(planes + (size_t)t * K + e) = (uint32_t)h0 | ((uint32_t)h1 << 16);
+    if (nsplit > 1) {
+        const float r0 = v0 - bf_to_f(h0), r1 = v1 - bf_to_f(h1);
+        const bf16_raw m0 = f_to_bf(r0), m1 = f_to_bf(r1);
+        *reinterpret_cast<uint32_t*>(planes + ((size_t)plane_rows + t) * K + e) = (uint32_t)m0 | ((uint32_t)m1 << 16);
+        if (nsplit > 2)
+            *reinterpret_cast<uint32_t*>(planes + ((size_t)2 * plane_rows + t) * K + e) =
+                (uint32_t)f_to_bf(r0 - bf_to_f(m0)) | ((uint32_t)f_to_bf(r1 - bf_to_f(m1)) << 16);
+    }
+}
+
 // attn_merge fused with the split into planes (the input of the Wo GEMM): block (head, plane row)
 __global__ void __launch_bounds__(128) attn_merge_planes_kernel(const float* __restrict__ part, int n_splits, bf16_raw* __restrict__ planes,
                                                                 int plane_rows, int nsplit, int n_tok) {
@@ -538,18 +552,21 @@ __global__ void __launch_bounds__(128) attn_merge_planes_kernel(const float* __r
 }
 
 constexpr int SILU_SLICES = 6;
-static_assert(INTER % SILU_SLICES == 0, "the FFN width must divide into the slices");
+static_assert(INTER % (2 * SILU_SLICES) == 0, "the FFN width must divide into slices of an even width");
 // silu(gate) * up fused with the split into planes (the input of the down GEMM): one block per plane row
 __global__ void __launch_bounds__(256) silu_planes_kernel(const float* __restrict__ g, const float* __restrict__ u, bf16_raw* __restrict__ planes,
                                                           int plane_rows, int nsplit, int n_tok) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
-    constexpr int SLICE = INTER / SILU_SLICES;   // columns per block: a row is cut into slices so that small batches still fill the GPU
-    for (int e = blockIdx.y * SLICE + threadIdx.x; e < (blockIdx.y + 1) * SLICE; e += 256) {
-        float v = 0.f;
-        if (t < n_tok) { const float a = g[(size_t)t * INTER + e]; v = (a / (1.f + expf(-a))) * u[(size_t)t * INTER + e]; }
-        store_planes(planes, plane_rows, nsplit, INTER, t, e, v);
+    const int slice = INTER / (int)gridDim.y;    // columns per block: a row is cut into slices so that small batches still fill the GPU
+    for (int e = blockIdx.y * slice + 2 * threadIdx.x; e < (blockIdx.y + 1) * slice; e += 512) {   // two elements a thread
+        float v0 = 0.f, v1 = 0.f;
+        if (t < n_tok) {
+            const float2 a = *reinterpret_cast<const float2*>(g + (size_t)t * INTER + e), b = *reinterpret_cast<const float2*>(u + (size_t)t * INTER + e);
+            v0 = (a.x / (1.f + expf(-a.x))) * b.x; v1 = (a.y / (1.f + expf(-a.y))) * b.y;
+        }
+        store_planes2(planes, plane_rows, nsplit, INTER, t, e, v0, v1);
     }
 }
 
@@ -568,32 +585,29 @@ __global__ void __launch_bounds__(256) act_split_kernel(const float* __restrict_
     if (t < n_tok) {
         for (int i = 0; i < 2; ++i)
             if (z.ptr[i] != nullptr)
-                for (int e = tid; e < z.cols[i]; e += 256) z.ptr[i][(size_t)t * z.ld[i] + e] = 0.f;
+                for (int e = 4 * tid; e < z.cols[i]; e += 1024)   // widths and pitches are multiples of four floats
+                    *reinterpret_cast<float4*>(z.ptr[i] + (size_t)t * z.ld[i] + e) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (t >= n_tok) {   // padding rows of the token tile
-        for (int e = tid; e < K; e += 256)
-            for (int s = 0; s < nsplit; ++s) planes[((size_t)s * plane_rows + t) * K + e] = 0;
+        for (int e = 2 * tid; e < K; e += 512) store_planes2(planes, plane_rows, nsplit, K, t, e, 0.f, 0.f);
         return;
     }
+    // two neighbouring elements a thread (K is even): 8-byte loads, one 32-bit store per plane
     const float* row = x + (size_t)t * ldx;
     float r = 1.f;
     if (gain != nullptr) {
         float ss = 0.f;
-        for (int e = tid; e < K; e += 256) { const float v = row[e]; ss = fmaf(v, v, ss); }
+        for (int e = 2 * tid; e < K; e += 512) { const float2 v = *reinterpret_cast<const float2*>(row + e); ss = fmaf(v.x, v.x, fmaf(v.y, v.y, ss)); }
         ss = block_sum<8>(ss, red);
         r = rsqrtf(ss / (float)K + EPS);
     }
-    for (int e = tid; e < K; e += 256) {
-        float v = row[e];
-        if (gain != nullptr) v = (v * r) * bf_to_f(gain[e]);
-        const bf16_raw h = f_to_bf(v);
-        planes[(size_t)t * K + e] = h;
-        if (nsplit > 1) {
-            const float r1 = v - bf_to_f(h);
-            const bf16_raw m = f_to_bf(r1);
-            planes[((size_t)plane_rows + t) * K + e] = m;
-            if (nsplit > 2) planes[((size_t)2 * plane_rows + t) * K + e] = f_to_bf(r1 - bf_to_f(m));
+    for (int e = 2 * tid; e < K; e += 512) {
+        float2 v = *reinterpret_cast<const float2*>(row + e);
+        if (gain != nullptr) {
+            const uint32_t gg = *reinterpret_cast<const uint32_t*>(gain + e);
+            v.x = (v.x * r) * bf_lo(gg); v.y = (v.y * r) * bf_hi(gg);
         }
+        store_planes2(planes, plane_rows, nsplit, K, t, e, v.x, v.y);
     }
 }
 
@@ -666,7 +680,7 @@ cudaError_t launch_act_split(const float* x, int ldx, int K, const bf16_raw* gai
     return launch_chain(act_split_kernel, dim3(plane_rows), dim3(256), 0, st, x, ldx, K, gain, planes, plane_rows, nsplit, n_tok, z);
 }
 cudaError_t launch_silu_planes(const float* g, const float* u, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st) {
-    return launch_chain(silu_planes_kernel, dim3(plane_rows, SILU_SLICES), dim3(256), 0, st, g, u, planes, plane_rows, nsplit, n_tok);
+    return launch_chain(silu_planes_kernel, dim3(plane_rows, plane_rows >= 512 ? 1 : SILU_SLICES), dim3(256), 0, st, g, u, planes, plane_rows, nsplit, n_tok);
 }
 cudaError_t launch_silu_mul(const float* g, const float* u, float* h, size_t n, cudaStream_t st) {
     silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, h, n);
