@@ -94,6 +94,19 @@ def test_any_position(oracle, path, ctx):
     gate_step(oracle, out, ref, f"{path} ctx {ctx}")
 
 
+@pytest.mark.parametrize("ctx", [40, 200, 300])
+def test_persist_on_a_grid_one_short_of_the_sm_count(oracle, ctx):
+    """147 CTAs is the smallest grid the persistent kernel's shared-memory slots allow; the row shares differ from 148's."""
+    shp = oracle.Shape(layers=2, vocab=2048)
+    inp = oracle.synthetic(300 + ctx, shp, context=ctx)
+    mk = engine("persist", layers=2, vocab=2048, grid_limit=147)
+    assert mk.grid == 147
+    out = mk.step(to_dev(inp))
+    mk.status()
+    ref = oracle.decode_step(oracle.to_fp32(inp), inp["token"], inp["kcache"], inp["vcache"])
+    gate_step(oracle, out, ref, f"persist grid 147 ctx {ctx}")
+
+
 def test_persist_reports_a_cache_longer_than_the_host_said(oracle):
     """The host's length bound picks the kernel variant; a longer cache on the device is reported, not served."""
     from qwen3mk.kernel import SeqTable
