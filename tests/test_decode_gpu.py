@@ -258,8 +258,9 @@ def test_full_model_vs_golden_and_oracle(oracle, synth_full, path):
     assert oracle.bf16_ulps(out["v_write"], torch.from_numpy(fx["v_write"])) <= GATE_KV_ULPS
     ref = oracle.decode_step(oracle.to_fp32(inp), inp["token"], inp["kcache"], inp["vcache"])
     gate_step(oracle, out, ref, f"{path} full")
-    # 64 greedy steps with a growing cache (positions 128..191) against the oracle's greedy loop
-    steps = 64
+    # Greedy steps with a growing cache against the oracle's greedy loop: 256 for the persistent kernel (positions
+    # 128..383 walk through all four of its attention variants), 64 for the layered path.
+    steps = 256 if path == "persist" else 64
     mk.bind(dev, chained=True, grow=steps)
     toks = []
     for _ in range(steps):
@@ -267,4 +268,9 @@ def test_full_model_vs_golden_and_oracle(oracle, synth_full, path):
         toks.append(mk.chain_token.clone())
     mk.status()
     g = oracle.greedy_decode(oracle.to_fp32(inp), inp["token"], inp["kcache"], inp["vcache"], steps)
-    assert torch.stack(toks).cpu().tolist() == g["tokens"].tolist(), f"min margin {float(g['margins'].min()):.3e}"
+    got, want = torch.stack(toks).cpu().tolist(), g["tokens"].tolist()
+    if got != want:
+        # identical tokens are the requirement; the one excuse is a step whose two best logits the oracle itself
+        # separates by less than the logits gate allows the kernel to differ (everything after it then differs too)
+        i = next(k for k in range(steps) if got[k] != want[k])
+        assert float(g["margins"][i]) < 1e-4, f"token {i}: got {got[i]}, oracle {want[i]}, top-2 margin {float(g['margins'][i]):.3e}"
