@@ -151,6 +151,29 @@ def test_ragged_batch(oracle, path, batch):
         gate_step(oracle, {k: out[k][b] for k in out}, ref, f"{path} seq {b} len {lens[b]}")
 
 
+def test_long_ragged_batch(oracle):
+    """Cache lengths up to 4096 in one batch (the benchmark's batched-decode shape): several attention splits per sequence,
+    a chunk of scores that fills the split kernel's shared memory, the tensor-core projections."""
+    from qwen3mk.kernel import SeqTable
+
+    shp = oracle.Shape(layers=2, vocab=2048)
+    inp = oracle.synthetic(77, shp, context=8)
+    w = oracle.to_fp32(inp)
+    g = torch.Generator().manual_seed(9)
+    lens = [4096, 3000, 129, 2287, 1024, 4095, 500, 2048]
+    toks = torch.randint(0, 2048, (len(lens),), generator=g)
+    kcs = [(torch.randn(2, n, 8, 128, generator=g) * 0.1).to(torch.bfloat16) for n in lens]
+    vcs = [(torch.randn(2, n, 8, 128, generator=g) * 0.1).to(torch.bfloat16) for n in lens]
+    mk = engine("auto", layers=2, vocab=2048, max_batch=len(lens))
+    seqs = SeqTable([k.cuda() for k in kcs], [v.cuda() for v in vcs])
+    out = mk.bind_sequences(to_dev({k: inp[k] for k in oracle.WEIGHT_NAMES}), toks.cuda(), seqs)
+    mk.launch()
+    mk.status()
+    refs = oracle.decode_batch(w, toks.tolist(), kcs, vcs)
+    for b, ref in enumerate(refs):
+        gate_step(oracle, {k: out[k][b] for k in out}, ref, f"seq {b} len {lens[b]}")
+
+
 @pytest.mark.parametrize("path", PATHS)
 def test_chained_growing_cache_matches_greedy_oracle(oracle, small, path):
     shp, inp, w = small
