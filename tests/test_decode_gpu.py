@@ -151,6 +151,33 @@ def test_ragged_batch(oracle, path, batch):
         gate_step(oracle, {k: out[k][b] for k in out}, ref, f"{path} seq {b} len {lens[b]}")
 
 
+@pytest.mark.parametrize("path", PATHS)
+def test_prefill_2048_then_greedy_decode(oracle, small, path):
+    """The benchmark's third shape on a small model: a 2048-token prompt on the GPU, then chained greedy steps over
+    2049.. positions (split attention in the persistent kernel), against the oracle run on the same cache."""
+    from qwen3mk import prefill
+
+    shp, inp, w = small
+    T, steps = 2048, 12
+    g = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, 4096, (T,), generator=g).tolist()
+    wdev = to_dev({k: inp[k] for k in oracle.WEIGHT_NAMES})
+    kc, vc, last = prefill.prefill(wdev, ids, "cuda", capacity=T + steps)
+    tok = last.argmax().to(torch.int64)
+    mk = engine(path, layers=2, vocab=4096, max_positions=4096)
+    mk.bind(dict(wdev, token=tok, kcache=kc[:, :T].contiguous(), vcache=vc[:, :T].contiguous()), chained=True, grow=steps)
+    toks = []
+    for _ in range(steps):
+        mk.launch()
+        toks.append(mk.chain_token.clone())
+    mk.status()
+    ref = oracle.greedy_decode(w, tok.cpu(), kc[:, :T].cpu(), vc[:, :T].cpu(), steps)
+    got, want = torch.stack(toks).cpu().tolist(), ref["tokens"].tolist()
+    if got != want:
+        i = next(k for k in range(steps) if got[k] != want[k])
+        assert float(ref["margins"][i]) < 1e-4, f"token {i}: got {got[i]}, oracle {want[i]}, margin {float(ref['margins'][i]):.3e}"
+
+
 def test_long_ragged_batch(oracle):
     """Cache lengths up to 4096 in one batch (the benchmark's batched-decode shape): several attention splits per sequence,
     a chunk of scores that fills the split kernel's shared memory, the tensor-core projections."""
