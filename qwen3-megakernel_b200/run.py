@@ -154,8 +154,12 @@ def cmd_batch(args) -> int:
     B, ctx = args.batch, args.context
     w = weights.baseline_init(args.seed, dev)
     g = torch.Generator(device=dev).manual_seed(args.seed)
-    mk_cache = lambda: (torch.randn(LAYERS, ctx, KV_HEADS, HEAD_DIM, device=dev, generator=g) * 0.1).to(torch.bfloat16)
-    kcs, vcs = [mk_cache() for _ in range(B)], [mk_cache() for _ in range(B)]
+    if args.ragged:   # cache lengths uniform in [128, context], seeded
+        lens = torch.randint(128, ctx + 1, (B,), generator=torch.Generator().manual_seed(args.seed)).tolist()
+    else:
+        lens = [ctx] * B
+    mk_cache = lambda n: (torch.randn(LAYERS, n, KV_HEADS, HEAD_DIM, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+    kcs, vcs = [mk_cache(n) for n in lens], [mk_cache(n) for n in lens]
     mk = Megakernel(dev, max_batch=B)
     seqs = SeqTable(kcs, vcs)
     toks = torch.randint(0, VOCAB, (B,), device=dev, generator=g)
@@ -172,8 +176,9 @@ def cmd_batch(args) -> int:
     torch.cuda.synchronize(dev)
     mk.status()
     us = e0.elapsed_time(e1) * 1e3 / args.steps
-    nbytes = 1_192_099_840 + B * (114_688 * ctx + 724_480)   # weights + gains + per-sequence K/V and activations
-    print(f"batch {B} x {ctx} cached positions: {us:.1f} us/step, {B * 1e6 / us:.0f} tokens/s, "
+    nbytes = 1_192_099_840 + sum(114_688 * n + 724_480 for n in lens)   # weights + gains + per-sequence K/V and activations
+    shape = f"{B} sequences of {min(lens)}..{max(lens)} (mean {sum(lens) / B:.0f})" if args.ragged else f"{B} x {ctx}"
+    print(f"batch {shape} cached positions: {us:.1f} us/step, {B * 1e6 / us:.0f} tokens/s, "
           f"{nbytes / us / 1e6:.2f} TB/s of algorithmic bytes, {(mk.launch_count - n0) / args.steps:.0f} kernels per step"
           f"{' (plain launches)' if args.plain else ' (graph replay)'}")
     return 0
@@ -245,6 +250,7 @@ def main(argv=None) -> int:
     p.add_argument("--steps", type=int, default=20)
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--plain", action="store_true", help="plain launches instead of CUDA-graph replay")
+    p.add_argument("--ragged", action="store_true", help="cache lengths drawn uniformly from [128, --context]")
     p = sub.add_parser("prefill")
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--reps", type=int, default=5)
