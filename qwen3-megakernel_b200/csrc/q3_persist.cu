@@ -50,8 +50,9 @@ constexpr int GROUP_CTAS = 2 * WO_SLICES;     // CTAs sharing one kv head
 constexpr int WO_ROWS_MAX = 116;              // largest slice: 4 * ceil(256 / 9)
 constexpr int PERSIST_MAX_BATCH = 3;          // sequences served by back-to-back launches
 constexpr int MIN_GRID = 147;                 // row shares must fit the shared-memory slots
-constexpr int SC_HALF = 128;                  // scores kept per head: the CTA's share of the cached positions
-constexpr int PERSIST_MAX_LEN = GROUP_CTAS * SC_HALF - GROUP_CTAS;   // 2286 cached positions
+constexpr int SC_HALF = 128;                  // the score buffer holds 3 * SC_HALF floats
+constexpr int SPLIT_SC = 3 * SC_HALF / 2;     // split attention: scores kept per head = the most positions a CTA takes (192)
+constexpr int PERSIST_MAX_LEN = GROUP_CTAS * SPLIT_SC - GROUP_CTAS;   // 3438 cached positions
 constexpr int WROW = 1032;                    // elements between weight rows in shared memory: 1024 + 8 of padding, so that
                                               // the eight row addresses of an ldmatrix fall into different banks
 constexpr int WOROW = 136;                    // the same for the 128-column Wo slice rows
@@ -331,7 +332,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     float* red = reinterpret_cast<float*>(hsp + 48);          // [32]
     float* lw = red + 32;        // [16] per-warp probability sums, [w][head]
     float* misc = lw + 16;       // [16]: [0] score of the new row for this CTA's head
-    float* sc = misc + 16;       // split attention: [2][SC_HALF] scores of this CTA's positions; local: [3 * SC_HALF] scores of all positions
+    float* sc = misc + 16;       // split attention: [2][SPLIT_SC] scores of this CTA's positions; local: [3 * SC_HALF] scores of all positions
     uint64_t* full = reinterpret_cast<uint64_t*>(sc + 3 * SC_HALF);   // [4] slot filled
     volatile int* abort_flag = reinterpret_cast<volatile int*>(full + 8);
 
@@ -822,7 +823,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         }
                         if (pos < cp1) {
                             tmax0 = fmaxf(tmax0, s0); tmax1 = fmaxf(tmax1, s1);
-                            if (sub == 0) { sc[idx] = s0; sc[SC_HALF + idx] = s1; }
+                            if (sub == 0) { sc[idx] = s0; sc[SPLIT_SC + idx] = s1; }
                         }
                     }
                     tmax0 = warp_max(tmax0); tmax1 = warp_max(tmax1);
@@ -847,7 +848,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     for (int i = 0; i < 8; ++i) {
                         const int idx = warp + ATT_WARPS * i;
                         const bool live = cp0 + idx < cp1;
-                        const float p0 = live ? __expf(sc[idx] - M0) : 0.f, p1 = live ? __expf(sc[SC_HALF + idx] - M1) : 0.f;
+                        const float p0 = live ? __expf(sc[idx] - M0) : 0.f, p1 = live ? __expf(sc[SPLIT_SC + idx] - M1) : 0.f;
                         l0 += p0; l1 += p1;
                         const uint4& src = ring[2 + (i >> 2)][(i >> 1) & 1];
                         const uint32_t vx = (i & 1) ? src.z : src.x, vy = (i & 1) ? src.w : src.y;
@@ -858,7 +859,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 #pragma unroll 2
                     for (int idx = warp + ATT_WARPS * 8; cp0 + idx < cp1; idx += ATT_WARPS) {
                         const uint2 v = ld_stream8(vl + (size_t)(cp0 + idx) * KV_DIM + lane * 4);
-                        const float p0 = __expf(sc[idx] - M0), p1 = __expf(sc[SC_HALF + idx] - M1);
+                        const float p0 = __expf(sc[idx] - M0), p1 = __expf(sc[SPLIT_SC + idx] - M1);
                         l0 += p0; l1 += p1;
                         const float f0 = bf_lo(v.x), f1 = bf_hi(v.x), f2 = bf_lo(v.y), f3 = bf_hi(v.y);
                         acc[0][0] = fmaf(p0, f0, acc[0][0]); acc[0][1] = fmaf(p0, f1, acc[0][1]); acc[0][2] = fmaf(p0, f2, acc[0][2]); acc[0][3] = fmaf(p0, f3, acc[0][3]);

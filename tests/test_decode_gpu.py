@@ -76,14 +76,14 @@ def test_small_model_step_vs_oracle_and_golden(oracle, small, path):
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("ctx", [0, 1, 7, 17, 19, 64, 128, 129, 191, 192, 240, 255, 256, 300, 515, 577, 1500, 2286, 2400])
+@pytest.mark.parametrize("ctx", [0, 1, 7, 17, 19, 64, 128, 129, 191, 192, 240, 255, 256, 300, 515, 577, 1500, 2286, 2400, 3438, 3500])
 def test_any_position(oracle, path, ctx):
     shp = oracle.Shape(layers=2, vocab=2048)
     inp = oracle.synthetic(100 + ctx, shp, context=max(ctx, 1))
     if ctx == 0:
         inp["kcache"], inp["vcache"] = inp["kcache"][:, :0].contiguous(), inp["vcache"][:, :0].contiguous()
     mk = engine(path, layers=2, vocab=2048)
-    if path == "persist" and ctx > 2286:
+    if path == "persist" and ctx > 3438:
         # beyond its context limit the persistent kernel refuses; "auto" then takes the layered path
         with pytest.raises(RuntimeError, match="persistent kernel"):
             mk.step(to_dev(inp))
