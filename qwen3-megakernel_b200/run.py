@@ -150,7 +150,16 @@ def cmd_batch(args) -> int:
     """One batched decode step (layered tensor-core path): `--batch` sequences of `--context` cached positions."""
     from qwen3mk.kernel import SeqTable, LAYERS, KV_HEADS, HEAD_DIM, VOCAB
 
-    dev = torch.device("cuda", torch.cuda.current_device())
+    # under torchrun every rank runs its own replica of the batch on its own GPU; the time is the slowest rank's
+    import os
+    import torch.distributed as dist
+    from qwen3mk import replicas
+
+    world, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     B, ctx = args.batch, args.context
     w = weights.baseline_init(args.seed, dev)
     g = torch.Generator(device=dev).manual_seed(args.seed)
@@ -167,6 +176,8 @@ def cmd_batch(args) -> int:
     for _ in range(3):
         mk.launch()
     torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n0 = mk.launch_count
     e0.record()
@@ -176,6 +187,13 @@ def cmd_batch(args) -> int:
     torch.cuda.synchronize(dev)
     mk.status()
     us = e0.elapsed_time(e1) * 1e3 / args.steps
+    if world > 1:
+        us = replicas.max_over_ranks(us, dev)
+        dist.barrier()
+        if dist.get_rank() == 0:
+            print(f"{world} replicas of batch {B}: {us:.1f} us/step on the slowest, {world * B * 1e6 / us:.0f} tokens/s over the job")
+        dist.destroy_process_group()
+        return 0
     nbytes = 1_192_099_840 + sum(114_688 * n + 724_480 for n in lens)   # weights + gains + per-sequence K/V and activations
     shape = f"{B} sequences of {min(lens)}..{max(lens)} (mean {sum(lens) / B:.0f})" if args.ragged else f"{B} x {ctx}"
     print(f"batch {shape} cached positions: {us:.1f} us/step, {B * 1e6 / us:.0f} tokens/s, "
