@@ -49,7 +49,7 @@ typedef struct q3_config {
     int32_t max_batch;      /* largest q3_decode_args.batch the scratch is sized for (>= 1)      */
     int32_t max_tokens;     /* largest q3_prefill_args.n_tokens the scratch is sized for (0: no prefill) */
     int32_t grid_limit;     /* 0 = one CTA per SM; otherwise cap the persistent grid (tests)     */
-    int32_t pace_cycles;    /* reserved, must be 0 (an earlier weight-streaming scheme was paced by it; the field keeps the struct layout) */
+    int32_t wait_limit_us;  /* patience of every device-side wait in microseconds; 0 = the default (200 ms).  Tests set it low to see a wait give up */
 } q3_config;
 
 /* The 13 weight tensors, device pointers to bf16.  Replaces slots 1..13 of the reference's
@@ -136,11 +136,19 @@ int q3_prefill(q3_engine* e, const q3_prefill_args* a, void* stream);
  * device array inside the library (about 0.4 MB per GPU, held until the process exits), which limits a
  * call to Q3_NOALLOC_MAX_BATCH sequences; larger batches are rejected with Q3_ERR_INVALID.  The first
  * call on a device looks up the array's address (make it before any stream capture).  All calls share
- * the array: do not let two calls overlap on the GPU.  `w`, `rope` and `a` are as for q3_set_weights,
+ * the array: do not let two calls overlap on the GPU, from one host thread or from several (the address
+ * look-up itself is locked; the array is not).  `w`, `rope` and `a` are as for q3_set_weights,
  * q3_set_rope and q3_decode; only the layered path is available. */
 #define Q3_NOALLOC_MAX_BATCH 2
 int q3_decode_noalloc(const q3_weights* w, const float* rope, int32_t rope_positions, int32_t n_layers, int32_t vocab,
                       const q3_decode_args* a, void* stream);
+
+/* Status of the last q3_decode_noalloc on the current device: synchronises `stream`, copies the status words
+ * of the static array to `words` (up to `n`, may be NULL; same layout as q3_status) and returns Q3_OK or
+ * Q3_ERR_DEVICE_WAIT (for example code 3: a token outside the vocabulary was replaced by token 0; code 5: a
+ * cache longer than max_len).  Every q3_decode_noalloc clears the words when it starts, so read them before
+ * the next call.  Allocates nothing.  No counterpart in the reference. */
+int q3_noalloc_status(void* stream, uint32_t* words, int32_t n);
 
 /* out[t, n] = (resid[t, n] +) sum_k w[n, k] * x[t, k] on the tensor cores (tcgen05 / TMEM / TMA): w bf16
  * [n_rows, K] row-major (n_rows a multiple of 128, K of 64), x fp32 [n_tok, K], out and resid fp32
@@ -161,9 +169,10 @@ int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n);
  * README.md:174-239).  `buf` is a device buffer of n_words 64-bit words, or NULL to switch tracing
  * off.  While set and large enough (grid * (4 + 12 * n_layers) words), every persistent launch makes
  * thread 0 of CTA c store %globaltimer (ns) at buf[c * (4 + 12 L) + ev].  ev 0 = start; for layer l,
- * base = 1 + 12 l: +0 Q activations staged, +1 Q done, +2 barrier passed, +3 F q/k/v prepared,
- * +4 F scores done, +5 F head output ready, +6 F done, +7 barrier passed, +8 GD activations staged,
- * +9 GD hid ready, +10 GD done, +11 barrier passed; then 1 + 12 L = LM-head rows done, 2 + 12 L = end.
+ * base = 1 + 12 l: +0 Q activations staged, +1 Q done, +2 K/V rows requested, +3 F q/k/v prepared,
+ * +4 F scores done, +5 F head output ready, +6 F done (attention delta sent), +7 attention delta complete,
+ * +8 GD activations staged, +9 GD hid ready, +10 GD done (FFN delta sent), +11 FFN delta complete; then
+ * 1 + 12 L = LM-head rows done, 2 + 12 L = end.
  * Borrowed. */
 int q3_set_trace(q3_engine* e, uint64_t* buf, int64_t n_words);
 
@@ -173,8 +182,9 @@ int64_t q3_launch_count(const q3_engine* e);
 /* Persistent-grid geometry chosen at creation: CTAs, threads per CTA, dynamic smem bytes. */
 int q3_grid_info(const q3_engine* e, int32_t* ctas, int32_t* threads, int32_t* smem_bytes);
 
-/* Engine-owned scratch for tools and tests: name in {"x","qkv","attn","hid","status"}; returns a
- * device pointer and its size in bytes, or Q3_ERR_INVALID. */
+/* Engine-owned scratch for tools and tests: name in {"x","qkv","attn","hid","status","persist_acc"}; returns a
+ * device pointer and its size in bytes, or Q3_ERR_INVALID.  "persist_acc" is the persistent kernel's four delta
+ * accumulators (64-bit words: contributions << 56 | fixed-point sum), all zero between launches. */
 int q3_scratch(const q3_engine* e, const char* name, void** ptr, int64_t* bytes);
 
 /* Message of the last error on this engine (or of the last failed q3_create when e == NULL). */

@@ -198,13 +198,14 @@ def decode_step(w: dict, token, kcache: torch.Tensor, vcache: torch.Tensor, pos:
 
 @torch.no_grad()
 def greedy_decode(w: dict, token, kcache: torch.Tensor, vcache: torch.Tensor, steps: int,
-                  forced_tokens=None) -> dict:
+                  forced_tokens=None, on_step=None) -> dict:
     """`steps` consecutive decode steps.  After each step the new K/V rows are appended to the cache
     ROUNDED TO bf16 (what a cache of the kernel's output dtype holds; qwen3mk/kernel.py:48-49), and the
     argmax token (or `forced_tokens[i]` when teacher-forcing) feeds the next step.
 
-    Returns tokens [steps] (the argmax of every step), margins [steps] (top-1 minus top-2 logit),
-    the final caches (bf16) and the last step's logits."""
+    `on_step(i, out)` is called with every step's full output (logits, k_write, v_write), so that a checker
+    can gate each step without this loop keeping all logits.  Returns tokens [steps] (the argmax of every
+    step), margins [steps] (top-1 minus top-2 logit), the final caches (bf16) and the last step's logits."""
     kc = kcache.to(torch.bfloat16).clone()
     vc = vcache.to(torch.bfloat16).clone()
     toks, margins = [], []
@@ -215,6 +216,8 @@ def greedy_decode(w: dict, token, kcache: torch.Tensor, vcache: torch.Tensor, st
         top2 = torch.topk(out["logits"], 2).values
         margins.append(float(top2[0] - top2[1]))
         toks.append(int(out["next_token"]))
+        if on_step is not None:
+            on_step(i, out)
         kc = torch.cat([kc, out["k_write"].to(torch.bfloat16)[:, None]], dim=1)
         vc = torch.cat([vc, out["v_write"].to(torch.bfloat16)[:, None]], dim=1)
         tok = toks[-1] if forced_tokens is None else int(forced_tokens[i])

@@ -46,6 +46,7 @@ static int alloc(q3_engine* e, void** p, size_t bytes) {
 struct GraphEntry {
     q3_decode_args key;
     int n_splits;
+    int chunk_pad;         // the attention kernel's padded chunk length is baked into the captured arguments
     int seen;
     int64_t launches;      // kernels inside the graph
     cudaGraphExec_t exec;
@@ -69,7 +70,7 @@ extern "C" const char* q3_last_error(const q3_engine* e) { return e ? e->err : g
 extern "C" int q3_create(int device, const q3_config* cfg, q3_engine** out) {
     if (!cfg || !out) return fail(nullptr, Q3_ERR_INVALID, "q3_create: null argument");
     *out = nullptr;
-    if (cfg->n_layers < 1 || cfg->vocab < 1 || cfg->max_batch < 1 || cfg->max_tokens < 0 || cfg->grid_limit < 0 || cfg->pace_cycles < 0)
+    if (cfg->n_layers < 1 || cfg->vocab < 1 || cfg->max_batch < 1 || cfg->max_tokens < 0 || cfg->grid_limit < 0 || cfg->wait_limit_us < 0)
         return fail(nullptr, Q3_ERR_INVALID, "q3_create: n_layers=%d vocab=%d max_batch=%d max_tokens=%d grid_limit=%d out of range",
                     cfg->n_layers, cfg->vocab, cfg->max_batch, cfg->max_tokens, cfg->grid_limit);
     CU(nullptr, cudaSetDevice(device));
@@ -197,6 +198,7 @@ extern "C" int q3_scratch(const q3_engine* e, const char* name, void** ptr, int6
     else if (!strcmp(name, "attn")) { *ptr = e->attn; *bytes = B * Q_DIM * 4; }
     else if (!strcmp(name, "hid")) { *ptr = e->hid; *bytes = B * INTER * 4; }
     else if (!strcmp(name, "status")) { *ptr = e->status; *bytes = Q3_STATUS_WORDS * 4; }
+    else if (!strcmp(name, "persist_acc")) { *ptr = persist_accumulators(e, bytes); if (!*ptr) return Q3_ERR_UNSUPPORTED; }
     else return Q3_ERR_INVALID;
     return Q3_OK;
 }
@@ -219,6 +221,9 @@ extern "C" int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n)
 // ------------------------------------------------------------------------------------------------
 // layered decode step
 // ------------------------------------------------------------------------------------------------
+// positions a split's block may take, rounded up to 32: with the split count it fixes the attention launch
+static int chunk_pad_for(int max_len, int ns) { return (((max_len + 1 + ns - 1) / ns) + 31) / 32 * 32; }
+
 static int splits_for(const q3_engine* e, int batch, int max_len) {
     const int n = max_len + 1;
     int by_len = (n + 31) / 32;                                   // at least 32 positions per split
@@ -269,7 +274,13 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
     const bool row_argmax = !last_token_only && B <= e->cfg.max_batch;
     unsigned long long* arg_keys = row_argmax ? reinterpret_cast<unsigned long long*>(e->pval) : nullptr;
     unsigned* arg_tickets = row_argmax ? reinterpret_cast<unsigned*>(e->pidx) : nullptr;
-    LAUNCH(launch_embed(reinterpret_cast<const long long*>(a->token), bf(w.embed), V, e->x, e->status, B, st, arg_keys, arg_tickets));
+    // what the launches of this step can serve: the attention split covers n_splits * chunk_pad positions (the new one
+    // included) and the RoPE table has rope_n rows; both are fixed by (n_splits, chunk_pad), like a captured graph
+    const int pad = chunk_pad_for(a->max_len, ns);
+    long long cover = (long long)ns * pad - 1;
+    if (cover > e->rope_n - 1) cover = e->rope_n - 1;
+    const int len_bound = (int)cover;
+    LAUNCH(launch_embed(reinterpret_cast<const long long*>(a->token), bf(w.embed), V, e->x, e->status, B, st, arg_keys, arg_tickets, a->seq_len, len_bound));
     for (int l = 0; l < L; ++l) {
         GemvArgs g{};
         // qkv = rms(x, ln1) @ [wq; wk; wv]^T
@@ -299,7 +310,7 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         h.qkv = e->qkv; h.qn = bf(w.qn); h.kn = bf(w.kn); h.rope = e->rope; h.seq_len = a->seq_len;
         h.k_write = reinterpret_cast<bf16_raw*>(a->k_write); h.v_write = reinterpret_cast<bf16_raw*>(a->v_write);
         h.seq_k = a->seq_k; h.seq_v = a->seq_v; h.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
-        h.layer = l; h.n_layers = L; h.append = append;
+        h.layer = l; h.n_layers = L; h.append = append; h.len_bound = len_bound;
         // A prompt's tokens attend rows that earlier tokens of the same launch append: those need the separate kernel.
         // A decode step prepares the heads inside the attention kernel (one launch less per layer).
         const bool fused_prep = prompt == nullptr;
@@ -309,7 +320,7 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         t.qkv = e->qkv; t.seq_k = a->seq_k; t.seq_v = a->seq_v;
         t.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
         t.seq_len = a->seq_len; t.part = e->part; t.layer = l; t.n_splits = ns;
-        t.chunk_pad = (((a->max_len + 1 + ns - 1) / ns) + 31) / 32 * 32;
+        t.chunk_pad = pad; t.len_bound = len_bound;
         t.fused_prep = fused_prep ? 1 : 0; t.qn = h.qn; t.kn = h.kn; t.rope = h.rope; t.k_write = h.k_write; t.v_write = h.v_write;
         t.n_layers = L; t.append = append;
         if (prompt != nullptr && B >= 64) {
@@ -414,18 +425,20 @@ extern "C" int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream) {
     if (path != Q3_F_PATH_LAYERED) return fail(e, Q3_ERR_INVALID, "q3_decode: unknown path flag 0x%x", path);
     if (!(a->flags & Q3_F_GRAPH)) return decode_layered(e, a, st);
 
-    // graph replay: the key is the argument block with max_len replaced by what it determines (the split count)
+    // graph replay: the key is the argument block with max_len replaced by what it determines in the captured
+    // launches: the split count and the padded chunk length (which also sizes the attention kernel's shared memory)
     q3_decode_args key = *a;
     key.max_len = 0;
     key.reserved = 0;
     const int ns = splits_for(e, a->batch, a->max_len);
+    const int pad = chunk_pad_for(a->max_len, ns);
     auto* cache = graph_cache(e);
     GraphEntry* hit = nullptr;
     for (auto& g : *cache)
-        if (g.n_splits == ns && !memcmp(&g.key, &key, sizeof(key))) { hit = &g; break; }
+        if (g.n_splits == ns && g.chunk_pad == pad && !memcmp(&g.key, &key, sizeof(key))) { hit = &g; break; }
     if (!hit) {
         if (cache->size() >= 64) drop_graphs(e);
-        cache->push_back(GraphEntry{key, ns, 0, 0, nullptr});
+        cache->push_back(GraphEntry{key, ns, pad, 0, 0, nullptr});
         hit = &cache->back();
     }
     if (hit->exec) {

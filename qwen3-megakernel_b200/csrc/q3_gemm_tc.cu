@@ -15,12 +15,16 @@
 // Replaces the dense `xn @ w.T` products of the reference's PyTorch prefill (qwen3mk/prefill.py:61-80).
 #include <cuda.h>
 
+#include <mutex>
 #include <vector>
 
 #include "q3_engine.h"
 #include "q3_gemm_tc.h"
 
 namespace q3 {
+
+constexpr int MAX_DEVICES = 64;
+static std::mutex& host_lock() { static std::mutex m; return m; }   // guards the per-device set-up flags and the tensor-map cache
 
 constexpr int TC_THREADS = 192;    // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
 constexpr int TC_BM = 128;         // weight rows per tile (UMMA M)
@@ -299,11 +303,17 @@ static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmT
     if (stages < 1) return cudaErrorInvalidValue;
     p.stages = stages;
     const size_t smem = (size_t)stages * stage_bytes + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
+    {   // the shared-memory limit of a function is a per-device attribute: set it once on every device that launches
+        static bool attr_set[MAX_DEVICES] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> hold(host_lock());
+        if (!attr_set[dev]) {
+            e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+            if (e != cudaSuccess) return e;
+            attr_set[dev] = true;
+        }
     }
     dim3 grid((n_rows + TC_BM - 1) / TC_BM, (n_tok + BN - 1) / BN, ksplit);
     return launch_chain(gemm_tc_kernel<BN>, grid, dim3(TC_THREADS), smem, st, tw[0], tw[1], tw[2], tx, p);
@@ -314,15 +324,27 @@ static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmT
 struct MapKey { const void* p; uint64_t rows, cols; uint32_t box; };
 struct MapEntry { MapKey k; CUtensorMap m; };
 static std::vector<MapEntry>& map_cache() { static std::vector<MapEntry> c; return c; }
-static const CUtensorMap* cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// (device addresses are unique across the GPUs of a process, so one cache serves them all; it is locked because
+// engines on different host threads share it)
+static bool cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> hold(host_lock());
     auto& c = map_cache();
     for (auto& e : c)
-        if (e.k.p == ptr && e.k.rows == rows && e.k.cols == cols && e.k.box == box_rows) return &e.m;
+        if (e.k.p == ptr && e.k.rows == rows && e.k.cols == cols && e.k.box == box_rows) { *out = e.m; return true; }
     if (c.size() > 4096) c.clear();
     MapEntry e{{ptr, rows, cols, box_rows}, {}};
-    if (!make_map(&e.m, ptr, rows, cols, box_rows)) return nullptr;
+    if (!make_map(&e.m, ptr, rows, cols, box_rows)) return false;
     c.push_back(e);
-    return &c.back().m;
+    *out = e.m;
+    return true;
+}
+static int sm_count_of_current_device() {
+    static int sms[MAX_DEVICES] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 0;
+    std::lock_guard<std::mutex> hold(host_lock());
+    if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    return sms[dev];
 }
 
 cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st) {
@@ -330,17 +352,14 @@ cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st) {
     // token tile: the smallest of 32 / 64 / 128 that covers the batch, 128 for long prompts
     const int bn = c.n_tok <= 32 ? 32 : (c.n_tok <= 64 ? 64 : 128);
     if (c.plane_rows % bn) return cudaErrorInvalidValue;
-    const CUtensorMap* pw = cached_map(c.w, (uint64_t)c.n_rows, (uint64_t)c.K, TC_BM);
-    if (!pw) return cudaErrorUnknown;
-    const CUtensorMap tw = *pw;   // copy: the cache may grow while the second map is looked up
-    const CUtensorMap* px = cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)bn);
-    if (!px) return cudaErrorUnknown;
-    const CUtensorMap tx = *px;
+    CUtensorMap tw, tx;
+    if (!cached_map(c.w, (uint64_t)c.n_rows, (uint64_t)c.K, TC_BM, &tw)) return cudaErrorUnknown;
+    if (!cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)bn, &tx)) return cudaErrorUnknown;
     GemmTcParams p{};
     p.out = c.out; p.resid = c.resid; p.ldo = c.ldo; p.ldr = c.ldr; p.n_rows = c.n_rows; p.n_tok = c.n_tok; p.K = c.K;
     p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = c.resid ? TC_EPI_RESID : TC_EPI_STORE; p.status = c.status;
-    static int sm_count = 0;
-    if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+    const int sm_count = sm_count_of_current_device();
+    if (sm_count < 1) return cudaErrorInvalidDevice;
     const CUtensorMap maps[3] = {tw, tw, tw};
     if (bn == 32) return launch_bn<32>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st);
     if (bn == 64) return launch_bn<64>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st);
@@ -356,20 +375,17 @@ cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st) {
     int rows = 0;
     for (int g = 0; g < c.n_groups; ++g) {
         if (c.n_rows[g] % TC_BM || c.n_rows[g] < TC_BM) return cudaErrorInvalidValue;
-        const CUtensorMap* pw = cached_map(c.w[g], (uint64_t)c.n_rows[g], (uint64_t)c.K, TC_BM);
-        if (!pw) return cudaErrorUnknown;
-        maps[g] = *pw;
+        if (!cached_map(c.w[g], (uint64_t)c.n_rows[g], (uint64_t)c.K, TC_BM, &maps[g])) return cudaErrorUnknown;
         p.g_tiles[g] = c.n_rows[g] / TC_BM; p.g_out[g] = c.out[g]; p.g_ldo[g] = c.ldo[g];
         rows += c.n_rows[g];
     }
     for (int g = c.n_groups; g < 3; ++g) maps[g] = maps[0];
-    const CUtensorMap* px = cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)bn);
-    if (!px) return cudaErrorUnknown;
-    const CUtensorMap tx = *px;
+    CUtensorMap tx;
+    if (!cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)bn, &tx)) return cudaErrorUnknown;
     p.n_groups = c.n_groups; p.out = c.out[0]; p.resid = nullptr; p.ldo = c.ldo[0]; p.ldr = 0; p.n_rows = rows; p.n_tok = c.n_tok; p.K = c.K;
     p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = TC_EPI_STORE; p.status = c.status; p.out_is_zero = c.out_is_zero;
-    static int sm_count = 0;
-    if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+    const int sm_count = sm_count_of_current_device();
+    if (sm_count < 1) return cudaErrorInvalidDevice;
     if (bn == 32) return launch_bn<32>(maps, tx, p, rows, c.n_tok, sm_count, st);
     if (bn == 64) return launch_bn<64>(maps, tx, p, rows, c.n_tok, sm_count, st);
     return launch_bn<128>(maps, tx, p, rows, c.n_tok, sm_count, st);

@@ -25,10 +25,14 @@ namespace q3 {
 __global__ void __launch_bounds__(256) embed_kernel(const long long* __restrict__ token,
                                                     const bf16_raw* __restrict__ embed, int vocab,
                                                     float* __restrict__ x, uint32_t* status,
-                                                    unsigned long long* argmax_keys, unsigned* argmax_tickets) {
+                                                    unsigned long long* argmax_keys, unsigned* argmax_tickets,
+                                                    const int* __restrict__ seq_len, int len_bound) {
     pdl_launch();
     pdl_wait();
     const int b = blockIdx.x;
+    // A cache longer than the host's bound for this launch (which sized the attention split and the RoPE table) is
+    // reported here; the kernels that follow clamp the length, so nothing is read out of range.
+    if (threadIdx.x == 0 && seq_len != nullptr && (seq_len[b] > len_bound || seq_len[b] < 0)) report(status, ST_BAD_LEN, 1000, (uint32_t)seq_len[b]);
     if (threadIdx.x == 0 && argmax_keys != nullptr) { argmax_keys[b] = 0ull; argmax_tickets[b] = 0u; }   // for the step's row argmax
     long long t = token[b];
     if (t < 0 || t >= vocab) {
@@ -227,7 +231,7 @@ __global__ void __launch_bounds__(256) head_prep_kernel(const HeadPrepArgs a) {
     const int g = hb - Q_HEADS;
     float* src = a.qkv + (size_t)b * QKV_DIM + (is_q ? hb * HEAD_DIM : Q_DIM + g * HEAD_DIM) + lane * 4;
     const bf16_raw* gain = (is_q ? a.qn : a.kn) + (size_t)a.layer * HEAD_DIM + lane * 4;
-    const int pos = a.seq_len[b];
+    const int pos = min(max(a.seq_len[b], 0), a.len_bound);
     const float4 v4 = *reinterpret_cast<const float4*>(src);
     float v[4] = {v4.x, v4.y, v4.z, v4.w};
     float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
@@ -291,7 +295,7 @@ __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
     const int sp = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int quarter = lane >> 3, sub = lane & 7;
-    const int len = a.seq_len[b];
+    const int len = min(max(a.seq_len[b], 0), a.len_bound);
     const int n = len + 1;
     const int chunk = (n + a.n_splits - 1) / a.n_splits;
     const int p0 = sp * chunk, p1 = min(min(p0 + chunk, n), p0 + a.chunk_pad);
@@ -724,8 +728,8 @@ cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStrea
 }
 
 cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st,
-                         unsigned long long* argmax_keys, unsigned* argmax_tickets) {
-    return launch_chain(embed_kernel, dim3(batch), dim3(256), 0, st, token, embed, vocab, x, status, argmax_keys, argmax_tickets);
+                         unsigned long long* argmax_keys, unsigned* argmax_tickets, const int* seq_len, int len_bound) {
+    return launch_chain(embed_kernel, dim3(batch), dim3(256), 0, st, token, embed, vocab, x, status, argmax_keys, argmax_tickets, seq_len, len_bound);
 }
 
 cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st) {

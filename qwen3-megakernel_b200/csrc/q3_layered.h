@@ -46,6 +46,7 @@ struct HeadPrepArgs {
     const uint64_t* seq_v;
     const long long* seq_layer_stride;
     int layer, n_layers, append;
+    int len_bound;                    // lengths are clamped to [0, len_bound] (the embed kernel reports a longer cache)
 };
 
 struct AttnArgs {
@@ -66,11 +67,13 @@ struct AttnArgs {
     bf16_raw* k_write;
     bf16_raw* v_write;
     int n_layers, append;
+    int len_bound;                    // n_splits * chunk_pad - 1 and the RoPE table's last row, whichever is smaller
 };
 
 cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStream_t st);
 cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int vocab, float* x, uint32_t* status, int batch, cudaStream_t st,
-                         unsigned long long* argmax_keys = nullptr, unsigned* argmax_tickets = nullptr);
+                         unsigned long long* argmax_keys = nullptr, unsigned* argmax_tickets = nullptr,
+                         const int* seq_len = nullptr, int len_bound = 0);
 cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st);
 cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st);
 cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st);

@@ -1,20 +1,25 @@
 // Persistent cooperative decode kernel: one launch runs a whole batch-1 decode step.
 //
 // One CTA of 16 warps per SM.  The schedule is static (every CTA owns fixed weight rows, all of them resident
-// in its 227 KB of shared memory for the layer at hand) and a layer costs TWO grid barriers:
+// in its 227 KB of shared memory for the layer at hand) and a layer has NO grid barrier: every exchange between
+// CTAs is a wait on the data itself.
 //
-//   Q   x = X0 + dB;  qkv rows = rms(x, ln1) . [wq;wk;wv] rows, published as tagged 64-bit words
-//       (tag << 32 | fp32 bits, one tag per launch and layer): no barrier follows, the readers poll the tags
+//   Q   x += dB (previous layer);  qkv rows = rms(x, ln1) . [wq;wk;wv] rows, published as tagged 64-bit words
+//       (tag << 32 | fp32 bits, one tag per launch and layer); the readers poll the tags
 //   F   four warps of every CTA poll the q/k/v rows of their kv group, normalise and rotate them; then either
 //       every CTA attends its whole head over all cached positions from registers (up to 255 positions), or the
 //       18 CTAs of a kv-head group (2 query heads x 9 Wo row slices) each attend 1/18 of the positions for both
 //       heads and exchange (max, sum, output) partials as tagged words; Wo[slice rows, head columns] . o_h is
-//       added into dA                                                           (red.global.add)   | barrier
-//   GD  x = X1 + dA;  hid rows = silu(gate) * up for this CTA's FFN rows, kept in shared memory,
-//       then the matching rows of the transposed down matrix scatter hid into dB (red.global.add)   | barrier
+//       added into dA                                                           (red.global.add.u64)
+//   GD  x += dA;  hid rows = silu(gate) * up for this CTA's FFN rows, kept in shared memory,
+//       then the matching rows of the transposed down matrix scatter hid into dB (red.global.add.u64)
 //
-// The residual stream lives as "materialised vector + pending delta": every CTA adds the two on load, one CTA
-// writes the sum back for the phase after next; the deltas alternate between two buffers per layer parity.
+// The residual stream x lives in registers, the same copy in every CTA (two elements per thread).  The deltas of a
+// phase are summed in "counted accumulators": one 64-bit word per element holding the number of contributions
+// in its top 8 bits and their sum as a 2^-36 fixed-point number below (red.global.add.u64 adds both at once).
+// A reader polls its own two words until the count is complete, which makes the wait and the load one L2 round
+// trip, needs no release fence on the writers' side, and makes the sum independent of the order of arrival:
+// every CTA derives bit-identical x, and a step's result is reproducible from run to run.
 //
 // Weights never wait for a barrier, and a barrier never waits behind weights.  Each CTA's rows of the seven
 // matrices of a layer are packed once (pack_weights_kernel) in the order and with the row padding of four
@@ -23,9 +28,8 @@
 // products run on the tensor cores (mma.sync m16n8k16) with the fp32 activation vector split into three bf16
 // columns, which is exact to fp32 and needs no warp-shuffle reductions.
 //
-// A grid barrier is an arrive (red.release) and a later bounded wait (relaxed poll + acquire fence).  Every wait
-// is bounded: a wait that gives up records a status word and turns the remaining waits of the CTA into no-ops,
-// so a launch always terminates and the host reads the error.
+// Every wait is bounded: a wait that gives up records a status word and turns the remaining waits of the CTA into
+// no-ops, so a launch always terminates and the host reads the error.
 //
 // What the reference does for the same step: csrc/qwen3_step.cu:382-818 (four barriers per layer,
 // attention recomputed by every slice CTA, fixed position 128).
@@ -59,12 +63,15 @@ constexpr int WOROW = 136;                    // the same for the 128-column Wo 
 constexpr int ATT_WARPS = 8;                  // split attention: warps that attend positions (32 positions per pass)
 // Local attention (every CTA attends its whole head over all cached positions) serves up to 255 positions; measured,
 // splitting the positions over the 18 CTAs of a kv group wins beyond that.
-#ifndef Q3_N_ACC
-#define Q3_N_ACC 2
-#endif
-constexpr int N_ACC = Q3_N_ACC;               // accumulators for the FFN delta (fewer same-address atomics each)
 constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
-constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;   // patience of every device-side wait: 200 ms
+constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;   // default patience of every device-side wait: 200 ms
+constexpr int MAX_LAYERS = 63;                // the q/k/v tags of a launch are epoch * 64 + layer + 1
+// Counted accumulators: word = (contributions << 56) + sum of round(v * 2^32) as a 56-bit two's complement number.
+// A contribution is clamped to +-ACC_CLAMP so that MAX_GRID of them cannot reach the count field (2^55 / 2^32 = 8.4e6).
+constexpr float ACC_SCALE = 4294967296.f;     // 2^32: resolution 2.3e-10, finer than fp32 for every |x| above 4e-3
+constexpr float ACC_CLAMP = 50000.f;
+constexpr int MAX_GRID = 160;                 // 160 * ACC_CLAMP < 2^23
+constexpr unsigned long long ACC_ONE = 1ull << 56, ACC_HALF = 1ull << 55;
 // fp32 tail of shared memory: 8 KB union | q_s[2][128] k_s v_s | o split [3][128] bf16 | hid split [3][32] bf16 | red lw misc | scores
 constexpr int FBUF_FLOATS = 2048 + 4 * 128 + 192 + 48 + 32 + 16 + 16 + 3 * SC_HALF;
 constexpr int TAIL_BYTES = FBUF_FLOATS * 4 + 8 * 8 + 16;
@@ -81,15 +88,14 @@ struct PersistParams {
     long long* next_token;
     bf16_raw* k_write;
     bf16_raw* v_write;
-    float* X0;        // [1024] materialised residual read by Q
-    float* X1;        // [1024] materialised residual read by GD
-    float* dA;        // [2][1024] attention delta of layer l in buffer l & 1
-    float* dB;        // [2][N_ACC][1024] FFN delta of layer l in buffer l & 1
+    unsigned long long* dA;   // [2][1024] counted accumulators: attention delta of layer l in buffer l & 1 (16 contributions an element)
+    unsigned long long* dB;   // [2][1024] FFN delta of layer l in buffer l & 1 (one contribution per CTA and element)
     unsigned long long* xq;   // [4096] q | k | v rows of the current layer, each a (tag << 32 | fp32 bits) word
     const unsigned* epoch;    // launches completed on this state; gives every (launch, layer) its own tag
     unsigned long long* xp;   // [8 groups][2 heads][18 CTAs][XP_STRIDE] split-attention partials (max, sum, -, -, o[128]), tagged like xq
     const float* rope;
-    unsigned* sync;   // [0] grid barrier counter, [2] end-of-step ticket
+    unsigned* sync;   // [2] end-of-step ticket
+    unsigned long long wait_ns;   // patience of every device-side wait
     uint32_t* status;
     float* pval;
     int* pidx;
@@ -100,7 +106,7 @@ struct PersistParams {
 struct PersistState {
     bf16_raw* packed;       // the layer matrices re-laid per CTA (see pack_weights_kernel)
     const void* src[7];     // the seven pointers `packed` was built from
-    float* X;               // X0 | X1 | dA[2] | dB[2][N_ACC] | xq[4096] (64-bit words) | epoch | xp
+    float* X;               // dA[2] | dB[2] (64-bit words) | xq[4096] (64-bit words) | epoch | xp
     int grid, smem;
 };
 
@@ -108,7 +114,8 @@ struct PersistState {
 // one layer takes.  Used by the decode kernel and by the kernel that packs the weights.
 constexpr int XP_STRIDE = 132;                // 64-bit words per published partial
 constexpr size_t XP_WORDS = (size_t)KV_HEADS * 2 * GROUP_CTAS * XP_STRIDE;
-constexpr size_t X_FLOATS = (size_t)(4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM + 64 + 2 * XP_WORDS;
+constexpr size_t ACC_FLOATS = (size_t)2 * 4 * HIDDEN;   // four vectors of 64-bit words
+constexpr size_t X_FLOATS = ACC_FLOATS + 2 * QKV_DIM + 64 + 2 * XP_WORDS;
 struct Share {
     int q0, nq, qmax;       // rows [q0, q0 + nq) of [wq; wk; wv], slot rows qmax
     int i0, ni, imax;       // FFN rows [i0, i0 + ni) of gate, up and down^T, slot rows imax
@@ -147,55 +154,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
+// ---- counted accumulators ----------------------------------------------------------------------------
+__device__ __forceinline__ void acc_add(unsigned long long* addr, float v) {
+    v = fminf(fmaxf(v, -ACC_CLAMP), ACC_CLAMP);
+    const unsigned long long w = ACC_ONE + (unsigned long long)__float2ll_rn(v * ACC_SCALE);
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(addr), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned acc_count(unsigned long long w) { return (unsigned)((w + ACC_HALF) >> 56); }
+__device__ __forceinline__ float acc_value(unsigned long long w) {
+    const long long s = (long long)((w + ACC_HALF) & (ACC_ONE - 1)) - (long long)ACC_HALF;
+    return __ll2float_rn(s) * (1.f / ACC_SCALE);
+}
 // barrier of the whole CTA (512 threads)
 __device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
-// ---- counters in global memory: arrive and bounded wait ---------------------------------------------
-__device__ __forceinline__ void counter_arrive(unsigned* cnt) {   // one thread, after a cta_sync
-    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
-}
-// thread 0 polls until *cnt has reached `target` (wrap-safe), then every thread passes a cta_sync
-__device__ __forceinline__ void counter_wait(const unsigned* cnt, unsigned target, volatile int* abort_flag,
-                                             uint32_t* status, uint32_t site) {
-    if (threadIdx.x == 0 && !*abort_flag) {
-        unsigned v;
-        unsigned long long t0 = 0;
-        unsigned it = 0;
-        for (;;) {
-            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
-            if ((int)(v - target) >= 0) break;
-            if ((++it & 1023u) == 0) {
-                const unsigned long long t = global_ns();
-                if (t0 == 0) t0 = t;
-                else if (t - t0 > WAIT_NS) {
-                    report(status, ST_BARRIER_TIMEOUT, site, v);
-                    *abort_flag = 1;
-                    break;
-                }
-            }
-        }
-        asm volatile("fence.acquire.gpu;" ::: "memory");
-    }
-    cta_sync();
-}
 // bounded wait on a shared-memory mbarrier; returns false when it gave up
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site,
+                                          unsigned long long wait_ns) {
     unsigned it = 0;
     unsigned long long t0 = 0;
     while (!mbar_try_wait(b, parity)) {
         if ((++it & 255u) == 0) {
             const unsigned long long t = global_ns();
             if (t0 == 0) t0 = t;
-            else if (t - t0 > WAIT_NS) {
+            else if (t - t0 > wait_ns) {
                 if ((threadIdx.x & 31) == 0) { report(status, ST_MBAR_TIMEOUT, site, parity); *abort_flag = 1; }
                 return false;
             }
@@ -206,12 +193,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile
 
 // a single non-blocking test when the slot is already full (the normal case: the copies were issued a
 // phase or more ahead); a late slot is polled by one lane per warp
-__device__ __forceinline__ void slot_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site) {
+__device__ __forceinline__ void slot_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site,
+                                          unsigned long long wait_ns) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
     if (__all_sync(0xffffffffu, ok != 0)) return;
-    if ((threadIdx.x & 31) == 0) mbar_wait(b, parity, abort_flag, status, site);
+    if ((threadIdx.x & 31) == 0) mbar_wait(b, parity, abort_flag, status, site, wait_ns);
     __syncwarp();
 }
 
@@ -295,6 +283,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int c = blockIdx.x, G = gridDim.x;
     const int L = p.n_layers;
+    const unsigned long long wait_ns = p.wait_ns;
     if (p.seq_len[0] > mode_max_len(MODE) || p.seq_len[0] < 0) {   // the same for every CTA: nothing has been started yet
         if (tid == 0) report(p.status, ST_BAD_LEN, (uint32_t)MODE, (uint32_t)p.seq_len[0]);
         return;
@@ -337,11 +326,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     volatile int* abort_flag = reinterpret_cast<volatile int*>(full + 8);
 
     const int n_ev = 4 + EV_PER_LAYER * L;
-#ifdef Q3_FINE
-#define Q3_FINE_T(k) do { if (p.trace != nullptr && tid == 0) p.trace[(size_t)G * n_ev + ((size_t)c * L + l) * 32 + (k)] = clock64(); } while (0)
-#else
-#define Q3_FINE_T(k) do {} while (0)
-#endif
 #define Q3_TRACE(ev) do { if (p.trace != nullptr && tid == 0) p.trace[(size_t)c * n_ev + (ev)] = global_ns(); } while (0)
     Q3_TRACE(0);
     if (tid == 0) {
@@ -439,22 +423,39 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     const bf16_raw* vcache = reinterpret_cast<const bf16_raw*>(p.seq_v[0]);
     const long long lstride = p.seq_layer_stride[0];
     const float* rope_row = p.rope + (size_t)len * HEAD_DIM;
-    // x = X0 + sum of the FFN delta accumulators, two elements per thread
-    auto load_x_ffn = [&](const float* dBl, float& x0, float& x1) {
-        float2 a = ldcg2(p.X0 + 2 * tid);
-        float2 d[N_ACC];
-#pragma unroll
-        for (int i = 0; i < N_ACC; ++i) d[i] = ldcg2(dBl + (size_t)i * HIDDEN + 2 * tid);
-        float s0 = d[0].x, s1 = d[0].y;
-#pragma unroll
-        for (int i = 1; i < N_ACC; ++i) { s0 += d[i].x; s1 += d[i].y; }
-        x0 = a.x + s0; x1 = a.y + s1;
+    // The residual stream: elements 2 tid and 2 tid + 1 of x, the same values in every CTA.
+    float x0, x1;
+    {
+        const uint32_t e = *reinterpret_cast<const uint32_t*>(p.embed + (size_t)tok * HIDDEN + 2 * tid);
+        x0 = bf_lo(e); x1 = bf_hi(e);
+    }
+    // x += a delta, once all `expect` contributions to this thread's two words have arrived (bounded).  The wait IS the
+    // load: no counter, no fence; a word that is complete cannot change any more until the buffer is cleared.
+    auto acc_wait = [&](const unsigned long long* vec, unsigned expect, uint32_t site) {
+        unsigned long long w0 = 0, w1 = 0;
+        if (!*abort_flag) {
+            const unsigned long long* src = vec + 2 * tid;
+            unsigned it = 0;
+            unsigned long long t0 = 0;
+            for (;;) {
+                asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(src) : "memory");
+                if (acc_count(w0) == expect && acc_count(w1) == expect) break;
+                if ((++it & 63u) == 0) {
+                    if (*abort_flag) break;
+                    const unsigned long long t = global_ns();
+                    if (t0 == 0) t0 = t;
+                    else if (t - t0 > wait_ns) {
+                        report(p.status, ST_BARRIER_TIMEOUT, site, acc_count(w0));
+                        *abort_flag = 1;
+                        break;
+                    }
+                }
+            }
+        }
+        x0 += acc_value(w0); x1 += acc_value(w1);
     };
     // Every (launch, layer) tags its q/k/v words differently, so a reader can tell a fresh word from an old one.
-    const unsigned tag_base = __ldcg(p.epoch) * 32u;
-
-    unsigned* bar = p.sync;
-    unsigned target = 0;
+    const unsigned tag_base = __ldcg(p.epoch) * 64u;
     const int quarter = lane >> 3, sub = lane & 7;
     // ldmatrix.x4 row addresses of a 16 x 16 A tile: lanes 0-7 rows 0-7, 8-15 rows 8-15 (k 0-7); 16-31 the same rows at k 8-15
     const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8, lm_k = (lane >> 4) * 8;
@@ -476,10 +477,13 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 
     for (int l = 0; l < L; ++l) {
         const int ev = 1 + EV_PER_LAYER * l;
-        // The two deltas alternate between two buffers: a buffer is cleared one phase after its last reader
-        // has passed a grid barrier and at least one grid barrier before its next writer starts.
-        float* dAl = p.dA + (size_t)(l & 1) * HIDDEN;
-        float* dBl = p.dB + (size_t)(l & 1) * N_ACC * HIDDEN;
+        // The two deltas alternate between two buffers.  CTA 1 clears, during the F phase of layer l, the attention
+        // buffer of layer l - 1 and the FFN buffer of layer l - 2: it has seen the FFN delta of layer l - 1 complete, so
+        // every CTA has finished GD of layer l - 1 and with it every read of those two.  The clearing warps fence before
+        // the CTA's own contributions to the attention delta of layer l go out, and nobody writes either buffer again
+        // before having seen that delta (the FFN buffer) or the next FFN delta (the attention buffer) complete.
+        unsigned long long* dAl = p.dA + (size_t)(l & 1) * HIDDEN;
+        unsigned long long* dBl = p.dB + (size_t)(l & 1) * HIDDEN;
         const unsigned tag = tag_base + (unsigned)l + 1u;
         // K and V rows of the cached positions, fetched at the very start of the layer (they depend on nothing of this
         // step), so that they have arrived, and the SM's input path is quiet, when the q/k/v exchange starts polling.
@@ -538,19 +542,9 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         };
         // ==================================================================== Q
         {
-            float x0, x1;
-            Q3_FINE_T(27);
-            if (l == 0) {
-                const uint32_t e = *reinterpret_cast<const uint32_t*>(p.embed + (size_t)tok * HIDDEN + 2 * tid);
-                x0 = bf_lo(e); x1 = bf_hi(e);
-            } else {
-                load_x_ffn(p.dB + (size_t)((l - 1) & 1) * N_ACC * HIDDEN, x0, x1);
-            }
+            if (l > 0) acc_wait(p.dB + (size_t)((l - 1) & 1) * HIDDEN, (unsigned)G, 300 + l - 1);
+            if (l > 0) Q3_TRACE(ev - 1);   // the previous layer's slot 11: FFN delta complete
             fetch_slot(3, l);   // down rows of this layer: landed before the q/k/v exchange starts polling
-            if (c == 0) __stcg(reinterpret_cast<float2*>(p.X1 + 2 * tid), make_float2(x0, x1));
-            if (c == 1 && l + 1 < L) __stcg(reinterpret_cast<float2*>(p.dA + (size_t)((l + 1) & 1) * HIDDEN + 2 * tid), make_float2(0.f, 0.f));
-            if (c == G - 1 && l == 0)
-                for (int i = tid; i < N_ACC * HIDDEN / 2; i += CT) __stcg(reinterpret_cast<float2*>(p.dB) + i, make_float2(0.f, 0.f));
             {   // stage x * gain split in three bf16 parts (the 1/rms factor is applied to the row sums)
                 bf16_raw h0, m0, l0, h1, m1, l1;
                 split3(x0 * bf_lo(gain2), h0, m0, l0);
@@ -559,16 +553,13 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 xsp[512 + tid] = (uint32_t)m0 | ((uint32_t)m1 << 16);
                 xsp[1024 + tid] = (uint32_t)l0 | ((uint32_t)l1 << 16);
             }
-            Q3_FINE_T(28);
             const float ss = warp_sum(x0 * x0 + x1 * x1);
             if (lane == 0) red[warp] = ss;
-            Q3_FINE_T(29);
             // the warps that will poll the q/k/v exchange request their K/V rows now (x is staged: nothing queues behind
             // these loads), the others while they wait for the exchange
             if (warp >= 8 && warp < 12) kv_prefetch();
             cta_sync();
             Q3_TRACE(ev + 0);
-            Q3_FINE_T(0);
             // warp w: k range [64 w, 64 w + 64) of both 16-row tiles of this CTA's rows
             uint32_t bq[4][2];
 #pragma unroll
@@ -577,9 +568,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 bq[t][0] = (fr_n < 3) ? xsp[fr_n * 512 + kp] : 0u;
                 bq[t][1] = (fr_n < 3) ? xsp[fr_n * 512 + kp + 4] : 0u;
             }
-            Q3_FINE_T(1);
-            slot_wait(&full[0], l & 1, abort_flag, p.status, 10);
-            Q3_FINE_T(2);
+            slot_wait(&full[0], l & 1, abort_flag, p.status, 10, wait_ns);
             {
                 uint32_t af[2][4][4];
 #pragma unroll
@@ -619,8 +608,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     const unsigned long long word = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint((v0 + v1) * r);
                     asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p.xq + q0 + tid), "l"(word) : "memory");
                 }
-                Q3_FINE_T(3);
-                Q3_FINE_T(4);
                 Q3_TRACE(ev + 1);
             }
             if (warp < 8 || warp >= 12) kv_prefetch();   // after the rows are published: nothing waits for these warps now
@@ -641,7 +628,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         }
         fetch_slot(2, l);       // gate/up rows of this layer: in flight during F, landed before its barrier is polled
         Q3_TRACE(ev + 2);
-        Q3_FINE_T(30);
 
         // ==================================================================== F
         if (has_f) {
@@ -662,7 +648,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         if ((++it & 127u) == 0) {
                             const unsigned long long t = global_ns();
                             if (t0 == 0) t0 = t;
-                            else if (t - t0 > WAIT_NS) {
+                            else if (t - t0 > wait_ns) {
                                 if (lane == 0) { report(p.status, ST_BARRIER_TIMEOUT, 100 + l, (uint32_t)(w0 >> 32)); *abort_flag = 1; }
                                 break;
                             }
@@ -699,7 +685,11 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     }
                 }
             }
-            Q3_FINE_T(31);
+            if (c == 1 && (warp == 13 || warp == 14)) {   // idle warps of CTA 1: recycle the delta buffers (see the top of the loop)
+                unsigned long long* buf = (warp == 13) ? p.dA + (size_t)((l + 1) & 1) * HIDDEN : dBl;
+                for (int i = lane; i < HIDDEN / 2; i += 32) __stcg(reinterpret_cast<ulonglong2*>(buf) + i, make_ulonglong2(0ull, 0ull));
+                __threadfence();
+            }
             cta_sync();
             Q3_TRACE(ev + 3);
 
@@ -708,7 +698,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 float qa[16];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) { qa[i] = q_s[fhh * 128 + sub * 8 + i]; qa[8 + i] = q_s[fhh * 128 + 64 + sub * 8 + i]; }
-                Q3_FINE_T(16);
                 float tmax = -INFINITY;
                 auto score_pass = [&](const uint4& k0, const uint4& k1, int ps) {
                     const int pos = ps * 64 + att_slot;
@@ -737,14 +726,11 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     if (lane == 0) misc[0] = sn_;
                     tmax = fmaxf(tmax, sn_);
                 }
-                Q3_FINE_T(17);
                 tmax = warp_max(tmax);
                 if (lane == 0) red[warp] = tmax;
                 cta_sync();
-                Q3_FINE_T(18);
                 float M = (lane < CW) ? red[lane] : -INFINITY;
                 M = warp_max(M);
-                Q3_FINE_T(19);
 
                 // P.V with a warp per position and four dims per lane: every lane of the warp forms the same
                 // probability from the shared score, so nothing crosses lanes
@@ -771,12 +757,10 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         acc[i & 1][2] = fmaf(pr, bf_lo(vy), acc[i & 1][2]); acc[i & 1][3] = fmaf(pr, bf_hi(vy), acc[i & 1][3]);
                     }
                 }
-                Q3_FINE_T(21);
                 *reinterpret_cast<float4*>(om + warp * 128 + lane * 4) =
                     make_float4(acc[0][0] + acc[1][0], acc[0][1] + acc[1][1], acc[0][2] + acc[1][2], acc[0][3] + acc[1][3]);
                 if (lane == 0) lw[warp] = lsum;
                 cta_sync();
-                Q3_FINE_T(23);
                 Q3_TRACE(ev + 4);
                 Q3_TRACE(ev + 5);
                 if (tid < HEAD_DIM) {
@@ -791,10 +775,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     reinterpret_cast<bf16_raw*>(osp + 128)[tid] = lo_;
                 }
                 cta_sync();
-                Q3_FINE_T(24);
             } else {
             // ---- scores of this CTA's cached positions, both heads: a quarter-warp per position ----
-                Q3_FINE_T(16);
                 float tmax0 = -INFINITY, tmax1 = -INFINITY;
                 if (warp < ATT_WARPS) {
                     float qa[2][16];
@@ -834,9 +816,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     const float sn_ = warp_sum(a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w);
                     if (lane == 0) misc[0] = sn_;
                 }
-                Q3_FINE_T(17);
                 cta_sync();
-                Q3_FINE_T(18);
                 float M0 = (lane < ATT_WARPS) ? red[lane] : -INFINITY, M1 = (lane < ATT_WARPS) ? red[8 + lane] : -INFINITY;
                 M0 = warp_max(M0); M1 = warp_max(M1);
 
@@ -869,9 +849,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     *reinterpret_cast<float4*>(om + (warp * 2 + 1) * 128 + lane * 4) = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
                     if (lane == 0) { lw[warp * 2] = l0; lw[warp * 2 + 1] = l1; }
                 }
-                Q3_FINE_T(19);
                 cta_sync();
-                Q3_FINE_T(21);
                 // ---- publish the CTA's partial of both heads: (max, sum, unnormalised output), every word tagged ----
                 if (tid < 256) {
                     const int hh = tid >> 7, d = tid & 127;
@@ -887,7 +865,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     }
                 }
                 Q3_TRACE(ev + 4);
-                Q3_FINE_T(23);
 
                 // ---- merge the 18 partials of this CTA's head with the new row.  Step 1: one warp polls the 18
                 //      (max, sum) pairs, which their writers store last, so that the polling stays light; step 2:
@@ -919,7 +896,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         if ((++it & 255u) == 0) {
                             const unsigned long long t = global_ns();
                             if (t0 == 0) t0 = t;
-                            else if (t - t0 > WAIT_NS) {
+                            else if (t - t0 > wait_ns) {
                                 if (lane == 0) { report(p.status, ST_BARRIER_TIMEOUT, 400 + l, 0); *abort_flag = 1; }
                                 break;
                             }
@@ -928,7 +905,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     if (lane < GROUP_CTAS) { pm_s[lane] = __uint_as_float((unsigned)wa); pl_s[lane] = __uint_as_float((unsigned)wb); }
                 }
                 cta_sync();
-                Q3_FINE_T(22);
                 if (tid < 2 * HEAD_DIM) {
                     const int half = mhalf, d = md;
                     float M, Ls, o;
@@ -952,14 +928,13 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         if ((++it & 63u) == 0) {
                             const unsigned long long t = global_ns();
                             if (t0 == 0) t0 = t;
-                            else if (t - t0 > WAIT_NS) {
+                            else if (t - t0 > wait_ns) {
                                 if (lane == 0) { report(p.status, ST_BARRIER_TIMEOUT, 450 + l, 0); *abort_flag = 1; }
                                 break;
                             }
                         }
                         load_outputs();
                     }
-                    Q3_FINE_T(24);
                     q_s[half * 128 + d] = o;                       // the queries are dead by now
                     if (d == 0) { misc[4 + 2 * half] = M; misc[5 + 2 * half] = Ls; }
                 }
@@ -983,8 +958,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             }
 
             // ---- Wo slice on the tensor cores: warp (rt, kh) = 16 rows x 64 head dims ----
-            slot_wait(&full[1], l & 1, abort_flag, p.status, 11);
-            Q3_FINE_T(25);
+            slot_wait(&full[1], l & 1, abort_flag, p.status, 11, wait_ns);
             {
                 const int rt = warp >> 1, kh = warp & 1;
                 float cc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1003,30 +977,18 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 if ((lane & 3) == 0) { wo_part[kh * 128 + 16 * rt + fr_n] = r0; wo_part[kh * 128 + 16 * rt + fr_n + 8] = r1; }
             }
             cta_sync();
-            Q3_FINE_T(26);
-            if (tid < fn / 4) {   // fn <= 116: warp 0 adds the slice to the attention delta
-                const float4 a = *reinterpret_cast<const float4*>(wo_part + 4 * tid), b = *reinterpret_cast<const float4*>(wo_part + 128 + 4 * tid);
-                red_add_v4(dAl + fr0 + 4 * tid, a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
-            }
-            if (warp == 0) __syncwarp();
+            if (tid < fn) acc_add(dAl + fr0 + tid, wo_part[tid] + wo_part[128 + tid]);   // fn <= 116: the slice joins the attention delta
+            cta_sync();   // wo_part is the next phase's staging area
         }
         Q3_TRACE(ev + 6);
-        if (tid == 0) counter_arrive(bar);
-        target += G;
         gain2 = *reinterpret_cast<const uint32_t*>(p.ln2 + (size_t)l * HIDDEN + 2 * tid);
-        counter_wait(bar, target, abort_flag, p.status, 200 + l);
-        Q3_TRACE(ev + 7);
 
         // ==================================================================== GD
         {
-            const float2 a = ldcg2(p.X1 + 2 * tid), d = ldcg2(dAl + 2 * tid);
-            const float x0 = a.x + d.x, x1 = a.y + d.y;
-            fetch_slot(0, l + 1);   // q/k/v rows and Wo slice of the next layer: landed before this phase's barrier is polled
+            acc_wait(dAl, (unsigned)Q_HEADS, 200 + l);   // every row of the attention delta receives one slice per query head
+            Q3_TRACE(ev + 7);
+            fetch_slot(0, l + 1);   // q/k/v rows and Wo slice of the next layer: landed before the next exchange is polled
             fetch_slot(1, l + 1);
-            if (c == 0) __stcg(reinterpret_cast<float2*>(p.X0 + 2 * tid), make_float2(x0, x1));
-            if (c == G - 1 && l + 1 < L)   // the next layer's FFN delta starts from zero
-                for (int i = tid; i < N_ACC * HIDDEN / 2; i += CT)
-                    __stcg(reinterpret_cast<float2*>(p.dB + (size_t)((l + 1) & 1) * N_ACC * HIDDEN) + i, make_float2(0.f, 0.f));
             {
                 bf16_raw h0, m0, l0, h1, m1, l1;
                 split3(x0 * bf_lo(gain2), h0, m0, l0);
@@ -1040,7 +1002,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             cta_sync();
             Q3_TRACE(ev + 8);
             {
-                Q3_FINE_T(5);
                 // The slot holds one matrix of 2 * imax = 42 rows (gate rows, then up rows): three 16-row tiles cover it
                 // (the last six rows of the third tile belong to the next slot and are never used).  Warp w takes
                 // the k range [64 w, 64 w + 64) of all three tiles.
@@ -1051,9 +1012,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     bx[t][0] = (fr_n < 3) ? xsp[fr_n * 512 + kp] : 0u;
                     bx[t][1] = (fr_n < 3) ? xsp[fr_n * 512 + kp + 4] : 0u;
                 }
-                Q3_FINE_T(6);
-                slot_wait(&full[2], l & 1, abort_flag, p.status, 12);
-                Q3_FINE_T(7);
+                slot_wait(&full[2], l & 1, abort_flag, p.status, 12, wait_ns);
                 uint32_t af[3][4][4];
 #pragma unroll
                 for (int rt = 0; rt < 3; ++rt) {
@@ -1080,7 +1039,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     fold_cols(cg[rt][0], r0, r1);
                     if ((lane & 3) == 0) { gpart[warp * 48 + 16 * rt + fr_n] = r0; gpart[warp * 48 + 16 * rt + fr_n + 8] = r1; }
                 }
-                Q3_FINE_T(8);
                 cta_sync();
                 if (tid < 32) {   // hid of this CTA's rows, split for the down projection; rows past the share are zero
                     float hv = 0.f;
@@ -1102,9 +1060,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             cta_sync();   // hid ready; the activations and the gate/up slot are no longer needed
             Q3_TRACE(ev + 9);
 
-            Q3_FINE_T(9);
-            slot_wait(&full[3], l & 1, abort_flag, p.status, 13);
-            Q3_FINE_T(10);
+            slot_wait(&full[3], l & 1, abort_flag, p.status, 13, wait_ns);
             {   // out[n] = sum_i wdT[i][n] * hid[i]: A = transposed tiles of the slot, k = this CTA's (<= 32) rows
                 uint32_t bh[2][2];
 #pragma unroll
@@ -1141,31 +1097,23 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     if ((lane & 3) == 0) { dout[n0 + fr_n] = r0; dout[n0 + fr_n + 8] = r1; }
                 }
             }
-            Q3_FINE_T(11);
             cta_sync();
-            Q3_FINE_T(12);
-            if (tid < 256) {
-                const float4 t = *reinterpret_cast<const float4*>(dout + tid * 4);
-                red_add_v4(dBl + (size_t)(c & (N_ACC - 1)) * HIDDEN + tid * 4, t.x, t.y, t.z, t.w);
+            {
+                const float2 t = *reinterpret_cast<const float2*>(dout + 2 * tid);
+                acc_add(dBl + 2 * tid, t.x);
+                acc_add(dBl + 2 * tid + 1, t.y);
             }
-            Q3_FINE_T(13);
-            cta_sync();
-            Q3_FINE_T(14);
+            cta_sync();   // dout is the next phase's staging area
             Q3_TRACE(ev + 10);
-            if (tid == 0) counter_arrive(bar);
         }
-        target += G;
         gain2 = (l + 1 < L) ? *reinterpret_cast<const uint32_t*>(p.ln1 + (size_t)(l + 1) * HIDDEN + 2 * tid)
                             : *reinterpret_cast<const uint32_t*>(p.fnorm + 2 * tid);
-        counter_wait(bar, target, abort_flag, p.status, 300 + l);
-        Q3_TRACE(ev + 11);
     }
 
     // ======================================================================== LM head + argmax
     {
-        float x0, x1;
-        load_x_ffn(p.dB + (size_t)((L - 1) & 1) * N_ACC * HIDDEN, x0, x1);
-        if (c == 1) __stcg(reinterpret_cast<float2*>(p.dA + 2 * tid), make_float2(0.f, 0.f));   // the next launch's first F phase adds into dA[0]
+        acc_wait(p.dB + (size_t)((L - 1) & 1) * HIDDEN, (unsigned)G, 300 + L - 1);
+        Q3_TRACE(EV_PER_LAYER * L);   // the last layer's slot 11
         const float ss = warp_sum(x0 * x0 + x1 * x1);
         if (lane == 0) red[warp] = ss;
         cta_sync();
@@ -1221,11 +1169,11 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     if (bv_s[w] > bv || (bv_s[w] == bv && bi_s[w] < bi)) { bv = bv_s[w]; bi = bi_s[w]; }
                 p.next_token[0] = bi;
                 if (p.append) p.seq_len[0] = len + 1;
-                // every CTA has passed every barrier: rearm the counters for the next launch
-                p.sync[0] = 0;
                 p.sync[2] = 0;
-                *const_cast<unsigned*>(p.epoch) = tag_base / 32u + 1u;
+                *const_cast<unsigned*>(p.epoch) = tag_base / 64u + 1u;
             }
+            // every CTA has read its last delta: the next launch starts from clean accumulators
+            for (int i = tid; i < 4 * HIDDEN / 2; i += CT) __stcg(reinterpret_cast<ulonglong2*>(p.dA) + i, make_ulonglong2(0ull, 0ull));
         }
         Q3_TRACE(2 + EV_PER_LAYER * L);
     }
@@ -1233,10 +1181,9 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     // shared memory back; after a clean step these four tests succeed at once.
     if (pumper) {
         for (int slot = 0; slot < 4; ++slot)
-            if (pump_armed & (1 << slot)) mbar_wait(&full[slot], (uint32_t)((pump_parity >> slot) & 1), abort_flag, p.status, 30 + slot);
+            if (pump_armed & (1 << slot)) mbar_wait(&full[slot], (uint32_t)((pump_parity >> slot) & 1), abort_flag, p.status, 30 + slot, wait_ns);
     }
 #undef Q3_TRACE
-#undef Q3_FINE_T
 }
 
 
@@ -1316,7 +1263,9 @@ int persist_setup(q3_engine* e) {
     e->p_grid = 0; e->p_threads = PT; e->p_smem = 0; e->p_state = nullptr;
     int grid = e->sm_count;
     if (e->cfg.grid_limit > 0 && e->cfg.grid_limit < grid) grid = e->cfg.grid_limit;
-    if (grid < MIN_GRID) return Q3_OK;   // too few CTAs for the slot sizes: the layered path serves everything
+    // too few CTAs for the slot sizes, too many for the accumulators' count field, or more layers than a launch has
+    // tags for: the layered path serves everything
+    if (grid < MIN_GRID || grid > MAX_GRID || e->cfg.n_layers > MAX_LAYERS) return Q3_OK;
     static_assert(2 * ((INTER + MIN_GRID - 1) / MIN_GRID) <= 48, "the gate/up rows of a CTA must fit three 16-row tiles");
     const int smem = smem_bytes_for(grid);
     cudaDeviceProp prop;
@@ -1391,6 +1340,13 @@ int persist_recover(q3_engine* e) {
     return Q3_OK;
 }
 
+void* persist_accumulators(const q3_engine* e, int64_t* bytes) {
+    PersistState* s = static_cast<PersistState*>(e->p_state);
+    if (!s) return nullptr;
+    *bytes = (int64_t)(ACC_FLOATS * sizeof(float));
+    return s->X;
+}
+
 void persist_invalidate_weights(q3_engine* e) {
     PersistState* s = static_cast<PersistState*>(e->p_state);
     if (s) for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
@@ -1407,10 +1363,11 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
     p.seq_k = a->seq_k; p.seq_v = a->seq_v; p.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
     p.seq_len = a->seq_len; p.logits = a->logits; p.next_token = reinterpret_cast<long long*>(a->next_token);
     p.k_write = reinterpret_cast<bf16_raw*>(a->k_write); p.v_write = reinterpret_cast<bf16_raw*>(a->v_write);
-    p.X0 = s->X; p.X1 = s->X + HIDDEN; p.dA = s->X + 2 * HIDDEN; p.dB = s->X + 4 * HIDDEN;
-    p.xq = reinterpret_cast<unsigned long long*>(s->X + (4 + 2 * N_ACC) * HIDDEN);
-    p.epoch = reinterpret_cast<const unsigned*>(s->X + (4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM);
-    p.xp = reinterpret_cast<unsigned long long*>(s->X + (4 + 2 * N_ACC) * HIDDEN + 2 * QKV_DIM + 64);
+    p.dA = reinterpret_cast<unsigned long long*>(s->X); p.dB = p.dA + 2 * HIDDEN;
+    p.xq = reinterpret_cast<unsigned long long*>(s->X + ACC_FLOATS);
+    p.epoch = reinterpret_cast<const unsigned*>(s->X + ACC_FLOATS + 2 * QKV_DIM);
+    p.xp = reinterpret_cast<unsigned long long*>(s->X + ACC_FLOATS + 2 * QKV_DIM + 64);
+    p.wait_ns = e->cfg.wait_limit_us > 0 ? (unsigned long long)e->cfg.wait_limit_us * 1000ull : WAIT_NS;
     p.rope = e->rope; p.sync = e->sync; p.status = e->status; p.pval = e->pval; p.pidx = e->pidx;
     p.trace = (e->trace && e->trace_words >= (int64_t)s->grid * (4 + EV_PER_LAYER * e->cfg.n_layers)) ? e->trace : nullptr;
     p.n_layers = e->cfg.n_layers; p.vocab = e->cfg.vocab; p.append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;

@@ -13,6 +13,7 @@
 // fully rewritten before it is read, the status words are cleared on the stream at the start of each
 // call), and two calls that overlap on the GPU would race on it.
 #include <cstring>
+#include <mutex>
 
 #include "q3_engine.h"
 
@@ -41,8 +42,48 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(Scratch)
 constexpr int MAX_DEVICES = 64;
 Scratch* g_device_ptr[MAX_DEVICES] = {};
 int g_sm_count[MAX_DEVICES] = {};
+std::mutex g_setup_lock;   // the per-device set-up may be reached from several host threads at once
+
+// Resolve (once per device, with that device current) the device address of the array.  Returns Q3_OK or an
+// error code with its message recorded.
+int scratch_of_current_device(int* dev_out, Scratch** out) {
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
+        return engine_fail(nullptr, Q3_ERR_CUDA, "q3_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(err));
+    *dev_out = dev;
+    std::lock_guard<std::mutex> hold(g_setup_lock);
+    if (!g_device_ptr[dev]) {
+        int major = 0, sms = 0;
+        err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess) return engine_fail(nullptr, Q3_ERR_CUDA, "q3_decode_noalloc: cudaDeviceGetAttribute: %s", cudaGetErrorString(err));
+        if (major != 10) return engine_fail(nullptr, Q3_ERR_UNSUPPORTED, "q3_decode_noalloc: device %d is sm_%dx; this library holds sm_100a code only", dev, major);
+        void* ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (err != cudaSuccess || !ptr) return engine_fail(nullptr, Q3_ERR_CUDA, "q3_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+        g_sm_count[dev] = sms;
+        g_device_ptr[dev] = static_cast<Scratch*>(ptr);
+    }
+    *out = g_device_ptr[dev];
+    return Q3_OK;
+}
 
 }  // namespace
+
+extern "C" int q3_noalloc_status(void* stream, uint32_t* words, int32_t n) {
+    int dev = -1;
+    Scratch* s = nullptr;
+    const int rc = scratch_of_current_device(&dev, &s);
+    if (rc != Q3_OK) return rc;
+    uint32_t h[Q3_STATUS_WORDS];
+    cudaError_t err = cudaStreamSynchronize((cudaStream_t)stream);
+    if (err == cudaSuccess) err = cudaMemcpy(h, s->status, sizeof(h), cudaMemcpyDeviceToHost);
+    if (err != cudaSuccess) return engine_fail(nullptr, Q3_ERR_CUDA, "q3_noalloc_status: %s", cudaGetErrorString(err));
+    for (int i = 0; words && i < n && i < Q3_STATUS_WORDS; ++i) words[i] = h[i];
+    if (h[0] == 0) return Q3_OK;
+    return engine_fail(nullptr, Q3_ERR_DEVICE_WAIT, "device status: code %u at site %u, block %u, value %u", h[0], h[1], h[2], h[3]);
+}
 
 extern "C" int q3_decode_noalloc(const q3_weights* w, const float* rope, int32_t rope_positions, int32_t n_layers, int32_t vocab,
                                  const q3_decode_args* a, void* stream) {
@@ -63,22 +104,10 @@ extern "C" int q3_decode_noalloc(const q3_weights* w, const float* rope, int32_t
             return engine_fail(nullptr, Q3_ERR_INVALID, "q3_decode_noalloc: weight %d is null or not 16-byte aligned", i);
 
     int dev = -1;
-    cudaError_t err = cudaGetDevice(&dev);
-    if (err != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
-        return engine_fail(nullptr, Q3_ERR_CUDA, "q3_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(err));
-    if (!g_device_ptr[dev]) {
-        // Set-up, once per device, with that device current: resolve the device address of the array.
-        void* ptr = nullptr;
-        err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-        if (err != cudaSuccess || !ptr)
-            return engine_fail(nullptr, Q3_ERR_CUDA, "q3_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
-        int sms = 0;
-        err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (err != cudaSuccess) return engine_fail(nullptr, Q3_ERR_CUDA, "q3_decode_noalloc: cudaDeviceGetAttribute: %s", cudaGetErrorString(err));
-        g_sm_count[dev] = sms;
-        g_device_ptr[dev] = static_cast<Scratch*>(ptr);
-    }
-    Scratch* s = g_device_ptr[dev];
+    Scratch* s = nullptr;
+    const int rc0 = scratch_of_current_device(&dev, &s);   // the first call on a device resolves the array's address
+    if (rc0 != Q3_OK) return rc0;
+    cudaError_t err;
 
     // A host-side engine record that points into the static array; nothing is allocated.
     q3_engine e;

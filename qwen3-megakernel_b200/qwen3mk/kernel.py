@@ -135,7 +135,7 @@ class Megakernel:
 
     def __init__(self, device=None, *, max_batch: int = 1, layers: int = LAYERS, vocab: int = VOCAB,
                  max_positions: int = 8192, path: str = "auto", grid_limit: int = 0, max_tokens: int = 0,
-                 pace_cycles: int = 0):
+                 wait_limit_us: int = 0):
         if not torch.cuda.is_available():
             raise RuntimeError("Megakernel needs a CUDA device (sm_100a); there is no CPU path")
         self.lib = _cabi.load()
@@ -150,7 +150,7 @@ class Megakernel:
         self.arch = f"sm_{major}{minor}"
         self.layers, self.vocab, self.max_batch = int(layers), int(vocab), int(max_batch)
         self._path_flag = {"auto": _cabi.F_PATH_AUTO, "layered": _cabi.F_PATH_LAYERED, "persist": _cabi.F_PATH_PERSIST}[path]
-        cfg = _cabi.Config(self.layers, self.vocab, self.max_batch, int(max_tokens), int(grid_limit), int(pace_cycles))
+        cfg = _cabi.Config(self.layers, self.vocab, self.max_batch, int(max_tokens), int(grid_limit), int(wait_limit_us))
         h = ctypes.c_void_p()
         rc = self.lib.q3_create(self.device.index or 0, ctypes.byref(cfg), ctypes.byref(h))
         _cabi.check(self.lib, None, rc, "q3_create")
@@ -162,6 +162,7 @@ class Megakernel:
         self.grid, self.threads, self.dyn_smem = g.value, t.value, s.value
         self._out_specs = output_specs(self.layers, self.vocab)
         self._weights_key = None
+        self._weights_ref = None
         self._seq_cache = {}     # step(): descriptors per (kcache ptr, vcache ptr, context)
         self._next = None        # step(): outputs of the next call, allocated while the kernel runs
         self._bound = None
@@ -190,16 +191,27 @@ class Megakernel:
         return tuple(torch.empty(lead + shape, dtype=dt, device=dev) for shape, dt in self._out_specs.values())
 
     def _set_weights(self, inputs: dict) -> None:
-        key = tuple(inputs[n].data_ptr() for n in WEIGHT_ORDER)
+        """Hand the 13 weight pointers to the engine when they, or the tensors' contents, have changed.
+
+        The persistent kernel streams an engine-owned re-layout of the layer matrices, so a change that keeps the
+        addresses must still reach the engine: the key holds every tensor's version counter (PyTorch bumps it on
+        every in-place write), and the engine keeps references to the tensors it packed, so that their memory cannot
+        be freed and handed out again, with other contents, at the same addresses."""
+        tensors = tuple(inputs[n] for n in WEIGHT_ORDER)
+        key = tuple((t.data_ptr(), t._version) for t in tensors)
         if key == self._weights_key:
             return
-        w = _cabi.Weights(*key)
+        ptrs = tuple(k[0] for k in key)
+        if self._weights_key is not None and ptrs == tuple(k[0] for k in self._weights_key):
+            self.lib.q3_invalidate_weights(self.handle)    # same addresses, rewritten in place
+        w = _cabi.Weights(*ptrs)
         _cabi.check(self.lib, self.handle, self.lib.q3_set_weights(self.handle, ctypes.byref(w)), "q3_set_weights")
         self._weights_key = key
+        self._weights_ref = tensors
 
     def refresh_weights(self) -> None:
-        """Forget the engine's packed copy of the layer matrices.  Call it after rewriting weight tensors
-        in place: the copy is otherwise rebuilt only when a weight tensor's address changes."""
+        """Forget the engine's packed copy of the layer matrices.  Only needed after a write that PyTorch's version
+        counters do not see (a raw-pointer write from another library): in-place tensor operations are noticed."""
         self.lib.q3_invalidate_weights(self.handle)
         self._weights_key = None
 
@@ -226,15 +238,17 @@ class Megakernel:
         """Kernels this engine has launched since creation."""
         return int(self.lib.q3_launch_count(self.handle))
 
-    def scratch(self, name: str) -> torch.Tensor:
-        """A copy of an engine scratch buffer ("x", "qkv", "attn", "hid") as a float32 tensor, for tools and tests."""
+    def scratch(self, name: str, view: bool = False) -> torch.Tensor:
+        """An engine scratch buffer ("x", "qkv", "attn", "hid", "status", "persist_acc") as a float32 tensor, for tools
+        and tests: a copy, or with view=True the engine's own memory (valid while the engine lives)."""
         p, n = ctypes.c_void_p(), ctypes.c_int64()
         rc = self.lib.q3_scratch(self.handle, name.encode(), ctypes.byref(p), ctypes.byref(n))
         _cabi.check(self.lib, self.handle, rc, "q3_scratch")
         class _Raw:  # expose the engine's buffer to torch through the CUDA array interface
             __cuda_array_interface__ = {"shape": (n.value // 4,), "typestr": "<f4", "data": (p.value, False), "version": 3}
         torch.cuda.synchronize(self.device)
-        return torch.as_tensor(_Raw(), device=self.device).clone()
+        t = torch.as_tensor(_Raw(), device=self.device)
+        return t if view else t.clone()
 
     def enable_trace(self, on: bool = True):
         """Phase time stamps of the persistent kernel: returns the int64 device tensor [grid, 4 + 12 * layers]

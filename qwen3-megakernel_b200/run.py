@@ -110,12 +110,14 @@ def cmd_bench(args) -> int:
     return 0
 
 
-PHASE_EVENTS = ["Q stage", "Q done", "K/V prefetch", "F q/k/v exchange", "F partial", "F group", "F done", "F->GD barrier",
-                "GD stage", "GD hid", "GD done", "GD->Q barrier"]
+PHASE_EVENTS = ["Q stage", "Q done", "K/V prefetch", "F q/k/v exchange", "F partial", "F group", "F done", "wait attn delta",
+                "GD stage", "GD hid", "GD done", "wait FFN delta"]
 
 
 def cmd_trace(args) -> int:
-    """Median duration of every traced segment of a layer, plus barrier skew and hop."""
+    """Median duration of every traced segment of a layer, plus the skew and the hop of the two delta waits (skew: how
+    long the last CTA's contribution trails the median CTA's; hop: from that last contribution to the median CTA having
+    the complete delta in registers)."""
     import numpy as np
 
     inputs, info = get_inputs("synthetic", args.seed, args.context)
@@ -142,7 +144,7 @@ def cmd_trace(args) -> int:
     for name, d in (("F", 6), ("GD", 10)):
         skew = np.median([t[:, 1 + ev * l + d].max() - np.median(t[:, 1 + ev * l + d]) for l in range(1, L)])
         hop = np.median([np.median(t[:, 2 + ev * l + d]) - t[:, 1 + ev * l + d].max() for l in range(1, L)])
-        print(f"  barrier after {name:<3} skew {skew:6.0f} ns  hop {hop:6.0f} ns")
+        print(f"  delta after {name:<3} skew {skew:6.0f} ns  hop {hop:6.0f} ns")
     return 0
 
 

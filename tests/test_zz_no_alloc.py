@@ -55,6 +55,18 @@ def test_noalloc_matches_engine_twice_in_a_row(oracle):
             assert int(nxt[b]) == int(ref["next_token"])
             assert oracle.rel_l2(logits[b], ref["logits"]) <= 1e-4
 
+        words = (ctypes.c_uint32 * 8)()
+        assert lib.q3_noalloc_status(torch.cuda.current_stream().cuda_stream, words, 8) == 0 and words[0] == 0
+
+    # a token outside the vocabulary is replaced by token 0 and reported through the status call
+    bad = torch.tensor([5, 10 ** 7], dtype=torch.int64, device="cuda")
+    a.token = bad.data_ptr()
+    assert lib.q3_decode_noalloc(ctypes.byref(w), rope.data_ptr(), rope.shape[0], 2, 2048, ctypes.byref(a),
+                                 torch.cuda.current_stream().cuda_stream) == 0
+    words = (ctypes.c_uint32 * 8)()
+    assert lib.q3_noalloc_status(torch.cuda.current_stream().cuda_stream, words, 8) == _cabi.ERR_DEVICE_WAIT
+    assert words[0] == 3 and b"code 3" in lib.q3_last_error(None)
+
     # sizes beyond the static scratch are refused, with a message
     a3 = _cabi.DecodeArgs(3, 10, _cabi.F_PATH_LAYERED, 0, 1, 1, 1, 1, 1, None, 1, None, None)
     assert lib.q3_decode_noalloc(ctypes.byref(w), rope.data_ptr(), rope.shape[0], 2, 2048, ctypes.byref(a3), None) == _cabi.ERR_INVALID
