@@ -198,13 +198,17 @@ def decode_step(w: dict, token, kcache: torch.Tensor, vcache: torch.Tensor, pos:
 
 @torch.no_grad()
 def greedy_decode(w: dict, token, kcache: torch.Tensor, vcache: torch.Tensor, steps: int,
-                  forced_tokens=None, on_step=None) -> dict:
+                  forced_tokens=None, on_step=None, forced_rows=None) -> dict:
     """`steps` consecutive decode steps.  After each step the new K/V rows are appended to the cache
     ROUNDED TO bf16 (what a cache of the kernel's output dtype holds; qwen3mk/kernel.py:48-49), and the
     argmax token (or `forced_tokens[i]` when teacher-forcing) feeds the next step.
 
     `on_step(i, out)` is called with every step's full output (logits, k_write, v_write), so that a checker
-    can gate each step without this loop keeping all logits.  Returns tokens [steps] (the argmax of every
+    can gate each step without this loop keeping all logits.  `forced_rows[i] = (k_row, v_row)` (bf16
+    [L, 8, 128]) replaces the rows this loop would append after step i: a checker replaying another
+    implementation's stream hands over that implementation's rows, so that both see the same cache at every
+    step (two correct implementations may round a row to different neighbouring bf16 values, after which
+    their caches, and with them all later logits, differ at the 2^-8 level).  Returns tokens [steps] (the argmax of every
     step), margins [steps] (top-1 minus top-2 logit), the final caches (bf16) and the last step's logits."""
     kc = kcache.to(torch.bfloat16).clone()
     vc = vcache.to(torch.bfloat16).clone()
@@ -218,8 +222,9 @@ def greedy_decode(w: dict, token, kcache: torch.Tensor, vcache: torch.Tensor, st
         toks.append(int(out["next_token"]))
         if on_step is not None:
             on_step(i, out)
-        kc = torch.cat([kc, out["k_write"].to(torch.bfloat16)[:, None]], dim=1)
-        vc = torch.cat([vc, out["v_write"].to(torch.bfloat16)[:, None]], dim=1)
+        k_row, v_row = (out["k_write"], out["v_write"]) if forced_rows is None else forced_rows[i]
+        kc = torch.cat([kc, k_row.to(torch.bfloat16)[:, None]], dim=1)
+        vc = torch.cat([vc, v_row.to(torch.bfloat16)[:, None]], dim=1)
         tok = toks[-1] if forced_tokens is None else int(forced_tokens[i])
     return {"tokens": torch.tensor(toks, dtype=torch.int64), "margins": torch.tensor(margins),
             "kcache": kc, "vcache": vc, "logits": out["logits"] if out else None}

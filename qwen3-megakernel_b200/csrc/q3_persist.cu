@@ -1,8 +1,8 @@
 // Persistent cooperative decode kernel: one launch runs a whole batch-1 decode step.
 //
 // One CTA of 16 warps per SM.  The schedule is static (every CTA owns fixed weight rows, all of them resident
-// in its 227 KB of shared memory for the layer at hand) and a layer has NO grid barrier: every exchange between
-// CTAs is a wait on the data itself.
+// in its 227 KB of shared memory for the layer at hand) and a layer has ONE grid barrier; the other two exchanges
+// between CTAs are waits on the data itself.
 //
 //   Q   x += dB (previous layer);  qkv rows = rms(x, ln1) . [wq;wk;wv] rows, published as tagged 64-bit words
 //       (tag << 32 | fp32 bits, one tag per launch and layer); the readers poll the tags
@@ -12,14 +12,16 @@
 //       heads and exchange (max, sum, output) partials as tagged words; Wo[slice rows, head columns] . o_h is
 //       added into dA                                                           (red.global.add.u64)
 //   GD  x += dA;  hid rows = silu(gate) * up for this CTA's FFN rows, kept in shared memory,
-//       then the matching rows of the transposed down matrix scatter hid into dB (red.global.add.u64)
+//       then the matching rows of the transposed down matrix scatter hid into dB (red.global.add.v4.f32) | barrier
 //
-// The residual stream x lives in registers, the same copy in every CTA (two elements per thread).  The deltas of a
-// phase are summed in "counted accumulators": one 64-bit word per element holding the number of contributions
-// in its top 8 bits and their sum as a 2^-36 fixed-point number below (red.global.add.u64 adds both at once).
-// A reader polls its own two words until the count is complete, which makes the wait and the load one L2 round
-// trip, needs no release fence on the writers' side, and makes the sum independent of the order of arrival:
-// every CTA derives bit-identical x, and a step's result is reproducible from run to run.
+// The residual stream x lives in registers, the same copy in every CTA (two elements per thread).  The attention
+// delta (16 contributions an element) is summed in "counted accumulators": one 64-bit word per element holding the
+// number of contributions in its top 8 bits and their sum as a 2^-32 fixed-point number below (red.global.add.u64
+// adds both at once).  A reader polls its own two words until the count is complete, which makes the wait and the
+// load one L2 round trip and needs no release fence on the writers' side.  The FFN delta has one contribution per
+// CTA and element: there 64-bit atomics are too slow (measured on B200: 36 G scalar 64-bit reds per second against
+// 600 G elements per second through red.v4.f32), so it stays on fp32 vector reds followed by a grid barrier:
+// an arrive (red.release) and a bounded wait (relaxed poll + acquire fence).
 //
 // Weights never wait for a barrier, and a barrier never waits behind weights.  Each CTA's rows of the seven
 // matrices of a layer are packed once (pack_weights_kernel) in the order and with the row padding of four
@@ -63,6 +65,10 @@ constexpr int WOROW = 136;                    // the same for the 128-column Wo 
 constexpr int ATT_WARPS = 8;                  // split attention: warps that attend positions (32 positions per pass)
 // Local attention (every CTA attends its whole head over all cached positions) serves up to 255 positions; measured,
 // splitting the positions over the 18 CTAs of a kv group wins beyond that.
+#ifndef Q3_N_ACC
+#define Q3_N_ACC 2
+#endif
+constexpr int N_ACC = Q3_N_ACC;               // accumulators for the FFN delta (fewer same-address atomics each)
 constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
 constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;   // default patience of every device-side wait: 200 ms
 constexpr int MAX_LAYERS = 63;                // the q/k/v tags of a launch are epoch * 64 + layer + 1
@@ -89,12 +95,12 @@ struct PersistParams {
     bf16_raw* k_write;
     bf16_raw* v_write;
     unsigned long long* dA;   // [2][1024] counted accumulators: attention delta of layer l in buffer l & 1 (16 contributions an element)
-    unsigned long long* dB;   // [2][1024] FFN delta of layer l in buffer l & 1 (one contribution per CTA and element)
+    float* dB;        // [3][N_ACC][1024] FFN delta of layer l in buffer l % 3 (fp32 accumulators, one contribution per CTA and element)
     unsigned long long* xq;   // [4096] q | k | v rows of the current layer, each a (tag << 32 | fp32 bits) word
     const unsigned* epoch;    // launches completed on this state; gives every (launch, layer) its own tag
     unsigned long long* xp;   // [8 groups][2 heads][18 CTAs][XP_STRIDE] split-attention partials (max, sum, -, -, o[128]), tagged like xq
     const float* rope;
-    unsigned* sync;   // [2] end-of-step ticket
+    unsigned* sync;   // [0] grid barrier counter, [2] end-of-step ticket
     unsigned long long wait_ns;   // patience of every device-side wait
     uint32_t* status;
     float* pval;
@@ -106,7 +112,7 @@ struct PersistParams {
 struct PersistState {
     bf16_raw* packed;       // the layer matrices re-laid per CTA (see pack_weights_kernel)
     const void* src[7];     // the seven pointers `packed` was built from
-    float* X;               // dA[2] | dB[2] (64-bit words) | xq[4096] (64-bit words) | epoch | xp
+    float* X;               // dA[2] (64-bit words) | dB[3][N_ACC] (fp32) | xq[4096] (64-bit words) | epoch | xp
     int grid, smem;
 };
 
@@ -114,7 +120,7 @@ struct PersistState {
 // one layer takes.  Used by the decode kernel and by the kernel that packs the weights.
 constexpr int XP_STRIDE = 132;                // 64-bit words per published partial
 constexpr size_t XP_WORDS = (size_t)KV_HEADS * 2 * GROUP_CTAS * XP_STRIDE;
-constexpr size_t ACC_FLOATS = (size_t)2 * 4 * HIDDEN;   // four vectors of 64-bit words
+constexpr size_t ACC_FLOATS = (size_t)(4 + 3 * N_ACC) * HIDDEN;   // two vectors of 64-bit words, 3 * N_ACC of floats
 constexpr size_t X_FLOATS = ACC_FLOATS + 2 * QKV_DIM + 64 + 2 * XP_WORDS;
 struct Share {
     int q0, nq, qmax;       // rows [q0, q0 + nq) of [wq; wk; wv], slot rows qmax
@@ -159,6 +165,10 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
 // ---- counted accumulators ----------------------------------------------------------------------------
 __device__ __forceinline__ void acc_add(unsigned long long* addr, float v) {
     v = fminf(fmaxf(v, -ACC_CLAMP), ACC_CLAMP);
@@ -173,6 +183,34 @@ __device__ __forceinline__ float acc_value(unsigned long long w) {
 // barrier of the whole CTA (512 threads)
 __device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
+// ---- counters in global memory: arrive and bounded wait ---------------------------------------------
+__device__ __forceinline__ void counter_arrive(unsigned* cnt) {   // one thread, after a cta_sync
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+}
+// thread 0 polls until *cnt has reached `target` (wrap-safe), then every thread passes a cta_sync
+__device__ __forceinline__ void counter_wait(const unsigned* cnt, unsigned target, volatile int* abort_flag,
+                                             uint32_t* status, uint32_t site, unsigned long long wait_ns) {
+    if (threadIdx.x == 0 && !*abort_flag) {
+        unsigned v;
+        unsigned long long t0 = 0;
+        unsigned it = 0;
+        for (;;) {
+            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+            if ((int)(v - target) >= 0) break;
+            if ((++it & 255u) == 0) {
+                const unsigned long long t = global_ns();
+                if (t0 == 0) t0 = t;
+                else if (t - t0 > wait_ns) {
+                    report(status, ST_BARRIER_TIMEOUT, site, v);
+                    *abort_flag = 1;
+                    break;
+                }
+            }
+        }
+        asm volatile("fence.acquire.gpu;" ::: "memory");
+    }
+    cta_sync();
+}
 // bounded wait on a shared-memory mbarrier; returns false when it gave up
 __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag, uint32_t* status, uint32_t site,
                                           unsigned long long wait_ns) {
@@ -429,9 +467,28 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         const uint32_t e = *reinterpret_cast<const uint32_t*>(p.embed + (size_t)tok * HIDDEN + 2 * tid);
         x0 = bf_lo(e); x1 = bf_hi(e);
     }
-    // x += a delta, once all `expect` contributions to this thread's two words have arrived (bounded).  The wait IS the
-    // load: no counter, no fence; a word that is complete cannot change any more until the buffer is cleared.
+    // x += the attention delta, once all 16 contributions to this thread's two words have arrived (bounded).  The wait IS
+    // the load: no counter, no fence; a word that is complete cannot change any more until the buffer is cleared.
+    // Thread 0 first polls one sentinel word until it is nearly complete, so that the grid does not hammer lines that
+    // are still being added to (measured: 0.5 us faster per wait than every thread polling from the start).
     auto acc_wait = [&](const unsigned long long* vec, unsigned expect, uint32_t site) {
+#ifndef Q3_X_NO_SENTINEL
+        if (tid == 0 && !*abort_flag) {
+            unsigned long long ws;
+            unsigned it = 0;
+            unsigned long long t0 = 0;
+            for (;;) {
+                asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(ws) : "l"(vec + HIDDEN - 1) : "memory");
+                if (acc_count(ws) + 2u >= expect) break;
+                if ((++it & 63u) == 0) {
+                    const unsigned long long t = global_ns();
+                    if (t0 == 0) t0 = t;
+                    else if (t - t0 > wait_ns) { report(p.status, ST_BARRIER_TIMEOUT, site, acc_count(ws)); *abort_flag = 1; break; }
+                }
+            }
+        }
+#endif
+        cta_sync();
         unsigned long long w0 = 0, w1 = 0;
         if (!*abort_flag) {
             const unsigned long long* src = vec + 2 * tid;
@@ -451,9 +508,22 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     }
                 }
             }
+            if (*abort_flag) { w0 = 0; w1 = 0; }
         }
         x0 += acc_value(w0); x1 += acc_value(w1);
     };
+    // x += the FFN delta: the sum of its fp32 accumulators (after the layer's grid barrier)
+    auto add_ffn_delta = [&](const float* dBl) {
+        float2 d[N_ACC];
+#pragma unroll
+        for (int i = 0; i < N_ACC; ++i) d[i] = ldcg2(dBl + (size_t)i * HIDDEN + 2 * tid);
+        float s0 = d[0].x, s1 = d[0].y;
+#pragma unroll
+        for (int i = 1; i < N_ACC; ++i) { s0 += d[i].x; s1 += d[i].y; }
+        x0 += s0; x1 += s1;
+    };
+    unsigned* bar = p.sync;
+    unsigned target = 0;
     // Every (launch, layer) tags its q/k/v words differently, so a reader can tell a fresh word from an old one.
     const unsigned tag_base = __ldcg(p.epoch) * 64u;
     const int quarter = lane >> 3, sub = lane & 7;
@@ -477,13 +547,13 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 
     for (int l = 0; l < L; ++l) {
         const int ev = 1 + EV_PER_LAYER * l;
-        // The two deltas alternate between two buffers.  CTA 1 clears, during the F phase of layer l, the attention
-        // buffer of layer l - 1 and the FFN buffer of layer l - 2: it has seen the FFN delta of layer l - 1 complete, so
-        // every CTA has finished GD of layer l - 1 and with it every read of those two.  The clearing warps fence before
-        // the CTA's own contributions to the attention delta of layer l go out, and nobody writes either buffer again
-        // before having seen that delta (the FFN buffer) or the next FFN delta (the attention buffer) complete.
+        // The attention delta alternates between two buffers, the FFN delta goes round three.  The last CTA clears, at the
+        // start of GD of layer l, the attention buffer of layer l - 1 (next written in F of layer l + 1) and the FFN buffer
+        // of layer l - 2 (next written in GD of layer l + 1): it has passed the grid barrier of layer l - 1, which every CTA
+        // reaches after its last read of both, and its arrival at the barrier of layer l releases the stores to every
+        // later writer.
         unsigned long long* dAl = p.dA + (size_t)(l & 1) * HIDDEN;
-        unsigned long long* dBl = p.dB + (size_t)(l & 1) * HIDDEN;
+        float* dBl = p.dB + (size_t)(l % 3) * N_ACC * HIDDEN;
         const unsigned tag = tag_base + (unsigned)l + 1u;
         // K and V rows of the cached positions, fetched at the very start of the layer (they depend on nothing of this
         // step), so that they have arrived, and the SM's input path is quiet, when the q/k/v exchange starts polling.
@@ -542,8 +612,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         };
         // ==================================================================== Q
         {
-            if (l > 0) acc_wait(p.dB + (size_t)((l - 1) & 1) * HIDDEN, (unsigned)G, 300 + l - 1);
-            if (l > 0) Q3_TRACE(ev - 1);   // the previous layer's slot 11: FFN delta complete
+            if (l > 0) add_ffn_delta(p.dB + (size_t)((l - 1) % 3) * N_ACC * HIDDEN);
             fetch_slot(3, l);   // down rows of this layer: landed before the q/k/v exchange starts polling
             {   // stage x * gain split in three bf16 parts (the 1/rms factor is applied to the row sums)
                 bf16_raw h0, m0, l0, h1, m1, l1;
@@ -684,11 +753,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         *reinterpret_cast<uint2*>(cb + (size_t)l * lstride + (size_t)len * KV_DIM + fg * HEAD_DIM + lane * 4) = pk;
                     }
                 }
-            }
-            if (c == 1 && (warp == 13 || warp == 14)) {   // idle warps of CTA 1: recycle the delta buffers (see the top of the loop)
-                unsigned long long* buf = (warp == 13) ? p.dA + (size_t)((l + 1) & 1) * HIDDEN : dBl;
-                for (int i = lane; i < HIDDEN / 2; i += 32) __stcg(reinterpret_cast<ulonglong2*>(buf) + i, make_ulonglong2(0ull, 0ull));
-                __threadfence();
             }
             cta_sync();
             Q3_TRACE(ev + 3);
@@ -978,8 +1042,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             }
             cta_sync();
             if (tid < fn) acc_add(dAl + fr0 + tid, wo_part[tid] + wo_part[128 + tid]);   // fn <= 116: the slice joins the attention delta
-            cta_sync();   // wo_part is the next phase's staging area
-        }
+        }   // (wo_part is the next phase's staging area: the wait below passes a CTA barrier before anything is staged)
         Q3_TRACE(ev + 6);
         gain2 = *reinterpret_cast<const uint32_t*>(p.ln2 + (size_t)l * HIDDEN + 2 * tid);
 
@@ -987,8 +1050,15 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         {
             acc_wait(dAl, (unsigned)Q_HEADS, 200 + l);   // every row of the attention delta receives one slice per query head
             Q3_TRACE(ev + 7);
-            fetch_slot(0, l + 1);   // q/k/v rows and Wo slice of the next layer: landed before the next exchange is polled
+#ifndef Q3_X_LATE_FETCH
+            fetch_slot(0, l + 1);   // q/k/v rows and Wo slice of the next layer: landed before this phase's barrier is polled
             fetch_slot(1, l + 1);
+#endif
+            if (c == G - 1) {   // recycle the delta buffers (see the top of the loop): 8 KB each, 16 bytes a thread
+                static_assert(N_ACC == 2, "both buffers are cleared as 8 KB");
+                __stcg(reinterpret_cast<float4*>(p.dA + (size_t)((l + 1) & 1) * HIDDEN) + tid, make_float4(0.f, 0.f, 0.f, 0.f));
+                __stcg(reinterpret_cast<float4*>(p.dB + (size_t)((l + 1) % 3) * N_ACC * HIDDEN) + tid, make_float4(0.f, 0.f, 0.f, 0.f));
+            }
             {
                 bf16_raw h0, m0, l0, h1, m1, l1;
                 split3(x0 * bf_lo(gain2), h0, m0, l0);
@@ -1058,6 +1128,10 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 }
             }
             cta_sync();   // hid ready; the activations and the gate/up slot are no longer needed
+#ifdef Q3_X_LATE_FETCH
+            fetch_slot(0, l + 1);
+            fetch_slot(1, l + 1);
+#endif
             Q3_TRACE(ev + 9);
 
             slot_wait(&full[3], l & 1, abort_flag, p.status, 13, wait_ns);
@@ -1098,22 +1172,24 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 }
             }
             cta_sync();
-            {
-                const float2 t = *reinterpret_cast<const float2*>(dout + 2 * tid);
-                acc_add(dBl + 2 * tid, t.x);
-                acc_add(dBl + 2 * tid + 1, t.y);
+            if (tid < 256) {
+                const float4 t = *reinterpret_cast<const float4*>(dout + tid * 4);
+                red_add_v4(dBl + (size_t)(c & (N_ACC - 1)) * HIDDEN + tid * 4, t.x, t.y, t.z, t.w);
             }
-            cta_sync();   // dout is the next phase's staging area
+            cta_sync();
             Q3_TRACE(ev + 10);
+            if (tid == 0) counter_arrive(bar);
         }
+        target += G;
         gain2 = (l + 1 < L) ? *reinterpret_cast<const uint32_t*>(p.ln1 + (size_t)(l + 1) * HIDDEN + 2 * tid)
                             : *reinterpret_cast<const uint32_t*>(p.fnorm + 2 * tid);
+        counter_wait(bar, target, abort_flag, p.status, 300 + l, wait_ns);
+        Q3_TRACE(ev + 11);
     }
 
     // ======================================================================== LM head + argmax
     {
-        acc_wait(p.dB + (size_t)((L - 1) & 1) * HIDDEN, (unsigned)G, 300 + L - 1);
-        Q3_TRACE(EV_PER_LAYER * L);   // the last layer's slot 11
+        add_ffn_delta(p.dB + (size_t)((L - 1) % 3) * N_ACC * HIDDEN);
         const float ss = warp_sum(x0 * x0 + x1 * x1);
         if (lane == 0) red[warp] = ss;
         cta_sync();
@@ -1169,11 +1245,13 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     if (bv_s[w] > bv || (bv_s[w] == bv && bi_s[w] < bi)) { bv = bv_s[w]; bi = bi_s[w]; }
                 p.next_token[0] = bi;
                 if (p.append) p.seq_len[0] = len + 1;
+                // every CTA has passed every barrier: rearm the counters for the next launch
+                p.sync[0] = 0;
                 p.sync[2] = 0;
                 *const_cast<unsigned*>(p.epoch) = tag_base / 64u + 1u;
             }
-            // every CTA has read its last delta: the next launch starts from clean accumulators
-            for (int i = tid; i < 4 * HIDDEN / 2; i += CT) __stcg(reinterpret_cast<ulonglong2*>(p.dA) + i, make_ulonglong2(0ull, 0ull));
+            // every CTA has read its last delta: the next launch starts from clean accumulators (dA and dB are adjacent)
+            for (int i = tid; i < (int)(ACC_FLOATS / 4); i += CT) __stcg(reinterpret_cast<float4*>(p.dA) + i, make_float4(0.f, 0.f, 0.f, 0.f));
         }
         Q3_TRACE(2 + EV_PER_LAYER * L);
     }
@@ -1363,7 +1441,7 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
     p.seq_k = a->seq_k; p.seq_v = a->seq_v; p.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
     p.seq_len = a->seq_len; p.logits = a->logits; p.next_token = reinterpret_cast<long long*>(a->next_token);
     p.k_write = reinterpret_cast<bf16_raw*>(a->k_write); p.v_write = reinterpret_cast<bf16_raw*>(a->v_write);
-    p.dA = reinterpret_cast<unsigned long long*>(s->X); p.dB = p.dA + 2 * HIDDEN;
+    p.dA = reinterpret_cast<unsigned long long*>(s->X); p.dB = s->X + 4 * HIDDEN;
     p.xq = reinterpret_cast<unsigned long long*>(s->X + ACC_FLOATS);
     p.epoch = reinterpret_cast<const unsigned*>(s->X + ACC_FLOATS + 2 * QKV_DIM);
     p.xp = reinterpret_cast<unsigned long long*>(s->X + ACC_FLOATS + 2 * QKV_DIM + 64);

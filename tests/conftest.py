@@ -55,25 +55,34 @@ def synth_full(oracle):
 # ---- helpers of the greedy-decode parity tests ---------------------------------------------------------
 
 def run_chained(mk, steps):
-    """`steps` chained launches on the bound inputs; returns the tokens and a copy of every step's logits."""
-    toks, logits = [], []
+    """`steps` chained launches on the bound inputs; returns the tokens [steps(, batch)] and a copy of every step's
+    logits and K/V rows."""
+    toks, outs = [], []
     out = mk._out
     for _ in range(steps):
         mk.launch()
         toks.append(mk.chain_token.clone())
-        logits.append(out[0].clone())
+        outs.append(tuple(t.clone() for t in (out[0], out[2], out[3])))
     mk.status()
-    return torch.stack(toks).cpu(), logits
+    return torch.stack(toks).cpu(), outs
 
 
-def gate_teacher_forced(oracle, w32, token, kc, vc, got_tokens, got_logits, what):
-    """Replay the GPU's token stream through the oracle and gate every step.  Returns the number of excused flips."""
+def gate_teacher_forced(oracle, w32, token, kc, vc, got_tokens, got_outs, what, seq=None):
+    """Replay the GPU's stream through the oracle and gate every step as a single step on identical inputs: the oracle is
+    fed the GPU's token AND appends the GPU's (bf16) K/V rows, so both sides see the same cache at every step.  Gates per
+    step: logits rel-L2 <= 1e-4, K/V rows <= 2 bf16 ulps, token equal unless the oracle's top-2 margin is below twice the
+    largest logit error of that step (printed).  `seq` picks one sequence of a batched run.  Returns the excused flips."""
     flips = []
+    pick = (lambda t: t) if seq is None else (lambda t: t[seq])
+    rows = [(pick(o[1]).cpu(), pick(o[2]).cpu()) for o in got_outs]
 
     def on_step(i, out):
-        g = got_logits[i].cpu()
+        g = pick(got_outs[i][0]).cpu()
         e = oracle.rel_l2(g, out["logits"])
         assert e <= 1e-4, f"{what}: step {i}: logits rel-L2 {e:.3e}"
+        for n, r in (("k_write", rows[i][0]), ("v_write", rows[i][1])):
+            u = oracle.bf16_ulps(r, out[n])
+            assert u <= 2, f"{what}: step {i}: {n} {u:.1f} bf16 ulps"
         want, got = int(out["next_token"]), int(got_tokens[i])
         if got != want:
             err = float((g - out["logits"]).abs().max())
@@ -82,7 +91,7 @@ def gate_teacher_forced(oracle, w32, token, kc, vc, got_tokens, got_logits, what
             assert margin <= 2 * err + 1e-7, f"{what}: step {i}: token {got}, oracle {want}, top-2 margin {margin:.3e}, max logit error {err:.3e}"
             flips.append((i, got, want, margin, err))
 
-    oracle.greedy_decode(w32, token, kc, vc, len(got_tokens), forced_tokens=got_tokens.tolist(), on_step=on_step)
+    oracle.greedy_decode(w32, token, kc, vc, len(got_tokens), forced_tokens=[int(t) for t in got_tokens], on_step=on_step, forced_rows=rows)
     for i, got, want, margin, err in flips:
         print(f"{what}: step {i}: token {got} instead of {want} excused: top-2 margin {margin:.3e} <= 2 x logit error {err:.3e}")
     return len(flips)
