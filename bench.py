@@ -14,13 +14,20 @@ One JSON line is printed by rank 0.  `value` is the device-timed figure with eve
 HBM; `e2e` is the same stream driven from host memory (token in from pinned memory, token out to the
 host, one synchronisation per step).  `--impl reference` times the CPU restatement of the reference's
 fp32 decode step (oracle/) on the host cores for the same workload, a bounded number of steps.
+
+Extra records in the line: `reference_kernel` (the reference project's own CUDA kernel timed on this GPU through its
+own launcher and timing code, from baseline/_ref, in a child process; `unavailable` with the reason otherwise),
+`batch64_ctx1024` (the replicated batched-decode configuration: 64 sequences of 1024 cached positions per GPU) and
+`static_ctx128` (position 128 held fixed, the case the reference's published figure is quoted on).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import statistics
+import subprocess
 import sys
 import threading
 import time
@@ -34,7 +41,7 @@ for p in (str(ROOT), str(ROOT / "qwen3-megakernel_b200")):
 import torch  # noqa: E402
 
 CTX0 = 128
-NCU_TRAFFIC_BYTES_CTX128 = 1_231_634_000 + 3_821_568   # dram__bytes_read + dram__bytes_write of one launch at cache length 128, from one ncu capture of that launch
+TRAFFIC_PROFILE = ROOT / "profiles" / "persist_decode_bs1_ctx128.md"   # the ncu summary that holds the kernel's DRAM traffic per launch
 PUBLISHED_US = 373.6        # the reference kernel's steady microseconds per step on one B200 (its README)
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
@@ -49,6 +56,35 @@ def algorithmic_bytes(ctx: int, layers: int = 28, vocab: int = 151936) -> int:
     kv_read = layers * ctx * 8 * 128 * 2 * 2
     per_seq = 1024 * 2 + vocab * 4 + layers * 8 * 128 * 2 * 2
     return weights + gains + kv_read + per_seq
+
+
+def ncu_traffic() -> dict | None:
+    """DRAM bytes per launch of the persistent kernel at cache length 128, read from the committed ncu summary (a line
+    `traffic_bytes_per_launch: <bytes> (commit <hash>)`), with the commit the capture was made on."""
+    try:
+        m = re.search(r"traffic_bytes_per_launch:\s*(\d+)\s*\(commit\s+(\w+)\)", TRAFFIC_PROFILE.read_text())
+        return {"bytes": int(m.group(1)), "commit": m.group(2)} if m else None
+    except OSError:
+        return None
+
+
+def reference_kernel_record(timeout_s: int = 240) -> dict:
+    """The reference project's own kernel on this GPU (baseline/time_ref_kernel.py, a child process that imports nothing
+    of this repository's engine).  Never raises: a failure is reported as {"unavailable": reason}."""
+    script = ROOT / "baseline" / "time_ref_kernel.py"
+    if not (ROOT / "baseline" / "_ref" / "qwen3mk" / "kernel.py").exists():
+        return {"unavailable": "baseline/_ref is not installed (python baseline/install_ref.py)"}
+    env = dict(os.environ)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "OMP_NUM_THREADS"):
+        env.pop(k, None)
+    try:
+        r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=timeout_s, env=env)
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        return json.loads(lines[-1]) if lines else {"unavailable": f"no output (exit {r.returncode}): {r.stderr.strip()[-200:]}"}
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"no answer within {timeout_s} s"}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"}
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -123,16 +159,21 @@ def build_workload(device, seed: int = 0):
     return inputs, ids
 
 
+def cpu_workload(O, seed: int = 0):
+    """The GPU arm's workload rebuilt on the host: the same seeded weights, the cache of the same 128 seeded ids (through the
+    oracle's fp32 prefill, rounded to bf16) and the prompt's greedy token."""
+    w32 = O.to_fp32(O.baseline_init(seed))
+    g = torch.Generator().manual_seed(seed + 1)
+    ids = torch.randint(0, 151936, (CTX0,), generator=g)
+    kc, vc, last = O.prefill(w32, ids.tolist())
+    return w32, int(last.argmax()), kc, vc
+
+
 def cpu_baseline(seconds: float = 12.0, seed: int = 0) -> dict:
     """The oracle's decode step on the host cores: same weights and cache length, a bounded number of steps."""
     from oracle import qwen3_oracle as O
 
-    w = O.baseline_init(seed)
-    w32 = O.to_fp32(w)
-    g = torch.Generator().manual_seed(seed + 1)
-    kc = (torch.randn(28, CTX0, 8, 128, generator=g) * 0.1).to(torch.bfloat16)
-    vc = (torch.randn(28, CTX0, 8, 128, generator=g) * 0.1).to(torch.bfloat16)
-    tok = 1234
+    w32, tok, kc, vc = cpu_workload(O, seed)
     O.decode_step(w32, tok, kc, vc)  # warm-up
     times = []
     t_end = time.perf_counter() + seconds
@@ -150,13 +191,11 @@ def run_reference_arm(args, rank: int, world: int) -> None:
     if rank != 0:
         return
     steps = max(1, min(args.steps, 64))
+    # every host core: a launcher such as torchrun sets OMP_NUM_THREADS=1 for its ranks, which would slow this arm fivefold
+    torch.set_num_threads(os.cpu_count() or 1)
     from oracle import qwen3_oracle as O
 
-    w32 = O.to_fp32(O.baseline_init(0))
-    g = torch.Generator().manual_seed(1)
-    kc = (torch.randn(28, CTX0, 8, 128, generator=g) * 0.1).to(torch.bfloat16)
-    vc = (torch.randn(28, CTX0, 8, 128, generator=g) * 0.1).to(torch.bfloat16)
-    tok = 1234
+    w32, tok, kc, vc = cpu_workload(O, 0)
     for _ in range(max(1, min(args.warmup, 3))):
         O.decode_step(w32, tok, kc, vc)
     t0 = time.perf_counter()
@@ -170,7 +209,7 @@ def run_reference_arm(args, rank: int, world: int) -> None:
             "config": {"workload": f"Qwen3-0.6B bs1 greedy decode, {args.steps} consecutive steps from position {CTX0} "
                                    f"(cache {CTX0 + 1}->{CTX0 + args.steps} positions)",
                        "sample": f"the first {steps} of those steps on the host cores (fp32 restatement of the reference's CPU path)",
-                       "weights": "bf16 N(0,0.02), RMSNorm gains 1, seed 0"},
+                       "weights": "bf16 N(0,0.02), RMSNorm gains 1, seed 0", "cache": "prefill of 128 uniform-random ids (fp32 on the host)"},
             "cpu_baseline": {"value": us, "unit": "us/step", "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(),
                              "kind": "port", "sample": f"{steps} greedy steps from position {CTX0}"},
             "e2e": {"value": us, "unit": "us/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -186,6 +225,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--path", choices=["auto", "layered", "persist"], default="auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-extras", action="store_true", help="leave out the batch64_ctx1024 and reference_kernel records (profiling runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -263,11 +303,21 @@ def main() -> int:
     static_us = bench_mod.steady(mk, inputs, steps=50, reps=5, warmup=50)["us_per_step_median"]
     mk.status()
 
+    # ---- the replicated batched configuration: 64 sequences of 1024 cached positions on every GPU ----------------
+    b64 = None
+    if not args.skip_extras:
+        barrier()
+        weights_only = {k: inputs[k] for k in inputs if k not in ("token", "kcache", "vcache")}
+        b64 = bench_mod.batched(dev, weights_only, 64, 1024, steps=20)
+        b64_us = replicas.max_over_ranks(b64["us_per_step"], dev)
+        barrier()
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return 0
 
+    traffic = ncu_traffic()
     mean_ctx = CTX0 + (K - 1) / 2.0
     bytes_step = algorithmic_bytes(int(round(mean_ctx)))
     peak, peak_kind = measured_peak_gbs()
@@ -289,7 +339,9 @@ def main() -> int:
         "tokens_per_s": world * 1e6 / us_step,
         "hbm_frac_of_8tbs": bytes_step / (us_step * 1e-6) / 1e9 / NOMINAL_HBM_GBS,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_BYTES_CTX128,
+                     "peak_kind": f"of {peak_kind}", "traffic": traffic["bytes"] if traffic else None,
+                     "traffic_source": (f"ncu capture of one launch at cache length 128 on commit {traffic['commit']} "
+                                        f"({TRAFFIC_PROFILE.name})") if traffic else None,
                      "algorithmic_bytes_per_step": bytes_step,
                      "kernel": "q3_persist_decode (one launch per step)" if launches_per_step <= 1.5 else
                                f"whole step ({launches_per_step:.0f} launches)"},
@@ -299,6 +351,16 @@ def main() -> int:
         "static_ctx128": {"us_per_step": static_us, "vs_published": static_us / PUBLISHED_US,
                           "note": "position 128 held fixed: the case the reference's 373.6 us is quoted on"},
     }
+    if b64 is not None:
+        line["batch64_ctx1024"] = {"us_per_step_slowest": b64_us, "tokens_per_s_job": world * 64 * 1e6 / b64_us,
+                                   "tokens_per_s_per_gpu": 64 * 1e6 / b64_us, "kernels_per_step": b64["kernels_per_step"],
+                                   "hbm_gbs": b64["algorithmic_bytes"] / (b64_us * 1e-6) / 1e9,
+                                   "hbm_frac": b64["algorithmic_bytes"] / (b64_us * 1e-6) / 1e9 / peak,
+                                   "note": "one replica per GPU, 64 sequences x 1024 cached positions each, no inter-GPU traffic"}
+        ref_k = reference_kernel_record()
+        if "steady_us" in ref_k:
+            ref_k["ours_static_over_reference_steady"] = static_us / ref_k["steady_us"]
+        line["reference_kernel"] = ref_k
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line))

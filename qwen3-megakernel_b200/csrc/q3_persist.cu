@@ -47,7 +47,7 @@ constexpr int PT = CT;                        // threads per CTA
 #endif
 constexpr int LM_KEEP_PCT = Q3_LM_KEEP_PCT;   // share of the LM head asked to stay in L2 from one step to the next (15 % = 47 MB; measured: 0 % 354 us, 15 % 350, 28 % 351, 40 % 358)
 #ifndef Q3_PUMP_CHUNK
-#define Q3_PUMP_CHUNK 32768
+#define Q3_PUMP_CHUNK 131072
 #endif
 constexpr int PUMP_CHUNK = Q3_PUMP_CHUNK;     // largest single bulk copy of the weight stream (a multiple of 16)
 constexpr int WO_SLICES = 9;                  // row slices of Wo; CTA c < 144 owns head c % 16, slice c / 16
@@ -304,6 +304,8 @@ __device__ __forceinline__ uint2 ld_stream8(const void* ptr) {
     return v;
 }
 constexpr int LOCAL_V_PRE = 8;   // V positions per warp fetched ahead of the barrier wait
+// Local attention: the i-th position whose V row warp w weighs.
+__device__ __forceinline__ int local_v_pos(int w, int i) { return w + CW * i; }
 
 // ====================================================================================================
 // MODE picks the attention scheme at compile time, so that each variant carries only its own code and registers:
@@ -472,7 +474,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     // Thread 0 first polls one sentinel word until it is nearly complete, so that the grid does not hammer lines that
     // are still being added to (measured: 0.5 us faster per wait than every thread polling from the start).
     auto acc_wait = [&](const unsigned long long* vec, unsigned expect, uint32_t site) {
-#ifndef Q3_X_NO_SENTINEL
         if (tid == 0 && !*abort_flag) {
             unsigned long long ws;
             unsigned it = 0;
@@ -487,7 +488,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 }
             }
         }
-#endif
         cta_sync();
         unsigned long long w0 = 0, w1 = 0;
         if (!*abort_flag) {
@@ -545,6 +545,9 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     // gains of the next GEMV phase, fetched ahead of the barrier wait
     uint32_t gain2 = *reinterpret_cast<const uint32_t*>(p.ln1 + 2 * tid);
 
+    uint4 ring[4][2];
+    uint4 ring3[XPASS > 0 ? XPASS : 1][2];    // passes 2..: K row of position 64 pass + slot
+    uint4 vext[XPASS > 0 ? 2 * XPASS : 1];    // ... and V[warp + 16 i][4 lane ..] for i = 8 .., two rows per uint4
     for (int l = 0; l < L; ++l) {
         const int ev = 1 + EV_PER_LAYER * l;
         // The attention delta alternates between two buffers, the FFN delta goes round three.  The last CTA clears, at the
@@ -560,13 +563,12 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         // Split attention: [0], [1] = K passes, [2], [3] = V passes of the CTA's positions.  Local attention:
         // [0], [1] = K passes 0, 1 (a quarter-warp per position) and [2], [3] = V[warp + 16 i][4 lane .. 4 lane + 3]
         // for i < 8, two positions per uint4.
-        uint4 ring[4][2];
-        uint4 ring3[XPASS > 0 ? XPASS : 1][2];    // passes 2..: K row of position 64 pass + slot
-        uint4 vext[XPASS > 0 ? 2 * XPASS : 1];    // ... and V[warp + 16 i][4 lane ..] for i = 8 .., two rows per uint4
         const bf16_raw* kl = kcache + (size_t)l * lstride + fg * HEAD_DIM;
         const bf16_raw* vl = vcache + (size_t)l * lstride + fg * HEAD_DIM;
-        auto kv_prefetch = [&]() {
-            if (has_f) {
+        auto kv_prefetch = [&](int ll) {
+            const bf16_raw* kl = kcache + (size_t)ll * lstride + fg * HEAD_DIM;
+            const bf16_raw* vl = vcache + (size_t)ll * lstride + fg * HEAD_DIM;
+            if (has_f && ll < L) {
                 if (local_attn) {
 #pragma unroll
                     for (int i = 0; i < 2; ++i) ring_load(ring[i], i, npl, len, att_slot, sub, kl);
@@ -575,7 +577,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                         for (int x = 0; x < XPASS; ++x) ring_load(ring3[x], 2 + x, npl, len, att_slot, sub, kl);
 #pragma unroll
                         for (int i = 0; i < 4 * XPASS; ++i) {
-                            const int pos = warp + CW * (LOCAL_V_PRE + i);
+                            const int pos = local_v_pos(warp, LOCAL_V_PRE + i);
                             const bool live = pos < len;
                             const bf16_raw* vp = vl + (size_t)(live ? pos : 0) * KV_DIM + lane * 4;
                             uint4& dst = vext[i >> 1];
@@ -584,7 +586,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                     }
 #pragma unroll
                     for (int i = 0; i < LOCAL_V_PRE; ++i) {
-                        const int pos = warp + CW * i;
+                        const int pos = local_v_pos(warp, i);
                         const bool live = pos < len;
                         const bf16_raw* vp = vl + (size_t)(live ? pos : 0) * KV_DIM + lane * 4;
                         uint4& dst = ring[2 + (i >> 2)][(i >> 1) & 1];
@@ -626,7 +628,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             if (lane == 0) red[warp] = ss;
             // the warps that will poll the q/k/v exchange request their K/V rows now (x is staged: nothing queues behind
             // these loads), the others while they wait for the exchange
-            if (warp >= 8 && warp < 12) kv_prefetch();
+            if (warp >= 8 && warp < 12) kv_prefetch(l);
             cta_sync();
             Q3_TRACE(ev + 0);
             // warp w: k range [64 w, 64 w + 64) of both 16-row tiles of this CTA's rows
@@ -679,7 +681,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 }
                 Q3_TRACE(ev + 1);
             }
-            if (warp < 8 || warp >= 12) kv_prefetch();   // after the rows are published: nothing waits for these warps now
+            if (warp < 8 || warp >= 12) kv_prefetch(l);   // after the rows are published: nothing waits for these warps now
         }
 
         // ---- what the F phase needs that no other CTA produces: norm gains and the RoPE row ----
@@ -1050,10 +1052,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         {
             acc_wait(dAl, (unsigned)Q_HEADS, 200 + l);   // every row of the attention delta receives one slice per query head
             Q3_TRACE(ev + 7);
-#ifndef Q3_X_LATE_FETCH
             fetch_slot(0, l + 1);   // q/k/v rows and Wo slice of the next layer: landed before this phase's barrier is polled
             fetch_slot(1, l + 1);
-#endif
             if (c == G - 1) {   // recycle the delta buffers (see the top of the loop): 8 KB each, 16 bytes a thread
                 static_assert(N_ACC == 2, "both buffers are cleared as 8 KB");
                 __stcg(reinterpret_cast<float4*>(p.dA + (size_t)((l + 1) & 1) * HIDDEN) + tid, make_float4(0.f, 0.f, 0.f, 0.f));
@@ -1128,10 +1128,6 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 }
             }
             cta_sync();   // hid ready; the activations and the gate/up slot are no longer needed
-#ifdef Q3_X_LATE_FETCH
-            fetch_slot(0, l + 1);
-            fetch_slot(1, l + 1);
-#endif
             Q3_TRACE(ev + 9);
 
             slot_wait(&full[3], l & 1, abort_flag, p.status, 13, wait_ns);

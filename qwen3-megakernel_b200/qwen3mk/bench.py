@@ -1,6 +1,8 @@
 """Timing of the decode engine: isolated launches and a steady chain.
 
-Same surface and result keys as the reference's module (qwen3mk/bench.py:22-89).
+`isolated`, `steady` and `gpu_info` restate the reference's functions of the same names (qwen3mk/bench.py:22-89): the
+signatures, the result keys and the two-clock method are the contract a caller of that module relies on, so they follow
+it step for step.  `grow` and `batched` are additions.
 isolated: one launch on an idle GPU between two synchronisations, timed by CUDA events and by the host clock.
 steady:   back-to-back chained launches (each launch's argmax is the next launch's token, no host sync);
           the value is the event time of a chain divided by its length.  `grow=True` lets the cache
@@ -94,3 +96,39 @@ def gpu_info(device) -> dict:
         except Exception:
             pass
     return info
+
+
+def batched(device, w: dict, batch: int = 64, context: int = 1024, steps: int = 20, warmup: int = 3, seed: int = 0,
+            lens: list[int] | None = None, graph: bool = True) -> dict:
+    """Microseconds per decode step of `batch` sequences with `context` cached positions each (or the given `lens`):
+    seeded random caches and tokens, one engine on `device`, CUDA-event time of `steps` back-to-back launches.
+    Also returns the kernels launched per step and the algorithmic HBM bytes of a step (every weight once, the norm
+    gains, and per sequence its K/V rows, embedding row, logits and new K/V rows)."""
+    from .kernel import HEAD_DIM, KV_HEADS, SeqTable
+
+    dev = torch.device(device)
+    layers, vocab = w["wq"].shape[0], w["embed"].shape[0]
+    lens = [context] * batch if lens is None else [int(n) for n in lens]
+    g = torch.Generator(device=dev).manual_seed(seed)
+    cache = lambda n: (torch.randn(layers, n, KV_HEADS, HEAD_DIM, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+    kcs, vcs = [cache(n) for n in lens], [cache(n) for n in lens]
+    mk = Megakernel(dev, max_batch=batch, layers=layers, vocab=vocab, max_positions=max(8192, max(lens) + 8))
+    toks = torch.randint(0, vocab, (batch,), device=dev, generator=g)
+    mk.bind_sequences(w, toks, SeqTable(kcs, vcs), graph=graph)
+    for _ in range(warmup):
+        mk.launch()
+    torch.cuda.synchronize(dev)
+    n0 = mk.launch_count
+    t0, t1 = _events()
+    t0.record()
+    for _ in range(steps):
+        mk.launch()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    mk.status()
+    us = t0.elapsed_time(t1) * 1e3 / steps
+    per_layer_w = (2048 * 1024 + 2 * 1024 * 1024 + 1024 * 2048 + 2 * 3072 * 1024 + 1024 * 3072) * 2
+    nbytes = layers * per_layer_w + vocab * 1024 * 2 + layers * (1024 * 2 + 128 * 2) * 2 + 1024 * 2
+    nbytes += sum(layers * n * 8 * 128 * 2 * 2 + 1024 * 2 + vocab * 4 + layers * 8 * 128 * 2 * 2 for n in lens)
+    return {"us_per_step": us, "tokens_per_s": batch * 1e6 / us, "kernels_per_step": (mk.launch_count - n0) / steps,
+            "algorithmic_bytes": nbytes, "batch": batch, "lens_min": min(lens), "lens_max": max(lens), "lens_mean": sum(lens) / batch}

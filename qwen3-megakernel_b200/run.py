@@ -164,31 +164,13 @@ def cmd_batch(args) -> int:
         dist.init_process_group("nccl", device_id=dev)
     B, ctx = args.batch, args.context
     w = weights.baseline_init(args.seed, dev)
-    g = torch.Generator(device=dev).manual_seed(args.seed)
+    lens = None
     if args.ragged:   # cache lengths uniform in [128, context], seeded
         lens = torch.randint(128, ctx + 1, (B,), generator=torch.Generator().manual_seed(args.seed)).tolist()
-    else:
-        lens = [ctx] * B
-    mk_cache = lambda n: (torch.randn(LAYERS, n, KV_HEADS, HEAD_DIM, device=dev, generator=g) * 0.1).to(torch.bfloat16)
-    kcs, vcs = [mk_cache(n) for n in lens], [mk_cache(n) for n in lens]
-    mk = Megakernel(dev, max_batch=B)
-    seqs = SeqTable(kcs, vcs)
-    toks = torch.randint(0, VOCAB, (B,), device=dev, generator=g)
-    mk.bind_sequences(w, toks, seqs, graph=not args.plain)
-    for _ in range(3):
-        mk.launch()
-    torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n0 = mk.launch_count
-    e0.record()
-    for _ in range(args.steps):
-        mk.launch()
-    e1.record()
-    torch.cuda.synchronize(dev)
-    mk.status()
-    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    res = bench_mod.batched(dev, w, B, ctx, steps=args.steps, seed=args.seed, lens=lens, graph=not args.plain)
+    us = res["us_per_step"]
     if world > 1:
         us = replicas.max_over_ranks(us, dev)
         dist.barrier()
@@ -196,10 +178,9 @@ def cmd_batch(args) -> int:
             print(f"{world} replicas of batch {B}: {us:.1f} us/step on the slowest, {world * B * 1e6 / us:.0f} tokens/s over the job")
         dist.destroy_process_group()
         return 0
-    nbytes = 1_192_099_840 + sum(114_688 * n + 724_480 for n in lens)   # weights + gains + per-sequence K/V and activations
-    shape = f"{B} sequences of {min(lens)}..{max(lens)} (mean {sum(lens) / B:.0f})" if args.ragged else f"{B} x {ctx}"
+    shape = f"{B} sequences of {res['lens_min']}..{res['lens_max']} (mean {res['lens_mean']:.0f})" if args.ragged else f"{B} x {ctx}"
     print(f"batch {shape} cached positions: {us:.1f} us/step, {B * 1e6 / us:.0f} tokens/s, "
-          f"{nbytes / us / 1e6:.2f} TB/s of algorithmic bytes, {(mk.launch_count - n0) / args.steps:.0f} kernels per step"
+          f"{res['algorithmic_bytes'] / us / 1e6:.2f} TB/s of algorithmic bytes, {res['kernels_per_step']:.0f} kernels per step"
           f"{' (plain launches)' if args.plain else ' (graph replay)'}")
     return 0
 
