@@ -160,6 +160,17 @@ int q3_noalloc_status(void* stream, uint32_t* words, int32_t n);
 int q3_linear_tc(const void* w, const float* x, float* out, const float* resid, int32_t n_rows, int32_t n_tok, int32_t K,
                  int32_t nsplit, void* planes, int64_t planes_bytes, void* stream);
 
+/* Sample one token per row from fp32 logits [batch, vocab] on the device: keep the `top_k` largest logits of a row
+ * (0 = all; ties at the k-th value are all kept), weigh them by exp((logit - max) / temperature) and return the first
+ * index whose cumulative weight exceeds uniform[row] * total, in index order.  `uniform` is a device array of `batch`
+ * numbers in [0, 1) drawn by the caller (so that a seed reproduces a run); temperature <= 0 or top_k == 1 returns the
+ * arg-max (ties -> lowest index) and ignores `uniform`.  `out_tokens` (device int64 [batch]) may be the token buffer
+ * of the next q3_decode, so that a sampled stream needs no host round trip.  Allocates nothing, no host sync.
+ * The reference stops at greedy decoding and hands the fp32 logits to the caller for this step
+ * (csrc/qwen3_step.cu:175, qwen3mk/kernel.py:44-50). */
+int q3_sample(const float* logits, int32_t batch, int32_t vocab, float temperature, int32_t top_k,
+              const float* uniform, int64_t* out_tokens, void* stream);
+
 /* Synchronise `stream`, read the device status words and clear them.  Returns Q3_OK or
  * Q3_ERR_DEVICE_WAIT; `words` (may be NULL) receives up to `n` raw status words:
  * [0] error code, [1] where (phase id), [2] CTA index, [3] observed counter value. */

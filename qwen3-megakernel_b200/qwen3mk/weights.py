@@ -49,14 +49,18 @@ def resolve_model_dir(model_id_or_path: str = MODEL_ID) -> Path:
     return Path(snapshot_download(model_id_or_path, allow_patterns=["*.safetensors", "*.json", "merges.txt", "vocab.json"]))
 
 
-def load_hf(model_id_or_path: str = MODEL_ID, device="cpu") -> dict:
+def load_hf(model_id_or_path: str = MODEL_ID, device="cpu", *, layers: int | None = None, vocab: int | None = None) -> dict:
     """The 13 weight tensors of a Qwen3-0.6B checkpoint: bf16, [out, in] layout, stacked over layers, on `device`.
-    Raises ValueError when config.json does not describe the architecture the kernels are built for."""
+    Raises ValueError when config.json does not describe the architecture the kernels are built for.  `layers` and
+    `vocab` override the two extents the engine takes at run time (a cut-down checkpoint for tests); the per-head
+    geometry always has to match."""
     from safetensors import safe_open
 
     root = resolve_model_dir(model_id_or_path)
     config = json.loads((root / "config.json").read_text())
+    want_layers, want_vocab = LAYERS if layers is None else int(layers), VOCAB if vocab is None else int(vocab)
     for key, want in _REQUIRED_CONFIG:
+        want = {"num_hidden_layers": want_layers, "vocab_size": want_vocab}.get(key, want)
         if config.get(key) != want:
             raise ValueError(f"config.json {key}={config.get(key)!r}, the kernel needs {want!r}")
     shards = sorted(root.glob("*.safetensors"))
@@ -68,10 +72,12 @@ def load_hf(model_id_or_path: str = MODEL_ID, device="cpu") -> dict:
         where.update({k: f for k in f.keys()})
 
     def tensor(key: str) -> torch.Tensor:
+        if key not in where:
+            raise KeyError(f"{key} is in none of the {len(shards)} .safetensors files of {root}")
         return where[key].get_tensor(key)
 
-    specs = input_specs()
-    raw = {name: torch.stack([tensor(f"model.layers.{i}.{suffix}") for i in range(LAYERS)]) for name, suffix in _PER_LAYER}
+    specs = input_specs(want_layers, want_vocab)
+    raw = {name: torch.stack([tensor(f"model.layers.{i}.{suffix}") for i in range(want_layers)]) for name, suffix in _PER_LAYER}
     raw["fnorm"] = tensor("model.norm.weight")
     raw["embed"] = tensor("model.embed_tokens.weight")
     out = {}

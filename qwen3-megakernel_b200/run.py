@@ -4,6 +4,7 @@
   run.py check [--weights hf|synthetic] [--seed N] [--context N]
   run.py bench [--weights hf|synthetic] [--iters N] [--context N] [--grow] [--chains N]
   run.py trace [--context N]            per-phase timing of the persistent kernel (device time stamps)
+  run.py compare [--context N]          the engine next to cuBLAS-through-PyTorch under a CUDA graph, same inputs
   run.py batch [--batch B] [--context N] [--steps K] [--plain]   one batched decode step of the layered path
   run.py prefill [--tokens T] [--reps N]                         causal forward over T random ids
   run.py demo --prompt "..."
@@ -68,16 +69,25 @@ def cmd_check(args) -> int:
     fast = Megakernel(path="auto")
     slow = Megakernel(path="layered")
     out = fast.step(inputs)
-    ref = slow.step(inputs)
+    lay = slow.step(inputs)
     fast.status()
     slow.status()
-    print(f"persistent kernel (grid {fast.grid} x {fast.threads} threads) vs layered kernels")
-    gate("next_token equal", f"{int(out['next_token'])} / {int(ref['next_token'])}", "equal", int(out["next_token"]) == int(ref["next_token"]))
-    e = rel_l2(out["logits"], ref["logits"])
-    gate("logits rel-L2", f"{e:.3e}", GATE_LOGITS_REL_L2, e <= GATE_LOGITS_REL_L2)
-    for n in ("k_write", "v_write"):
-        u = bf16_ulps(out[n], ref[n])
-        gate(f"{n} max bf16 ulps", f"{u:.0f}", GATE_KV_ULPS, u <= GATE_KV_ULPS)
+    # the checker: the same step in fp32 PyTorch on the GPU, which shares no code with the kernels (the reference's own
+    # check compares its kernel with an fp32 PyTorch step: run.py:57-104)
+    from qwen3mk import baselines
+
+    chk = baselines.TorchGraphDecoder(inputs, products="fp32")
+    with torch.no_grad():
+        chk._step()
+    ref = {"logits": chk.logits, "next_token": chk.next_token, "k_write": chk.k_write, "v_write": chk.v_write}
+    for label, got in ((f"persistent kernel (grid {fast.grid} x {fast.threads} threads)", out), ("layered kernels", lay)):
+        print(f"{label} vs fp32 PyTorch")
+        gate("next_token equal", f"{int(got['next_token'])} / {int(ref['next_token'])}", "equal", int(got["next_token"]) == int(ref["next_token"]))
+        e = rel_l2(got["logits"], ref["logits"])
+        gate("logits rel-L2", f"{e:.3e}", GATE_LOGITS_REL_L2, e <= GATE_LOGITS_REL_L2)
+        for n in ("k_write", "v_write"):
+            u = bf16_ulps(got[n], ref[n])
+            gate(f"{n} max bf16 ulps", f"{u:.0f}", GATE_KV_ULPS, u <= GATE_KV_ULPS)
     changed = [k for k in inputs if not torch.equal(inputs[k], snap[k])]
     gate("inputs not mutated", changed or "none changed", "none", not changed)
     first = {k: v.clone() for k, v in out.items()}
@@ -145,6 +155,18 @@ def cmd_trace(args) -> int:
         skew = np.median([t[:, 1 + ev * l + d].max() - np.median(t[:, 1 + ev * l + d]) for l in range(1, L)])
         hop = np.median([np.median(t[:, 2 + ev * l + d]) - t[:, 1 + ev * l + d].max() for l in range(1, L)])
         print(f"  delta after {name:<3} skew {skew:6.0f} ns  hop {hop:6.0f} ns")
+    return 0
+
+
+def cmd_compare(args) -> int:
+    """The measured-comparator table (the reference's README.md:12-18 rows that need no extra package)."""
+    from qwen3mk import baselines
+
+    inputs, info = get_inputs(args.weights, args.seed, args.context)
+    g = bench_mod.gpu_info("cuda")
+    print(f"gpu: {g['name']}  SM clock: {g['sm_clock_mhz']} MHz  inputs: {info}")
+    for r in baselines.compare(inputs):
+        print(f"  {r['name']:<40} {r['us_per_step_median']:9.1f} us/step (min {r['us_per_step_min']:.1f})   {r['note']}")
     return 0
 
 
@@ -236,7 +258,7 @@ def cmd_demo(args) -> int:
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
-    for name in ("check", "bench", "trace"):
+    for name in ("check", "bench", "trace", "compare"):
         p = sub.add_parser(name)
         p.add_argument("--weights", choices=["hf", "synthetic"], default="synthetic")
         p.add_argument("--seed", type=int, default=0)
@@ -259,7 +281,7 @@ def main(argv=None) -> int:
     p = sub.add_parser("demo")
     p.add_argument("--prompt", default=DEFAULT_PROMPT)
     args = ap.parse_args(argv)
-    return {"check": cmd_check, "bench": cmd_bench, "trace": cmd_trace, "batch": cmd_batch, "prefill": cmd_prefill, "demo": cmd_demo}[args.cmd](args)
+    return {"check": cmd_check, "bench": cmd_bench, "trace": cmd_trace, "compare": cmd_compare, "batch": cmd_batch, "prefill": cmd_prefill, "demo": cmd_demo}[args.cmd](args)
 
 
 if __name__ == "__main__":

@@ -161,3 +161,45 @@ def test_oracle_batch_and_greedy_consistency(oracle):
     assert tuple(kc.shape) == (1, 4, 8, 128)
     alll = oracle.prefill(w, ids, return_all_logits=True)[2]
     assert torch.allclose(alll[-1], last, rtol=1e-5, atol=1e-6)
+
+
+def test_load_hf_reads_a_sharded_checkpoint_end_to_end(tmp_path):
+    """A 2-layer, 512-word checkpoint in the Hugging Face layout, split over two .safetensors files and stored as
+    fp32: names, stacking over layers, dtype and shapes must come out as the engine's 13 inputs."""
+    import json
+
+    import torch
+    from safetensors.torch import save_file
+
+    from qwen3mk import weights
+    from qwen3mk.kernel import input_specs
+
+    L, V = 2, 512
+    g = torch.Generator().manual_seed(0)
+    specs = input_specs(L, V)
+    want = {n: torch.randn(specs[n][0], generator=g).to(torch.bfloat16) for n in weights.WEIGHT_NAMES}
+    shard0, shard1 = {}, {}
+    for name, suffix in weights._PER_LAYER:
+        for i in range(L):
+            (shard0 if i == 0 else shard1)[f"model.layers.{i}.{suffix}"] = want[name][i].float().contiguous()
+    shard1["model.norm.weight"] = want["fnorm"].float()
+    shard0["model.embed_tokens.weight"] = want["embed"].float()
+    shard1["lm_head.weight"] = want["embed"].float()           # tied head stored twice, as some exports do: ignored
+    save_file(shard0, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file(shard1, str(tmp_path / "model-00002-of-00002.safetensors"))
+    cfg = {"hidden_size": 1024, "num_hidden_layers": L, "num_attention_heads": 16, "num_key_value_heads": 8, "head_dim": 128,
+           "intermediate_size": 3072, "vocab_size": V, "rope_theta": 1e6}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    got = weights.load_hf(str(tmp_path), layers=L, vocab=V)
+    assert tuple(got) == weights.WEIGHT_NAMES
+    for n in weights.WEIGHT_NAMES:
+        assert got[n].dtype == torch.bfloat16 and got[n].is_contiguous() and tuple(got[n].shape) == specs[n][0], n
+        assert torch.equal(got[n], want[n]), n
+    # the full-size extents are still the default
+    import pytest
+    with pytest.raises(ValueError, match="num_hidden_layers"):
+        weights.load_hf(str(tmp_path))
+    # a missing tensor is named
+    (tmp_path / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(KeyError, match="model.layers.1"):
+        weights.load_hf(str(tmp_path), layers=L, vocab=V)
