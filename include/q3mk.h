@@ -118,6 +118,23 @@ int q3_set_weights(q3_engine* e, const q3_weights* w);
  * No counterpart in the reference, which reads the caller's tensors directly. */
 int q3_invalidate_weights(q3_engine* e);
 
+/* Tensor parallelism over 2, 4 or 8 GPUs of one node, one process and one engine per GPU.  Rank r then owns query
+ * heads [r 16/size, ..), kv heads [r 8/size, ..), FFN rows [r 3072/size, ..) and, for the LM head, words
+ * [r vocab/size, ..); every rank keeps the whole residual stream.  The two per-layer sums over ranks (after the output
+ * projection and after the down projection) are red instructions from every rank's CTAs straight into every rank's
+ * accumulators over NVLink, fused into the phases that produce the partial sums; the grid barrier spans all ranks; the
+ * arg-max is settled through per-rank mailboxes.  Peer memory is only ever written (red / st), never read.
+ *   q3_tp_export: 64 bytes identifying this engine's state allocation (a CUDA IPC handle); the host exchanges them.
+ *   q3_tp_attach: map the `size` handles (64 bytes each, in rank order; this rank's own entry is ignored) and switch
+ *                 the engine to its share.  Call q3_set_weights afterwards (the FULL tensors: the engine packs its
+ *                 share).  size = 1 switches tensor parallelism off again.
+ * While attached, q3_decode serves batch 1 with up to 255 cached positions on the persistent path; every rank must
+ * enqueue the same step (the kernels wait for one another, bounded by the wait limit).  Outputs: next_token on every
+ * rank; logits only for the rank's words; k_write / v_write (and the appended cache rows) only for the rank's kv heads.
+ * The reference is single-GPU (qwen3mk/kernel.py:120-131); no counterpart. */
+int q3_tp_export(q3_engine* e, void* handle);
+int q3_tp_attach(q3_engine* e, int32_t rank, int32_t size, const void* handles);
+
 /* RoPE table: device fp32 [n_positions][128], row p = cos(p * f_0..f_63) then sin(p * f_0..f_63),
  * f_i = 1e6^(-2i/128).  Generalises the reference's single-position table
  * (qwen3mk/kernel.py:102-106).  Borrowed. */

@@ -165,6 +165,19 @@ extern "C" int q3_invalidate_weights(q3_engine* e) {
     return Q3_OK;
 }
 
+extern "C" int q3_tp_export(q3_engine* e, void* handle) {
+    if (!e || !handle) return fail(e, Q3_ERR_INVALID, "q3_tp_export: null argument");
+    CU(e, cudaSetDevice(e->device));
+    return persist_tp_export(e, handle);
+}
+
+extern "C" int q3_tp_attach(q3_engine* e, int32_t rank, int32_t size, const void* handles) {
+    if (!e) return fail(e, Q3_ERR_INVALID, "q3_tp_attach: null argument");
+    CU(e, cudaSetDevice(e->device));
+    drop_graphs(e);
+    return persist_tp_attach(e, rank, size, handles);
+}
+
 extern "C" int q3_set_rope(q3_engine* e, const float* table, int32_t n_positions) {
     if (!e || !table || n_positions < 1) return fail(e, Q3_ERR_INVALID, "q3_set_rope: bad argument");
     drop_graphs(e);

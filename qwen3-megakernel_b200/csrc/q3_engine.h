@@ -61,6 +61,8 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st);
 int persist_weights_changed(q3_engine* e);
 void persist_invalidate_weights(q3_engine* e);
 void* persist_accumulators(const q3_engine* e, int64_t* bytes);   // the four counted accumulator vectors (tests), or nullptr
+int persist_tp_export(q3_engine* e, void* handle64);
+int persist_tp_attach(q3_engine* e, int rank, int size, const void* handles);
 int persist_recover(q3_engine* e);   // after a device-side wait gave up: clear the exchange buffers and accumulators
 int engine_fail(q3_engine* e, int code, const char* fmt, ...);
 // the layered decode step on engine `e` (one launch per phase); `e` supplies weights, RoPE table and scratch

@@ -35,6 +35,8 @@
 //
 // What the reference does for the same step: csrc/qwen3_step.cu:382-818 (four barriers per layer,
 // attention recomputed by every slice CTA, fixed position 128).
+#include <cstring>
+
 #include "q3_engine.h"
 
 namespace q3 {
@@ -71,6 +73,7 @@ constexpr int ATT_WARPS = 8;                  // split attention: warps that att
 constexpr int N_ACC = Q3_N_ACC;               // accumulators for the FFN delta (fewer same-address atomics each)
 constexpr int EV_PER_LAYER = 12;              // trace stamps per layer
 constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;   // default patience of every device-side wait: 200 ms
+constexpr int MAX_TP = 8;                     // tensor-parallel ranks: 1, 2, 4 or 8 (at least one kv head each)
 constexpr int MAX_LAYERS = 63;                // the q/k/v tags of a launch are epoch * 64 + layer + 1
 // Counted accumulators: word = (contributions << 56) + sum of round(v * 2^32) as a 56-bit two's complement number.
 // A contribution is clamped to +-ACC_CLAMP so that MAX_GRID of them cannot reach the count field (2^55 / 2^32 = 8.4e6).
@@ -102,6 +105,15 @@ struct PersistParams {
     const float* rope;
     unsigned* sync;   // [0] grid barrier counter, [2] end-of-step ticket
     unsigned long long wait_ns;   // patience of every device-side wait
+    // Tensor parallelism over tp_size GPUs (1 = off).  Entry r of every array is rank r's buffer (this rank's own at
+    // r = tp_rank): the attention delta, the FFN delta, the grid-barrier counter and the end-of-step mailbox
+    // (two words per sender).  Peers' buffers are their memory, mapped into this process: they are only ever the
+    // target of red / st instructions, never read.
+    int tp_rank, tp_size;
+    unsigned long long* tp_dA[MAX_TP];
+    float* tp_dB[MAX_TP];
+    unsigned* tp_bar[MAX_TP];
+    unsigned long long* tp_mail[MAX_TP];
     uint32_t* status;
     float* pval;
     int* pidx;
@@ -112,6 +124,8 @@ struct PersistParams {
 struct PersistState {
     bf16_raw* packed;       // the layer matrices re-laid per CTA (see pack_weights_kernel)
     const void* src[7];     // the seven pointers `packed` was built from
+    int tp_rank, tp_size;   // tensor-parallel position (0, 1 when off)
+    float* peer_X[MAX_TP];  // the state allocations of all ranks as mapped here (own at tp_rank)
     float* X;               // dA[2] (64-bit words) | dB[3][N_ACC] (fp32) | xq[4096] (64-bit words) | epoch | xp
     int grid, smem;
 };
@@ -121,25 +135,33 @@ struct PersistState {
 constexpr int XP_STRIDE = 132;                // 64-bit words per published partial
 constexpr size_t XP_WORDS = (size_t)KV_HEADS * 2 * GROUP_CTAS * XP_STRIDE;
 constexpr size_t ACC_FLOATS = (size_t)(4 + 3 * N_ACC) * HIDDEN;   // two vectors of 64-bit words, 3 * N_ACC of floats
-constexpr size_t X_FLOATS = ACC_FLOATS + 2 * QKV_DIM + 64 + 2 * XP_WORDS;
+constexpr size_t TP_OFFSET = ACC_FLOATS + 2 * QKV_DIM + 64 + 2 * XP_WORDS;   // [0] barrier counter of the tensor-parallel mode; mailbox at + 64 floats
+constexpr size_t X_FLOATS = TP_OFFSET + 128;
 struct Share {
-    int q0, nq, qmax;       // rows [q0, q0 + nq) of [wq; wk; wv], slot rows qmax
-    int i0, ni, imax;       // FFN rows [i0, i0 + ni) of gate, up and down^T, slot rows imax
-    int fh, fs, fr0, fn;    // F: query head, Wo row slice index, slice rows [fr0, fr0 + fn)
+    int q0, nq, qmax;       // rows [q0, q0 + nq) of this rank's [wq; wk; wv] rows, slot rows qmax
+    int i0, ni, imax;       // FFN rows [i0, i0 + ni) of gate, up and down^T (global row numbers), slot rows imax
+    int fh, fhl, fs, fr0, fn;   // F: query head (global, local), Wo row slice index, slice rows [fr0, fr0 + fn)
+    int slices;             // Wo row slices per head
     bool has_f;
 };
-__host__ __device__ inline Share share_of(int c, int G) {
+// With T tensor-parallel ranks, rank r owns query heads [r 16/T, (r+1) 16/T), kv heads [r 8/T, (r+1) 8/T), FFN rows
+// [r 3072/T, (r+1) 3072/T) and, for the LM head, words [r V/T, (r+1) V/T); its 144 F CTAs are its 16/T heads times
+// 9 T row slices of Wo.
+__host__ __device__ inline Share share_of(int c, int G, int T = 1, int rank = 0) {
     Share s;
-    s.q0 = (int)((long long)c * QKV_DIM / G); s.nq = (int)((long long)(c + 1) * QKV_DIM / G) - s.q0; s.qmax = (QKV_DIM + G - 1) / G;
-    s.i0 = (int)((long long)c * INTER / G); s.ni = (int)((long long)(c + 1) * INTER / G) - s.i0; s.imax = (INTER + G - 1) / G;
+    const int QL = QKV_DIM / T, IL = INTER / T, HL = Q_HEADS / T;
+    s.q0 = (int)((long long)c * QL / G); s.nq = (int)((long long)(c + 1) * QL / G) - s.q0; s.qmax = (QL + G - 1) / G;
+    s.i0 = (int)((long long)c * IL / G); s.ni = (int)((long long)(c + 1) * IL / G) - s.i0; s.imax = (IL + G - 1) / G;
+    s.i0 += rank * IL;
     s.has_f = c < F_CTAS;
-    s.fh = c % Q_HEADS; s.fs = c / Q_HEADS;
-    s.fr0 = (s.fs * 256 / WO_SLICES) * 4; s.fn = ((s.fs + 1) * 256 / WO_SLICES) * 4 - s.fr0;
+    s.slices = F_CTAS / HL;
+    s.fhl = c % HL; s.fs = c / HL; s.fh = rank * HL + s.fhl;
+    s.fr0 = (s.fs * 256 / s.slices) * 4; s.fn = ((s.fs + 1) * 256 / s.slices) * 4 - s.fr0;
     return s;
 }
 // packed share of one (layer, CTA): A [qmax][WROW] | B [116][WOROW] | C [2 imax][WROW] | D [imax][WROW]
-__host__ __device__ inline size_t share_elems(int G) {
-    const int qmax = (QKV_DIM + G - 1) / G, imax = (INTER + G - 1) / G;
+__host__ __device__ inline size_t share_elems(int G, int T = 1) {
+    const int qmax = (QKV_DIM / T + G - 1) / G, imax = (INTER / T + G - 1) / G;
     return (size_t)(qmax + 3 * imax) * WROW + (size_t)WO_ROWS_MAX * WOROW;
 }
 
@@ -165,15 +187,27 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// SYS = true: system scope, for buffers that other GPUs add to as well (tensor parallelism)
+template <bool SYS>
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+    if (SYS) asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+    else asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 __device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
 // ---- counted accumulators ----------------------------------------------------------------------------
-__device__ __forceinline__ void acc_add(unsigned long long* addr, float v) {
+__device__ __forceinline__ unsigned long long acc_word(float v) {
     v = fminf(fmaxf(v, -ACC_CLAMP), ACC_CLAMP);
-    const unsigned long long w = ACC_ONE + (unsigned long long)__float2ll_rn(v * ACC_SCALE);
-    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(addr), "l"(w) : "memory");
+    return ACC_ONE + (unsigned long long)__float2ll_rn(v * ACC_SCALE);
+}
+template <bool SYS>
+__device__ __forceinline__ void acc_add(unsigned long long* addr, unsigned long long w) {
+    if (SYS) asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(addr), "l"(w) : "memory");
+    else asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(addr), "l"(w) : "memory");
+}
+template <bool SYS>
+__device__ __forceinline__ void acc_load2(const unsigned long long* src, unsigned long long& w0, unsigned long long& w1) {
+    if (SYS) asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(src) : "memory");
+    else asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(src) : "memory");
 }
 __device__ __forceinline__ unsigned acc_count(unsigned long long w) { return (unsigned)((w + ACC_HALF) >> 56); }
 __device__ __forceinline__ float acc_value(unsigned long long w) {
@@ -187,7 +221,13 @@ __device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 512;" :::
 __device__ __forceinline__ void counter_arrive(unsigned* cnt) {   // one thread, after a cta_sync
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
 }
+// the same on the counters of all `n` tensor-parallel ranks: one system-scope release fence, then one arrival each
+__device__ __forceinline__ void counter_arrive_all(unsigned* const* cnt, int n) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    for (int r = 0; r < n; ++r) asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(cnt[r]) : "memory");
+}
 // thread 0 polls until *cnt has reached `target` (wrap-safe), then every thread passes a cta_sync
+template <bool SYS>
 __device__ __forceinline__ void counter_wait(const unsigned* cnt, unsigned target, volatile int* abort_flag,
                                              uint32_t* status, uint32_t site, unsigned long long wait_ns) {
     if (threadIdx.x == 0 && !*abort_flag) {
@@ -195,7 +235,8 @@ __device__ __forceinline__ void counter_wait(const unsigned* cnt, unsigned targe
         unsigned long long t0 = 0;
         unsigned it = 0;
         for (;;) {
-            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+            if (SYS) asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
+            else asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(cnt) : "memory");
             if ((int)(v - target) >= 0) break;
             if ((++it & 255u) == 0) {
                 const unsigned long long t = global_ns();
@@ -207,7 +248,8 @@ __device__ __forceinline__ void counter_wait(const unsigned* cnt, unsigned targe
                 }
             }
         }
-        asm volatile("fence.acquire.gpu;" ::: "memory");
+        if (SYS) asm volatile("fence.acq_rel.sys;" ::: "memory");
+        else asm volatile("fence.acquire.gpu;" ::: "memory");
     }
     cta_sync();
 }
@@ -317,7 +359,9 @@ __device__ __forceinline__ int local_v_pos(int w, int i) { return w + CW * i; }
 // The host picks the variant from its upper bound of the length; a cache longer than the variant serves is reported.
 constexpr int N_MODES = 4;
 __host__ __device__ constexpr int mode_max_len(int mode) { return mode == 0 ? 128 : mode < N_MODES - 1 ? 127 + 64 * mode : PERSIST_MAX_LEN; }
-template <int MODE>
+// TP: tensor-parallel build of the same kernel (system-scope atomics on the deltas, every rank's CTAs arrive at every
+// rank's barrier, the arg-max is settled through the mailboxes); local attention only.
+template <int MODE, bool TP>
 __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -330,11 +374,15 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     }
 
     // ---- static ownership ----
-    const Share sh = share_of(c, G);
+    static_assert(!TP || MODE < N_MODES - 1, "tensor parallelism serves the local-attention variants only");
+    const int T = TP ? p.tp_size : 1, rank = TP ? p.tp_rank : 0;
+    const Share sh = share_of(c, G, T, rank);
     const int q0 = sh.q0, nq = sh.nq, i0 = sh.i0, ni = sh.ni, qmax = sh.qmax, imax = sh.imax;
     const bool has_f = sh.has_f;
-    const int fh = sh.fh, fs = sh.fs, fg = fh >> 1, fhh = fh & 1;
-    const int fj = fhh * WO_SLICES + fs;                          // index inside the kv-head group, 0..17
+    const int fh = sh.fh, fs = sh.fs, fg = fh >> 1, fhh = fh & 1;   // fg: the (global) kv head of this CTA's query head
+    const int fgl = sh.fhl >> 1;                                  // ... and its number among this rank's kv heads
+    const int qrows = Q_DIM / T, kvrows = KV_DIM / T;             // this rank's q rows and k (= v) rows
+    const int fj = fhh * sh.slices + fs;                          // index inside the kv-head group, 0..17 (without tensor parallelism)
     const int fr0 = sh.fr0, fn = sh.fn;
     (void)i0;
     const bool kv_writer = has_f && fj == 0;                      // one CTA per kv head stores the new K/V rows
@@ -384,8 +432,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_stream));
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_keep));
     auto lm_stream = [&](int wi, int nw, float& bestv, int& besti) {
-        const int V = p.vocab;
-        const int v0 = (int)((long long)c * V / G), v1 = (int)((long long)(c + 1) * V / G);
+        const int vlo = (int)((long long)rank * p.vocab / T), V = (int)((long long)(rank + 1) * p.vocab / T) - vlo;   // this rank's words
+        const int v0 = vlo + (int)((long long)c * V / G), v1 = vlo + (int)((long long)(c + 1) * V / G);
         const int vkeep = v0 + (int)((long long)(v1 - v0) * LM_KEEP_PCT / 100);
         for (int base = v0 + wi * 4; base < v1; base += nw * 4) {
             uint4 w[4][4];
@@ -439,7 +487,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         if (!pumper || layer >= L || (slot == 1 && !has_f)) return;
         const int bytes = slot == 0 ? bytesA : slot == 1 ? bytesB : slot == 2 ? bytesC : bytesD;
         const int off = slot == 0 ? 0 : slot == 1 ? bytesA : slot == 2 ? bytesA + bytesB : bytesA + bytesB + bytesC;
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.packed + ((size_t)layer * G + c) * share_elems(G)) + off;
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.packed + ((size_t)layer * G + c) * share_elems(G, T)) + off;
         unsigned char* dst = reinterpret_cast<unsigned char*>(slot == 0 ? sA : slot == 1 ? sB : slot == 2 ? sC : sD);
         fence_proxy_async();   // the slot's last readers used ordinary loads; they are behind a CTA barrier
         mbar_expect_tx(&full[slot], (uint32_t)bytes);
@@ -479,7 +527,8 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             unsigned it = 0;
             unsigned long long t0 = 0;
             for (;;) {
-                asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(ws) : "l"(vec + HIDDEN - 1) : "memory");
+                if (TP) asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(ws) : "l"(vec + HIDDEN - 1) : "memory");
+                else asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(ws) : "l"(vec + HIDDEN - 1) : "memory");
                 if (acc_count(ws) + 2u >= expect) break;
                 if ((++it & 63u) == 0) {
                     const unsigned long long t = global_ns();
@@ -495,7 +544,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             unsigned it = 0;
             unsigned long long t0 = 0;
             for (;;) {
-                asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(src) : "memory");
+                acc_load2<TP>(src, w0, w1);
                 if (acc_count(w0) == expect && acc_count(w1) == expect) break;
                 if ((++it & 63u) == 0) {
                     if (*abort_flag) break;
@@ -522,7 +571,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
         for (int i = 1; i < N_ACC; ++i) { s0 += d[i].x; s1 += d[i].y; }
         x0 += s0; x1 += s1;
     };
-    unsigned* bar = p.sync;
+    unsigned* bar = TP ? p.tp_bar[rank] : p.sync;
     unsigned target = 0;
     // Every (launch, layer) tags its q/k/v words differently, so a reader can tell a fresh word from an old one.
     const unsigned tag_base = __ldcg(p.epoch) * 64u;
@@ -705,7 +754,7 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             // ---- q (both heads of the group), k, v of the new position: warps 8..11 ----
             if (warp >= 8 && warp < 12) {
                 const int role = warp - 8;   // 0, 1: q heads 2g, 2g+1;  2: k;  3: v
-                const unsigned long long* src = p.xq + (role < 2 ? (2 * fg + role) * HEAD_DIM : (role == 2 ? Q_DIM + fg * HEAD_DIM : Q_DIM + KV_DIM + fg * HEAD_DIM)) + lane * 4;
+                const unsigned long long* src = p.xq + (role < 2 ? (2 * fgl + role) * HEAD_DIM : (role == 2 ? qrows + fgl * HEAD_DIM : qrows + kvrows + fgl * HEAD_DIM)) + lane * 4;
                 unsigned long long w0, w1, w2, w3;
                 {   // bounded poll: the four words of this lane must all carry this layer's tag
                     unsigned it = 0;
@@ -1043,7 +1092,11 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
                 if ((lane & 3) == 0) { wo_part[kh * 128 + 16 * rt + fr_n] = r0; wo_part[kh * 128 + 16 * rt + fr_n + 8] = r1; }
             }
             cta_sync();
-            if (tid < fn) acc_add(dAl + fr0 + tid, wo_part[tid] + wo_part[128 + tid]);   // fn <= 116: the slice joins the attention delta
+            if (tid < fn) {   // fn <= 116: the slice joins the attention delta (of every rank)
+                const unsigned long long w = acc_word(wo_part[tid] + wo_part[128 + tid]);
+                if (TP) { for (int r = 0; r < T; ++r) acc_add<true>(p.tp_dA[r] + (size_t)(l & 1) * HIDDEN + fr0 + tid, w); }
+                else acc_add<false>(dAl + fr0 + tid, w);
+            }
         }   // (wo_part is the next phase's staging area: the wait below passes a CTA barrier before anything is staged)
         Q3_TRACE(ev + 6);
         gain2 = *reinterpret_cast<const uint32_t*>(p.ln2 + (size_t)l * HIDDEN + 2 * tid);
@@ -1170,16 +1223,21 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             cta_sync();
             if (tid < 256) {
                 const float4 t = *reinterpret_cast<const float4*>(dout + tid * 4);
-                red_add_v4(dBl + (size_t)(c & (N_ACC - 1)) * HIDDEN + tid * 4, t.x, t.y, t.z, t.w);
+                const size_t off = (size_t)(l % 3) * N_ACC * HIDDEN + (size_t)(c & (N_ACC - 1)) * HIDDEN + tid * 4;
+                if (TP) { for (int r = 0; r < T; ++r) red_add_v4<true>(p.tp_dB[r] + off, t.x, t.y, t.z, t.w); }
+                else red_add_v4<false>(p.dB + off, t.x, t.y, t.z, t.w);
             }
             cta_sync();
             Q3_TRACE(ev + 10);
-            if (tid == 0) counter_arrive(bar);
+            if (tid == 0) {
+                if (TP) counter_arrive_all(p.tp_bar, T);
+                else counter_arrive(bar);
+            }
         }
-        target += G;
+        target += (unsigned)(T * G);
         gain2 = (l + 1 < L) ? *reinterpret_cast<const uint32_t*>(p.ln1 + (size_t)(l + 1) * HIDDEN + 2 * tid)
                             : *reinterpret_cast<const uint32_t*>(p.fnorm + 2 * tid);
-        counter_wait(bar, target, abort_flag, p.status, 300 + l, wait_ns);
+        counter_wait<TP>(bar, target, abort_flag, p.status, 300 + l, wait_ns);
         Q3_TRACE(ev + 11);
     }
 
@@ -1236,18 +1294,48 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
             cta_sync();
             if (lane == 0) { bv_s[warp] = bv; bi_s[warp] = bi; }
             cta_sync();
+            // every CTA has read its last delta: the next launch starts from clean accumulators (dA and dB are adjacent)
+            for (int i = tid; i < (int)(ACC_FLOATS / 4); i += CT) __stcg(reinterpret_cast<float4*>(p.dA) + i, make_float4(0.f, 0.f, 0.f, 0.f));
+            cta_sync();
             if (tid == 0) {
                 for (int w = 1; w < CW; ++w)
                     if (bv_s[w] > bv || (bv_s[w] == bv && bi_s[w] < bi)) { bv = bv_s[w]; bi = bi_s[w]; }
+                if (TP) {
+                    // This rank's best word goes to every rank's mailbox; the best of all ranks is the token.  The mail is
+                    // also the hand-over to the next launch: a peer that holds it may start adding to this rank's deltas
+                    // and arriving at its barrier, so the accumulators are clean and the counter is rearmed before it leaves.
+                    *bar = 0u;
+                    asm volatile("fence.acq_rel.sys;" ::: "memory");
+                    const unsigned long long mtag = (unsigned long long)(tag_base / 64u + 1u) << 32;
+                    for (int r = 0; r < T; ++r)
+                        asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(p.tp_mail[r] + 2 * rank),
+                                     "l"(mtag | __float_as_uint(bv)), "l"(mtag | (unsigned)bi) : "memory");
+                    for (int r = 0; r < T && !*abort_flag; ++r) {
+                        unsigned long long m0, m1;
+                        unsigned it = 0;
+                        unsigned long long t0 = 0;
+                        for (;;) {
+                            asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(m0), "=l"(m1) : "l"(p.tp_mail[rank] + 2 * r) : "memory");
+                            if ((m0 >> 32) == (mtag >> 32) && (m1 >> 32) == (mtag >> 32)) break;
+                            if ((++it & 63u) == 0) {
+                                const unsigned long long t = global_ns();
+                                if (t0 == 0) t0 = t;
+                                else if (t - t0 > wait_ns) { report(p.status, ST_PEER_TIMEOUT, 500 + r, (uint32_t)(m0 >> 32)); *abort_flag = 1; break; }
+                            }
+                        }
+                        if (*abort_flag) break;
+                        const float ov = __uint_as_float((unsigned)m0);
+                        const int oi = (int)(unsigned)m1;
+                        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+                    }
+                } else {
+                    p.sync[0] = 0;   // every CTA has passed every barrier: rearm the counter for the next launch
+                }
                 p.next_token[0] = bi;
                 if (p.append) p.seq_len[0] = len + 1;
-                // every CTA has passed every barrier: rearm the counters for the next launch
-                p.sync[0] = 0;
                 p.sync[2] = 0;
                 *const_cast<unsigned*>(p.epoch) = tag_base / 64u + 1u;
             }
-            // every CTA has read its last delta: the next launch starts from clean accumulators (dA and dB are adjacent)
-            for (int i = tid; i < (int)(ACC_FLOATS / 4); i += CT) __stcg(reinterpret_cast<float4*>(p.dA) + i, make_float4(0.f, 0.f, 0.f, 0.f));
         }
         Q3_TRACE(2 + EV_PER_LAYER * L);
     }
@@ -1268,21 +1356,24 @@ __global__ void __launch_bounds__(PT, 1) q3_persist_decode(const PersistParams p
 struct PackArgs {
     const bf16_raw *wq, *wk, *wv, *wo, *wg, *wu, *wd;
     bf16_raw* packed;
+    int tp_size, tp_rank;   // the rank's share of the heads and FFN rows is what gets packed
 };
 __global__ void __launch_bounds__(256) pack_weights_kernel(const PackArgs a) {
     const int c = blockIdx.x, G = gridDim.x, l = blockIdx.y;
-    const Share sh = share_of(c, G);
-    bf16_raw* dst = a.packed + ((size_t)l * G + c) * share_elems(G);
+    const int T = a.tp_size, rank = a.tp_rank;
+    const Share sh = share_of(c, G, T, rank);
+    const int qrows = Q_DIM / T, kvrows = KV_DIM / T;
+    bf16_raw* dst = a.packed + ((size_t)l * G + c) * share_elems(G, T);
     const uint4 zero = make_uint4(0, 0, 0, 0);
     // A: 129 16-byte units per row (128 of data, 1 of padding)
     for (int u = threadIdx.x; u < sh.qmax * 129; u += 256) {
         const int j = u / 129, k = u % 129;
         uint4 v = zero;
         if (j < sh.nq && k < 128) {
-            const int r = sh.q0 + j;
-            const bf16_raw* src = r < Q_DIM ? a.wq + ((size_t)l * Q_DIM + r) * HIDDEN
-                                : r < Q_DIM + KV_DIM ? a.wk + ((size_t)l * KV_DIM + (r - Q_DIM)) * HIDDEN
-                                                     : a.wv + ((size_t)l * KV_DIM + (r - Q_DIM - KV_DIM)) * HIDDEN;
+            const int r = sh.q0 + j;   // row of this rank's [q rows; k rows; v rows]
+            const bf16_raw* src = r < qrows ? a.wq + ((size_t)l * Q_DIM + rank * qrows + r) * HIDDEN
+                                : r < qrows + kvrows ? a.wk + ((size_t)l * KV_DIM + rank * kvrows + (r - qrows)) * HIDDEN
+                                                     : a.wv + ((size_t)l * KV_DIM + rank * kvrows + (r - qrows - kvrows)) * HIDDEN;
             v = reinterpret_cast<const uint4*>(src)[k];
         }
         reinterpret_cast<uint4*>(dst)[u] = v;
@@ -1324,12 +1415,19 @@ static int smem_bytes_for(int grid) {
     return (qmax + 3 * imax) * WROW * 2 + WO_ROWS_MAX * WOROW * 2 + TAIL_BYTES;
 }
 
-static const void* persist_kernel(int mode) {
+static const void* persist_kernel(int mode, bool tp = false) {
+    if (tp) {
+        switch (mode) {
+            case 0: return reinterpret_cast<const void*>(q3_persist_decode<0, true>);
+            case 1: return reinterpret_cast<const void*>(q3_persist_decode<1, true>);
+            default: return reinterpret_cast<const void*>(q3_persist_decode<2, true>);
+        }
+    }
     switch (mode) {
-        case 0: return reinterpret_cast<const void*>(q3_persist_decode<0>);
-        case 1: return reinterpret_cast<const void*>(q3_persist_decode<1>);
-        case 2: return reinterpret_cast<const void*>(q3_persist_decode<2>);
-        default: return reinterpret_cast<const void*>(q3_persist_decode<3>);
+        case 0: return reinterpret_cast<const void*>(q3_persist_decode<0, false>);
+        case 1: return reinterpret_cast<const void*>(q3_persist_decode<1, false>);
+        case 2: return reinterpret_cast<const void*>(q3_persist_decode<2, false>);
+        default: return reinterpret_cast<const void*>(q3_persist_decode<3, false>);
     }
 }
 
@@ -1345,17 +1443,20 @@ int persist_setup(q3_engine* e) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, e->device) != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "cudaGetDeviceProperties failed");
     if ((size_t)smem > prop.sharedMemPerBlockOptin) return Q3_OK;
-    for (int mode = 0; mode < N_MODES; ++mode) {
-        cudaError_t err = cudaFuncSetAttribute(persist_kernel(mode), cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    for (int variant = 0; variant < 2 * N_MODES - 1; ++variant) {   // the four attention variants, then the three tensor-parallel ones
+        const void* fn = variant < N_MODES ? persist_kernel(variant) : persist_kernel(variant - N_MODES, true);
+        cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: set smem attribute (%d B): %s", smem, cudaGetErrorString(err));
         int per_sm = 0;
-        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, persist_kernel(mode), PT, smem);
+        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, PT, smem);
         if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: occupancy query: %s", cudaGetErrorString(err));
         if (per_sm < 1 || per_sm * e->sm_count < grid || !prop.cooperativeLaunch)
             return engine_fail(e, Q3_ERR_NOT_RESIDENT, "persist: %d CTAs of %d threads and %d B shared memory cannot be co-resident", grid, PT, smem);
     }
     PersistState* s = new PersistState();
     s->packed = nullptr; s->X = nullptr; s->grid = grid; s->smem = smem;
+    s->tp_rank = 0; s->tp_size = 1;
+    for (int i = 0; i < MAX_TP; ++i) s->peer_X[i] = nullptr;
     for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
     if (cudaMalloc(&s->X, X_FLOATS * sizeof(float)) != cudaSuccess ||
         cudaMemset(s->X, 0, X_FLOATS * sizeof(float)) != cudaSuccess ||
@@ -1372,6 +1473,8 @@ int persist_setup(q3_engine* e) {
 void persist_teardown(q3_engine* e) {
     PersistState* s = static_cast<PersistState*>(e->p_state);
     if (!s) return;
+    for (int r = 0; r < MAX_TP; ++r)
+        if (s->peer_X[r] && s->peer_X[r] != s->X) cudaIpcCloseMemHandle(s->peer_X[r]);
     if (s->packed) cudaFree(s->packed);
     if (s->X) cudaFree(s->X);
     delete s;
@@ -1382,7 +1485,10 @@ void persist_teardown(q3_engine* e) {
 // positions: 2 sequences 2 x 0.47 ms against 1.60 ms on the layered path; from 4 sequences on the layered path's
 // tensor-core projections win).
 bool persist_supports(const q3_engine* e, const q3_decode_args* a) {
-    return e->p_state != nullptr && a->batch >= 1 && a->batch <= PERSIST_MAX_BATCH && a->max_len <= PERSIST_MAX_LEN;
+    const PersistState* s = static_cast<const PersistState*>(e->p_state);
+    if (s == nullptr || a->batch < 1) return false;
+    if (s->tp_size > 1) return a->batch == 1 && a->max_len <= mode_max_len(N_MODES - 2);   // one sequence, local attention
+    return a->batch <= PERSIST_MAX_BATCH && a->max_len <= PERSIST_MAX_LEN;
 }
 
 // (Re)pack the layer matrices when one of the caller's pointers changes.  Runs on the legacy default
@@ -1397,7 +1503,7 @@ int persist_weights_changed(q3_engine* e) {
     for (int i = 0; i < 7; ++i) same = same && (s->src[i] == now[i]);
     if (same) return Q3_OK;
     auto bf = [](const void* p) { return reinterpret_cast<const bf16_raw*>(p); };
-    PackArgs a{bf(now[0]), bf(now[1]), bf(now[2]), bf(now[3]), bf(now[4]), bf(now[5]), bf(now[6]), s->packed};
+    PackArgs a{bf(now[0]), bf(now[1]), bf(now[2]), bf(now[3]), bf(now[4]), bf(now[5]), bf(now[6]), s->packed, s->tp_size, s->tp_rank};
     pack_weights_kernel<<<dim3(s->grid, e->cfg.n_layers), 256>>>(a);
     ++e->launches;
     cudaError_t err = cudaDeviceSynchronize();
@@ -1421,6 +1527,46 @@ void* persist_accumulators(const q3_engine* e, int64_t* bytes) {
     return s->X;
 }
 
+// ---- tensor parallelism: the ranks' state allocations are mapped into one another with CUDA IPC ----
+int persist_tp_export(q3_engine* e, void* handle64) {
+    PersistState* s = static_cast<PersistState*>(e->p_state);
+    if (!s) return engine_fail(e, Q3_ERR_UNSUPPORTED, "tensor parallelism needs the persistent kernel, which this engine does not have");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI hands IPC handles over as 64 bytes");
+    cudaIpcMemHandle_t h;
+    const cudaError_t err = cudaIpcGetMemHandle(&h, s->X);
+    if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(err));
+    memcpy(handle64, &h, 64);
+    return Q3_OK;
+}
+
+int persist_tp_attach(q3_engine* e, int rank, int size, const void* handles) {
+    PersistState* s = static_cast<PersistState*>(e->p_state);
+    if (!s) return engine_fail(e, Q3_ERR_UNSUPPORTED, "tensor parallelism needs the persistent kernel, which this engine does not have");
+    if (!(size == 1 || size == 2 || size == 4 || size == 8) || rank < 0 || rank >= size)
+        return engine_fail(e, Q3_ERR_INVALID, "q3_tp_attach: rank %d of %d (sizes 1, 2, 4, 8)", rank, size);
+    if (e->cfg.vocab % size) return engine_fail(e, Q3_ERR_INVALID, "q3_tp_attach: vocabulary %d does not divide over %d ranks", e->cfg.vocab, size);
+    for (int r = 0; r < MAX_TP; ++r) {   // drop earlier mappings
+        if (s->peer_X[r] && s->peer_X[r] != s->X) cudaIpcCloseMemHandle(s->peer_X[r]);
+        s->peer_X[r] = nullptr;
+    }
+    s->tp_rank = 0; s->tp_size = 1;
+    persist_invalidate_weights(e);       // the packed copy depends on the rank's share
+    if (size == 1) return Q3_OK;
+    if (!handles) return engine_fail(e, Q3_ERR_INVALID, "q3_tp_attach: handles are required");
+    for (int r = 0; r < size; ++r) {
+        if (r == rank) { s->peer_X[r] = s->X; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const char*>(handles) + 64 * r, 64);
+        void* ptr = nullptr;
+        const cudaError_t err = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "cudaIpcOpenMemHandle (rank %d): %s", r, cudaGetErrorString(err));
+        s->peer_X[r] = static_cast<float*>(ptr);
+    }
+    s->tp_rank = rank; s->tp_size = size;
+    if (cudaMemset(s->X, 0, X_FLOATS * sizeof(float)) != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "q3_tp_attach: clearing the state failed");
+    return Q3_OK;
+}
+
 void persist_invalidate_weights(q3_engine* e) {
     PersistState* s = static_cast<PersistState*>(e->p_state);
     if (s) for (int i = 0; i < 7; ++i) s->src[i] = nullptr;
@@ -1442,6 +1588,15 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
     p.epoch = reinterpret_cast<const unsigned*>(s->X + ACC_FLOATS + 2 * QKV_DIM);
     p.xp = reinterpret_cast<unsigned long long*>(s->X + ACC_FLOATS + 2 * QKV_DIM + 64);
     p.wait_ns = e->cfg.wait_limit_us > 0 ? (unsigned long long)e->cfg.wait_limit_us * 1000ull : WAIT_NS;
+    const bool tp = s->tp_size > 1;
+    p.tp_rank = s->tp_rank; p.tp_size = s->tp_size;
+    for (int r = 0; r < s->tp_size; ++r) {
+        float* X = s->peer_X[r] ? s->peer_X[r] : s->X;
+        p.tp_dA[r] = reinterpret_cast<unsigned long long*>(X);
+        p.tp_dB[r] = X + 4 * HIDDEN;
+        p.tp_bar[r] = reinterpret_cast<unsigned*>(X + TP_OFFSET);
+        p.tp_mail[r] = reinterpret_cast<unsigned long long*>(X + TP_OFFSET + 64);
+    }
     p.rope = e->rope; p.sync = e->sync; p.status = e->status; p.pval = e->pval; p.pidx = e->pidx;
     p.trace = (e->trace && e->trace_words >= (int64_t)s->grid * (4 + EV_PER_LAYER * e->cfg.n_layers)) ? e->trace : nullptr;
     p.n_layers = e->cfg.n_layers; p.vocab = e->cfg.vocab; p.append = (a->flags & Q3_F_APPEND_KV) ? 1 : 0;
@@ -1458,7 +1613,7 @@ int persist_decode(q3_engine* e, const q3_decode_args* a, cudaStream_t st) {
         q.k_write = p.k_write ? p.k_write + b * kv_row : nullptr;
         q.v_write = p.v_write ? p.v_write + b * kv_row : nullptr;
         void* args[] = {&q};
-        cudaError_t err = cudaLaunchCooperativeKernel(persist_kernel(mode), dim3(s->grid), dim3(PT), args, (size_t)s->smem, st);
+        cudaError_t err = cudaLaunchCooperativeKernel(persist_kernel(mode, tp), dim3(s->grid), dim3(PT), args, (size_t)s->smem, st);
         ++e->launches;
         if (err != cudaSuccess) return engine_fail(e, Q3_ERR_CUDA, "persist: cooperative launch failed: %s", cudaGetErrorString(err));
     }

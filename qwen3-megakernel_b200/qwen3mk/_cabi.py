@@ -10,7 +10,7 @@ OK, ERR_INVALID, ERR_CUDA, ERR_NOT_RESIDENT, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 
 F_APPEND_KV, F_PATH_AUTO, F_PATH_LAYERED, F_PATH_PERSIST, F_GRAPH = 0x1, 0x0, 0x10, 0x20, 0x100
 
 # every symbol include/q3mk.h declares
-SYMBOLS = ("q3_create", "q3_destroy", "q3_set_weights", "q3_invalidate_weights", "q3_set_rope", "q3_decode", "q3_decode_noalloc", "q3_noalloc_status", "q3_linear_tc", "q3_prefill", "q3_sample", "q3_status",
+SYMBOLS = ("q3_create", "q3_destroy", "q3_set_weights", "q3_invalidate_weights", "q3_set_rope", "q3_tp_export", "q3_tp_attach", "q3_decode", "q3_decode_noalloc", "q3_noalloc_status", "q3_linear_tc", "q3_prefill", "q3_sample", "q3_status",
            "q3_set_trace", "q3_launch_count", "q3_grid_info", "q3_scratch", "q3_last_error", "q3_version")
 
 WEIGHT_FIELDS = ("ln1", "wq", "wk", "wv", "qn", "kn", "wo", "ln2", "wg", "wu", "wd", "fnorm", "embed")
@@ -59,6 +59,10 @@ def load() -> C.CDLL:
     lib.q3_invalidate_weights.restype = C.c_int
     lib.q3_set_rope.argtypes = [C.c_void_p, C.c_void_p, C.c_int32]
     lib.q3_set_rope.restype = C.c_int
+    lib.q3_tp_export.argtypes = [C.c_void_p, C.c_void_p]
+    lib.q3_tp_export.restype = C.c_int
+    lib.q3_tp_attach.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+    lib.q3_tp_attach.restype = C.c_int
     lib.q3_decode.argtypes = [C.c_void_p, C.POINTER(DecodeArgs), C.c_void_p]
     lib.q3_decode.restype = C.c_int
     lib.q3_decode_noalloc.argtypes = [C.POINTER(Weights), C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(DecodeArgs), C.c_void_p]

@@ -163,6 +163,7 @@ class Megakernel:
         self._out_specs = output_specs(self.layers, self.vocab)
         self._weights_key = None
         self._weights_ref = None
+        self.tp = None           # the rank's tensor-parallel share (qwen3mk.tp.attach), or None
         self._seq_cache = {}     # step(): descriptors per (kcache ptr, vcache ptr, context)
         self._next = None        # step(): outputs of the next call, allocated while the kernel runs
         self._bound = None
