@@ -217,6 +217,46 @@ def run_reference_arm(args, rank: int, world: int) -> None:
     print(json.dumps(line))
 
 
+def tensor_parallel_record(dev, inputs: dict, world: int, barrier) -> dict:
+    """Batch-1 decode split over all `world` GPUs (heads, FFN rows and vocabulary sharded; the per-layer sums run inside the
+    kernel over NVLink).  Tokens of 64 growing steps are compared with the single-GPU engine's on the same inputs; the time
+    is the steady figure at position 128 and the mean of the 64 growing steps, the slowest rank's."""
+    from qwen3mk import Megakernel, bench as bench_mod, replicas, tp
+
+    n_tok = 64
+
+    def stream(mk):
+        mk.bind(inputs, chained=True, grow=n_tok)
+        toks = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(n_tok):
+            mk.launch()
+            toks.append(mk.chain_token.clone())
+        e1.record()
+        torch.cuda.synchronize(dev)
+        mk.status()
+        return torch.stack(toks).cpu().tolist(), e0.elapsed_time(e1) * 1e3 / n_tok
+
+    single = Megakernel(dev, path="persist", max_positions=8192)
+    want, _ = stream(single)
+    del single
+    mk = Megakernel(dev, path="persist", max_positions=8192, wait_limit_us=2_000_000)
+    shard = tp.attach(mk)
+    got, grow_us = stream(mk)
+    barrier()
+    static_us = bench_mod.steady(mk, inputs, steps=50, reps=5, warmup=50)["us_per_step_median"]
+    mk.status()
+    barrier()
+    same = sum(int(a == b) for a, b in zip(got, want))
+    return {"ranks": world, "us_per_step_ctx128": replicas.max_over_ranks(static_us, dev),
+            "us_per_step_growing_64": replicas.max_over_ranks(grow_us, dev), "tokens_equal_to_single_gpu": f"{same}/{n_tok}",
+            "tokens_per_s": 1e6 / replicas.max_over_ranks(static_us, dev),
+            "shard": {"q_heads": len(shard.q_heads), "kv_heads": len(shard.kv_heads), "ffn_rows": len(shard.ffn_rows), "words": len(shard.words)},
+            "note": "one decode stream over all GPUs; sums over ranks by red instructions into every rank's accumulators over NVLink"}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -312,6 +352,11 @@ def main() -> int:
         b64_us = replicas.max_over_ranks(b64["us_per_step"], dev)
         barrier()
 
+    # ---- tensor parallelism over all N GPUs: the same stream as one job instead of N replicas ------------------------
+    tp_rec = None
+    if world in (2, 4, 8) and not args.skip_extras:
+        tp_rec = tensor_parallel_record(dev, inputs, world, barrier)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -351,6 +396,8 @@ def main() -> int:
         "static_ctx128": {"us_per_step": static_us, "vs_published": static_us / PUBLISHED_US,
                           "note": "position 128 held fixed: the case the reference's 373.6 us is quoted on"},
     }
+    if tp_rec is not None:
+        line["tp"] = tp_rec
     if b64 is not None:
         line["batch64_ctx1024"] = {"us_per_step_slowest": b64_us, "tokens_per_s_job": world * 64 * 1e6 / b64_us,
                                    "tokens_per_s_per_gpu": 64 * 1e6 / b64_us, "kernels_per_step": b64["kernels_per_step"],

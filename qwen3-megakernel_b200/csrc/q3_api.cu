@@ -502,7 +502,10 @@ static int prefill_batched(q3_engine* e, const q3_prefill_args* a, cudaStream_t 
     s.logits = a->last_logits;
     s.next_token = a->next_token ? a->next_token : reinterpret_cast<int64_t*>(d + 32);
     const PrefillCtx ctx{a->kcache, a->vcache, (long long)a->cache_capacity * KV_DIM};
-    return decode_layered(e, &s, st, 2, &ctx);
+    #ifndef Q3_PREFILL_PLANES
+#define Q3_PREFILL_PLANES 2
+#endif
+    return decode_layered(e, &s, st, Q3_PREFILL_PLANES, &ctx);
 }
 
 extern "C" int q3_linear_tc(const void* w, const float* x, float* out, const float* resid, int32_t n_rows, int32_t n_tok, int32_t K,
