@@ -109,7 +109,9 @@ int q3_create(int device, const q3_config* cfg, q3_engine** out);
 void q3_destroy(q3_engine* e);
 
 /* Record the weight pointers used by later calls (borrowed, never written).  Replaces the
- * pointer marshalling of Megakernel.step / bind (qwen3mk/kernel.py:185-188,203-206). */
+ * pointer marshalling of Megakernel.step / bind (qwen3mk/kernel.py:185-188,203-206).  When a pointer of the seven
+ * layer matrices differs from the last call's, the persistent kernel's packed copy is rebuilt: a kernel on the legacy
+ * default stream followed by cudaDeviceSynchronize (a device-wide wait, once per weight set). */
 int q3_set_weights(q3_engine* e, const q3_weights* w);
 
 /* The persistent kernel streams an engine-owned re-layout of the seven layer matrices (built by

@@ -340,7 +340,11 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
             // a prompt: tiled causal attention over the rows head_prep has just written into the cache
             const bf16_raw* kc = bf(prompt->kcache) + (size_t)l * prompt->layer_stride;
             const bf16_raw* vc = bf(prompt->vcache) + (size_t)l * prompt->layer_stride;
+#ifdef Q3_PREFILL_ATTN_MMA_SYNC
             LAUNCH(launch_prefill_attn(e->qkv, kc, vc, e->attn, B, st));
+#else
+            LAUNCH(launch_prefill_attn_tc(e->qkv, kc, vc, (int)(prompt->layer_stride / KV_DIM), e->attn, B, e->status, st));
+#endif
             if (tc) LAUNCH(launch_act_split(e->attn, Q_DIM, Q_DIM, nullptr, planes, prow, tc_planes, B, st));
         } else if (tc) {
             LAUNCH(launch_attn_planes(t, planes, prow, tc_planes, B, st));   // the merge writes the Wo GEMM's input planes

@@ -338,6 +338,9 @@ static bool cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t b
     *out = e.m;
     return true;
 }
+bool tc_cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
+    return cached_map(ptr, rows, cols, box_rows, out);
+}
 static int sm_count_of_current_device() {
     static int sms[MAX_DEVICES] = {};
     int dev = 0;

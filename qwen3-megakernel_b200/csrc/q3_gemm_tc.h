@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+struct CUtensorMap_st;   // <cuda.h>'s tensor map
+
 namespace q3 {
 
 enum { TC_EPI_STORE = 0, TC_EPI_RESID = 1, TC_EPI_ATOMIC = 2 };
@@ -56,5 +58,9 @@ struct GemmTcGroupCall {
     int out_is_zero;       // the caller has cleared the outputs: a split-K launch adds into them without a memset
 };
 cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st);
+
+// A cached tensor map of a row-major bf16 matrix [rows, cols]: boxes of 64 columns x box_rows rows, 128-byte swizzle,
+// out-of-range rows read as zeros.  (CUtensorMap is declared by <cuda.h>, which the caller includes.)
+bool tc_cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, ::CUtensorMap_st* out);
 
 }  // namespace q3
