@@ -5,13 +5,15 @@
 // 0..63 head 2g, rows 64..127 head 2g + 1), so every K/V tile is fetched once for both heads (GQA sharing).  It walks
 // the key tiles (128 keys) up to its diagonal:
 //     S  = Q K^T      M 128 x N 128 keys x K 128 dims: Q as TWO bf16 planes (hi + lo, so the scores carry fp32-grade
-//                     accuracy into the exponent), both K-major operands             -> TMEM columns [0, 128)
+//                     accuracy into the exponent), both K-major operands      -> TMEM columns [0, 128) / [128, 256)
 //     P  = exp(S - m) eight warps, two threads per row (64 keys each): tcgen05.ld, causal mask on the diagonal tile,
 //                     running max / sum, P rounded to bf16 into shared memory in the K-major swizzled operand layout
 //     PV = P V        M 128 x N 128 dims x K 128 keys; V is the MN-major B operand straight from its TMA tile
-//                                                                                    -> TMEM columns [128, 256)
+//                                                                             -> TMEM columns [256, 384) / [384, 512)
 //     O  = O c + PV   in registers (64 dims per thread), rescaled by c = exp(m_old - m_new)
-// The MMA thread issues S of the next tile right after PV of this one, so the tensor pipe overlaps the O update.
+// S and PV are double-buffered in TMEM (all 512 columns): the MMA thread issues S of tile t + 1 before it waits for P
+// of tile t, and the softmax warps fold PV of tile t - 1 into O after they have posted P of tile t, so the exponentials
+// (the bottleneck: 16 K of them per tile on the SFUs) run back to back while the tensor pipe works beside them.
 // A CTA takes a light and a heavy causal query tile (i and n - 1 - i), like the kernel it replaces, so the grid is
 // one even wave.  Every mbarrier wait is bounded.
 //
@@ -40,7 +42,9 @@ __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, volatile
     unsigned long long t0 = 0;
     for (;;) {
         uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        // test_wait, not try_wait: a try_wait on a phase that is not complete yet parks the thread for a while, and a tile
+        // has eight hand-offs between the MMA thread and the softmax warps
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(at_smem(bar)), "r"(parity) : "memory");
         if (ok) return true;
         if (*abort_flag) return false;
@@ -83,6 +87,20 @@ __device__ __forceinline__ uint32_t at_swz(int row, int col) {
     return (uint32_t)box * AT_BOX + (uint32_t)row * 128u + (uint32_t)((((c >> 3) ^ (row & 7)) << 4) + ((c & 7) << 1));
 }
 
+// The special-function pipe (16 results a cycle and SM) is this kernel's bottleneck: a tile needs 16 K exponentials and
+// the conversion of 16 K probabilities to bf16.  So: one ex2 per element (log2(e) is folded into the scale of Q) and one
+// conversion per PAIR of elements.
+__device__ __forceinline__ float at_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t at_pack_bf16(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
 __device__ __forceinline__ void at_ld32(uint32_t (&r)[32], uint32_t taddr) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -105,7 +123,7 @@ struct PrefillAttnTcArgs {
 __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                                         const __grid_constant__ CUtensorMap tm_v, const PrefillAttnTcArgs a) {
     extern __shared__ __align__(1024) unsigned char at_raw[];
-    __shared__ __align__(8) uint64_t k_full[AT_STAGES], v_full[AT_STAGES], kv_empty[AT_STAGES], s_full, p_full, o_full;
+    __shared__ __align__(8) uint64_t k_full[AT_STAGES], v_full[AT_STAGES], k_empty[AT_STAGES], v_empty[AT_STAGES], s_full[2], p_full, o_full[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
     __shared__ float pm[2][128];   // per-row partial maxima of the two column halves; reused for the partial sums at the end
@@ -122,16 +140,19 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
         for (int s = 0; s < AT_STAGES; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&k_full[s])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&v_full[s])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&kv_empty[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&k_empty[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&v_empty[s])) : "memory");
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&s_full)) : "memory");
+        for (int b = 0; b < 2; ++b) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&s_full[b])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&o_full[b])) : "memory");
+        }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 256;" ::"r"(at_smem(&p_full)) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&o_full)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         abort_flag = 0;
     }
     if (warp == 9) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(&tmem_base_s)), "r"(256u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(&tmem_base_s)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -152,7 +173,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
             const int row = i >> 5, c4 = (i & 31) * 4;
             const int pos = min(q0 + (row & 63), a.T - 1), head = 2 * g + (row >> 6);
             const float4 v = *reinterpret_cast<const float4*>(a.qkv + (size_t)pos * QKV_DIM + head * HEAD_DIM + c4);
-            const float x[4] = {v.x * ATTN_SCALE, v.y * ATTN_SCALE, v.z * ATTN_SCALE, v.w * ATTN_SCALE};
+            constexpr float QS = ATTN_SCALE * 1.4426950408889634f;   // scores in units of log2: probabilities are ex2(s - m)
+            const float x[4] = {v.x * QS, v.y * QS, v.z * QS, v.w * QS};
             bf16_raw h[4], l[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) { h[j] = f_to_bf(x[j]); l[j] = f_to_bf(x[j] - bf_to_f(h[j])); }
@@ -166,20 +188,24 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
         if (warp == 8) {
             // ------------------------------------------------------------------ TMA producer
             if (lane == 0) {
+                // K and V of a tile share a stage but are released separately: the K half is free as soon as S of its tile has
+                // been computed, a whole tile before the V half (after PV), so the next K is on its way that much earlier
                 for (int t = 0; t < n_kt; ++t) {
                     const int it = it0 + t, s = it % AT_STAGES;
-                    if (it >= AT_STAGES && !at_wait(&kv_empty[s], ((it / AT_STAGES) - 1) & 1, &abort_flag, a.status, 40)) break;
                     unsigned char* sk = sKV + (size_t)s * 2 * AT_KV_BYTES;
                     unsigned char* sv = sk + AT_KV_BYTES;
+                    if (it >= AT_STAGES && !at_wait(&k_empty[s], ((it / AT_STAGES) - 1) & 1, &abort_flag, a.status, 40)) break;
                     asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(&k_full[s])), "r"(AT_KV_BYTES) : "memory");
-                    asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(&v_full[s])), "r"(AT_KV_BYTES) : "memory");
 #pragma unroll
-                    for (int b = 0; b < 2; ++b) {      // the two 64-dim halves of the head
+                    for (int b = 0; b < 2; ++b)        // the two 64-dim halves of the head
                         asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                                      ::"r"(at_smem(sk + b * AT_BOX)), "l"(&tm_k), "r"(g * HEAD_DIM + 64 * b), "r"(t * AT_KT), "r"(at_smem(&k_full[s])) : "memory");
+                    if (it >= AT_STAGES && !at_wait(&v_empty[s], ((it / AT_STAGES) - 1) & 1, &abort_flag, a.status, 47)) break;
+                    asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(&v_full[s])), "r"(AT_KV_BYTES) : "memory");
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
                         asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                                      ::"r"(at_smem(sv + b * AT_BOX)), "l"(&tm_v), "r"(g * HEAD_DIM + 64 * b), "r"(t * AT_KT), "r"(at_smem(&v_full[s])) : "memory");
-                    }
                 }
             }
         } else if (warp == 9) {
@@ -188,7 +214,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
                 // D fp32, A and B bf16, M 128, N 128; bit 16: B is MN-major (V)
                 const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
                 const uint32_t idesc_o = idesc_s | (1u << 16);
-                auto issue_s = [&](int t) -> bool {    // S = (Q hi + Q lo) K^T of key tile t
+                auto issue_s = [&](int t) -> bool {    // S = (Q hi + Q lo) K^T of key tile t, into S buffer it & 1
                     const int it = it0 + t, s = it % AT_STAGES;
                     if (!at_wait(&k_full[s], (it / AT_STAGES) & 1, &abort_flag, a.status, 41)) return false;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -203,30 +229,33 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
                             const uint32_t acc = (plane | k) ? 1u : 0u;
                             asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                                          "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-                                         ::"r"(tmem_base), "l"(da), "l"(db), "r"(idesc_s), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+                                         ::"r"(tmem_base + (uint32_t)(it & 1) * 128u), "l"(da), "l"(db), "r"(idesc_s), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
                         }
                     }
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(&s_full)) : "memory");
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(&s_full[it & 1])) : "memory");
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(&k_empty[s])) : "memory");
                     return true;
                 };
                 bool ok = issue_s(0);
                 for (int t = 0; t < n_kt && ok; ++t) {
                     const int it = it0 + t, s = it % AT_STAGES;
-                    ok = at_wait(&p_full, it & 1, &abort_flag, a.status, 42) && at_wait(&v_full[s], (it / AT_STAGES) & 1, &abort_flag, a.status, 43);
+                    // S of the next tile first: its buffer was read before P of tile t - 1 was posted, and the exponentials of
+                    // tile t can be followed by those of tile t + 1 without waiting for the tensor pipe
+                    if (t + 1 < n_kt) ok = issue_s(t + 1);
+                    ok = ok && at_wait(&p_full, it & 1, &abort_flag, a.status, 42) && at_wait(&v_full[s], (it / AT_STAGES) & 1, &abort_flag, a.status, 43);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t sv = at_smem(sKV + (size_t)s * 2 * AT_KV_BYTES + AT_KV_BYTES), sp = at_smem(sP);
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {      // 16 keys a step
+                    for (int k = 0; k < 8; ++k) {      // 16 keys a step; PV buffer it & 1 (its previous tenant, tile t - 2, was folded into O before P of tile t was posted)
                         const uint64_t da = at_desc_k(sp + (uint32_t)(k >> 2) * AT_BOX + (uint32_t)(k & 3) * 32u);
                         const uint64_t db = at_desc_mn(sv + (uint32_t)k * 2048u);
                         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                                      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-                                     ::"r"(tmem_base + 128u), "l"(da), "l"(db), "r"(idesc_o), "r"(k ? 1u : 0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+                                     ::"r"(tmem_base + 256u + (uint32_t)(it & 1) * 128u), "l"(da), "l"(db), "r"(idesc_o), "r"(k ? 1u : 0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
                     }
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(&o_full)) : "memory");
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(&kv_empty[s])) : "memory");
-                    if (t + 1 < n_kt) ok = issue_s(t + 1);   // S of this tile has been read before P was posted
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(&o_full[it & 1])) : "memory");
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(&v_empty[s])) : "memory");
                 }
             }
         } else {
@@ -237,43 +266,64 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
             float o[64];
 #pragma unroll
             for (int j = 0; j < 64; ++j) o[j] = 0.f;
-            float m = -INFINITY, lsum = 0.f;
+            float m = -INFINITY, lsum = 0.f, c_prev = 1.f;
             bool ok = true;
+            // O = O c + PV of tile `it` (this thread's 64 dims), once its MMAs have completed
+            auto fold = [&](int it, float c) -> bool {
+                if (!at_wait(&o_full[it & 1], (it >> 1) & 1, &abort_flag, a.status, 45)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t v0[32], v1[32];
+                const uint32_t col = 256u + (uint32_t)(it & 1) * 128u + (uint32_t)(half * 64);
+                at_ld32(v0, trow + col);
+                at_ld32(v1, trow + col + 32u);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    o[j] = fmaf(o[j], c, __uint_as_float(v0[j]));
+                    o[32 + j] = fmaf(o[32 + j], c, __uint_as_float(v1[j]));
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                return true;
+            };
             for (int t = 0; t < n_kt && ok; ++t) {
                 const int it = it0 + t;
-                ok = at_wait(&s_full, it & 1, &abort_flag, a.status, 44);
+                ok = at_wait(&s_full[it & 1], (it >> 1) & 1, &abort_flag, a.status, 44);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 uint32_t r0[32], r1[32];
-                at_ld32(r0, trow + (uint32_t)(half * 64));
-                at_ld32(r1, trow + (uint32_t)(half * 64 + 32));
+                const uint32_t scol = (uint32_t)(it & 1) * 128u + (uint32_t)(half * 64);
+                at_ld32(r0, trow + scol);
+                at_ld32(r1, trow + scol + 32u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int key0 = t * AT_KT + half * 64;
+                if (t == n_kt - 1) {   // the diagonal tile: causal mask (it also hides keys past the prompt)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (key0 + j > qpos) r0[j] = 0xff800000u;            // -inf
+                        if (key0 + 32 + j > qpos) r1[j] = 0xff800000u;
+                    }
+                }
                 float tmax = -INFINITY;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float s0 = __uint_as_float(r0[j]), s1 = __uint_as_float(r1[j]);
-                    if (key0 + j > qpos) s0 = -INFINITY;            // causal mask (also hides keys past the prompt)
-                    if (key0 + 32 + j > qpos) s1 = -INFINITY;
-                    r0[j] = __float_as_uint(s0); r1[j] = __float_as_uint(s1);
-                    tmax = fmaxf(tmax, fmaxf(s0, s1));
-                }
+                for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
                 pm[half][row] = tmax;
                 asm volatile("bar.sync 1, 256;" ::: "memory");
                 const float mn = fmaxf(m, fmaxf(tmax, pm[half ^ 1][row]));   // finite: key 0 is visible to every row
-                const float c = __expf(m - mn);
+                const float c = at_ex2(m - mn);
                 m = mn;
                 float psum = 0.f;
                 uint32_t pk[32];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const float e0 = __expf(__uint_as_float(r0[2 * j]) - mn), e1 = __expf(__uint_as_float(r0[2 * j + 1]) - mn);
-                    const float e2 = __expf(__uint_as_float(r1[2 * j]) - mn), e3 = __expf(__uint_as_float(r1[2 * j + 1]) - mn);
+                    const float e0 = at_ex2(__uint_as_float(r0[2 * j]) - mn), e1 = at_ex2(__uint_as_float(r0[2 * j + 1]) - mn);
+                    const float e2 = at_ex2(__uint_as_float(r1[2 * j]) - mn), e3 = at_ex2(__uint_as_float(r1[2 * j + 1]) - mn);
                     psum += (e0 + e1) + (e2 + e3);
-                    pk[j] = (uint32_t)f_to_bf(e0) | ((uint32_t)f_to_bf(e1) << 16);
-                    pk[16 + j] = (uint32_t)f_to_bf(e2) | ((uint32_t)f_to_bf(e3) << 16);
+                    pk[j] = at_pack_bf16(e0, e1);
+                    pk[16 + j] = at_pack_bf16(e2, e3);
                 }
                 lsum = lsum * c + psum;
+                // the P buffer is free once PV of the previous tile has completed (long ago in practice)
+                if (t > 0 && !at_wait(&o_full[(it - 1) & 1], ((it - 1) >> 1) & 1, &abort_flag, a.status, 46)) { ok = false; break; }
                 // P[row][64 half .. 64 half + 63] as eight 16-byte chunks of box `half`
 #pragma unroll
                 for (int ch = 0; ch < 8; ++ch)
@@ -282,20 +332,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(at_smem(&p_full)) : "memory");
-                // ---- O = O c + P V (this thread's 64 dims) ----
-                ok = at_wait(&o_full, it & 1, &abort_flag, a.status, 45);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                at_ld32(r0, trow + 128u + (uint32_t)(half * 64));
-                at_ld32(r1, trow + 128u + (uint32_t)(half * 64 + 32));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    o[j] = fmaf(o[j], c, __uint_as_float(r0[j]));
-                    o[32 + j] = fmaf(o[32 + j], c, __uint_as_float(r1[j]));
-                }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                // fold the PREVIOUS tile's PV into O while the tensor pipe works on this one
+                if (t > 0) ok = fold(it - 1, c_prev);
+                c_prev = c;
             }
+            if (ok) ok = fold(it0 + n_kt - 1, c_prev);
             // the row sum is split over the two halves' key ranges
             asm volatile("bar.sync 1, 256;" ::: "memory");   // the last tile's maxima have been read
             pm[half][row] = lsum;
@@ -315,7 +356,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
     __syncthreads();
     if (warp == 9) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
