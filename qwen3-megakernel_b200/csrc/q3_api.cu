@@ -298,8 +298,10 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         GemvArgs g{};
         // qkv = rms(x, ln1) @ [wq; wk; wv]^T
         if (tc) {
+            // a split-K launch adds its partial tiles onto zeros, which the producer of its input planes writes on the side
             const ZeroRows zq{{e->qkv, nullptr}, {QKV_DIM, 0}, {QKV_DIM, 0}};
-            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln1) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st, &zq));
+            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln1) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st,
+                                    gemm_tc_splits_k(QKV_DIM, B, HIDDEN) ? &zq : nullptr));
             {   // the three projections in one launch: 32 weight tiles instead of 16 + 8 + 8
                 GemmTcGroupCall c{};
                 c.n_groups = 3;
@@ -340,12 +342,8 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
             // a prompt: tiled causal attention over the rows head_prep has just written into the cache
             const bf16_raw* kc = bf(prompt->kcache) + (size_t)l * prompt->layer_stride;
             const bf16_raw* vc = bf(prompt->vcache) + (size_t)l * prompt->layer_stride;
-#ifdef Q3_PREFILL_ATTN_MMA_SYNC
-            LAUNCH(launch_prefill_attn(e->qkv, kc, vc, e->attn, B, st));
-#else
-            LAUNCH(launch_prefill_attn_tc(e->qkv, kc, vc, (int)(prompt->layer_stride / KV_DIM), e->attn, B, e->status, st));
-#endif
-            if (tc) LAUNCH(launch_act_split(e->attn, Q_DIM, Q_DIM, nullptr, planes, prow, tc_planes, B, st));
+            // tcgen05 attention; it writes the Wo GEMM's input planes itself
+            LAUNCH(launch_prefill_attn_tc(e->qkv, kc, vc, (int)(prompt->layer_stride / KV_DIM), planes, prow, tc_planes, B, e->status, st));
         } else if (tc) {
             LAUNCH(launch_attn_planes(t, planes, prow, tc_planes, B, st));   // the merge writes the Wo GEMM's input planes
             ++e->launches;  // two kernels
@@ -359,7 +357,8 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
             LAUNCH(gemm(bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN, Q_DIM, e->x, HIDDEN, e->x, HIDDEN));
             // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
             const ZeroRows zf{{e->gate, e->up}, {INTER, INTER}, {INTER, INTER}};
-            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st, &zf));
+            LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st,
+                                    gemm_tc_splits_k(2 * INTER, B, HIDDEN) ? &zf : nullptr));
             {   // gate and up in one launch
                 GemmTcGroupCall c{};
                 c.n_groups = 2;
@@ -483,11 +482,17 @@ extern "C" int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream) {
     return Q3_OK;
 }
 
+// Activation planes of a prompt's GEMMs.  One: the activations enter the tensor cores rounded to bf16, like the weights and
+// like the cached K/V rows that the prompt's later positions attend anyway.  Measured at 2048 tokens, full model, against
+// the fp32 CPU checker: K/V rows rel-L2 6.6e-3 and logits 5.6e-3 with one plane, 4.0e-3 and 3.2e-3 with two (the cache
+// rounding dominates both; the gates are 1e-2 and 2e-2); 5.6 ms against 7.3 ms.
+constexpr int PREFILL_PLANES = 1;
+
 // Prefill: the T prompt tokens run through the layered path as T one-token "sequences" of the same
 // cache, token t at position t.  head_prep writes every K/V row into the cache before the attention
 // kernels run, so token t attends rows [0, t) from the cache (rounded to bf16, as a later decode step
 // will see them) and its own row in fp32: causal attention, the numerics of token-by-token decode.
-// The projections are tensor-core GEMMs over two bf16 planes of the activations (relative error 2^-16).
+// The projections are tensor-core GEMMs over PREFILL_PLANES bf16 planes of the activations.
 static int prefill_batched(q3_engine* e, const q3_prefill_args* a, cudaStream_t st) {
     const int T = a->n_tokens;
     char* d = reinterpret_cast<char*>(e->pf_desc);
@@ -506,10 +511,7 @@ static int prefill_batched(q3_engine* e, const q3_prefill_args* a, cudaStream_t 
     s.logits = a->last_logits;
     s.next_token = a->next_token ? a->next_token : reinterpret_cast<int64_t*>(d + 32);
     const PrefillCtx ctx{a->kcache, a->vcache, (long long)a->cache_capacity * KV_DIM};
-    #ifndef Q3_PREFILL_PLANES
-#define Q3_PREFILL_PLANES 2
-#endif
-    return decode_layered(e, &s, st, Q3_PREFILL_PLANES, &ctx);
+    return decode_layered(e, &s, st, PREFILL_PLANES, &ctx);
 }
 
 extern "C" int q3_linear_tc(const void* w, const float* x, float* out, const float* resid, int32_t n_rows, int32_t n_tok, int32_t K,

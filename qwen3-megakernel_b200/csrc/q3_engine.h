@@ -73,7 +73,6 @@ struct PrefillCtx {
     long long layer_stride;
 };
 int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes = 3, const PrefillCtx* prompt = nullptr);
-cudaError_t launch_prefill_attn(const float* qkv, const void* kcache_layer, const void* vcache_layer, float* attn, int T, cudaStream_t st);
-cudaError_t launch_prefill_attn_tc(const float* qkv, const void* kcache_layer, const void* vcache_layer, int cap_rows, float* attn, int T,
-                                   uint32_t* status, cudaStream_t st);
+cudaError_t launch_prefill_attn_tc(const float* qkv, const void* kcache_layer, const void* vcache_layer, int cap_rows, void* planes,
+                                   int plane_rows, int nsplit, int T, uint32_t* status, cudaStream_t st);
 }  // namespace q3

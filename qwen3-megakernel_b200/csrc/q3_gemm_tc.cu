@@ -256,25 +256,28 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t co
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Few output tiles (decode batches, short prompts) cannot fill the GPU: slice K so that about `fill` CTAs per SM stream
+// weights, at least two k blocks per slice.  Measured with fill = 1 / 2 / 3: prefill of 2048 tokens 13.9 / 11.2 / 10.9 ms
+// (the Wo and down launches have 128 tiles of long K: one wave of long serial CTAs unless K is cut), batch-8 decode step
+// 1322 / 1250 / 1249 us, batch 64 3017 / 3031 / 3000 us; a prompt of 128 tokens (one 128-token tile) is the exception:
+// 1.70 / 1.86 / 1.82 ms.  k blocks per slice at least 2 (batch 64 / batch 8 steps: 2 -> 3077 / 1433 us, 4 -> 3121 / 1477).
+static int sm_count_of_current_device();
+static int k_slices(int n_rows, int n_tok, int bn, int nkb, int sm_count) {
+    const int tiles = ((n_rows + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
+    const int fill = (n_tok > 64 && n_tok < 256) ? 1 : 3;
+    if (tiles >= fill * sm_count) return 1;
+    int ksplit = fill * sm_count / tiles;
+    if (ksplit > nkb / 2) ksplit = nkb / 2;
+    return ksplit < 1 ? 1 : ksplit;
+}
+
 template <int BN>
 static cudaError_t launch_bn(const CUtensorMap* tw, const CUtensorMap& tx, GemmTcParams p, int n_rows, int n_tok, int sm_count, cudaStream_t st) {
     // n_rows: all weight rows of the launch (the sum over the groups); tw: three maps (unused ones repeat the first)
     const int nkb = p.K / TC_BK;
     const int tiles = ((n_rows + TC_BM - 1) / TC_BM) * ((n_tok + BN - 1) / BN);
-    // Few output tiles (decode batches, short prompts) cannot fill the GPU: slice K so that about one
-    // CTA per SM streams weights, at least two k blocks per slice.
     int ksplit = 1;
-    // CTAs per SM the split aims at.  Measured with 1 / 2 / 3: prefill of 2048 tokens 13.9 / 11.2 / 10.9 ms (the Wo and
-    // down launches have 128 tiles of long K: one wave of long serial CTAs unless K is cut), batch-8 decode step
-    // 1322 / 1250 / 1249 us, batch 64 3017 / 3031 / 3000 us; a prompt of 128 tokens (one 128-token tile) is the
-    // exception: 1.70 / 1.86 / 1.82 ms.
-    const int fill = (n_tok > 64 && n_tok < 256) ? 1 : 3;
-    if (tiles < fill * sm_count && (p.epi == TC_EPI_STORE || p.resid == p.out)) {
-        ksplit = fill * sm_count / tiles;
-        int min_kb = 2;   // k blocks per slice at least (measured, batch 64 / batch 8 steps: 2 -> 3077 / 1433 us, 4 -> 3121 / 1477, 8 -> 3366 / 1760)
-        if (ksplit > nkb / min_kb) ksplit = nkb / min_kb;
-        if (ksplit < 1) ksplit = 1;
-    }
+    if (p.epi == TC_EPI_STORE || p.resid == p.out) ksplit = k_slices(n_rows, n_tok, BN, nkb, sm_count);
     p.kb_per_split = (nkb + ksplit - 1) / ksplit;
     ksplit = (nkb + p.kb_per_split - 1) / p.kb_per_split;
     if (ksplit > 1) {
@@ -337,6 +340,10 @@ static bool cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t b
     c.push_back(e);
     *out = e.m;
     return true;
+}
+bool gemm_tc_splits_k(int n_rows, int n_tok, int K) {
+    const int bn = n_tok <= 32 ? 32 : (n_tok <= 64 ? 64 : 128);
+    return k_slices(n_rows, n_tok, bn, K / TC_BK, sm_count_of_current_device()) > 1;
 }
 bool tc_cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
     return cached_map(ptr, rows, cols, box_rows, out);

@@ -59,6 +59,10 @@ struct GemmTcGroupCall {
 };
 cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st);
 
+// Whether a launch of n_rows weight rows (all groups together) against n_tok tokens will slice K, i.e. add partial tiles
+// into an output that must hold zeros (or the residual) beforehand.
+bool gemm_tc_splits_k(int n_rows, int n_tok, int K);
+
 // A cached tensor map of a row-major bf16 matrix [rows, cols]: boxes of 64 columns x box_rows rows, 128-byte swizzle,
 // out-of-range rows read as zeros.  (CUtensorMap is declared by <cuda.h>, which the caller includes.)
 bool tc_cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, ::CUtensorMap_st* out);

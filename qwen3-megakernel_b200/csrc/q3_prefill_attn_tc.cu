@@ -10,7 +10,8 @@
 //                     running max / sum, P rounded to bf16 into shared memory in the K-major swizzled operand layout
 //     PV = P V        M 128 x N 128 dims x K 128 keys; V is the MN-major B operand straight from its TMA tile
 //                                                                             -> TMEM columns [256, 384) / [384, 512)
-//     O  = O c + PV   in registers (64 dims per thread), rescaled by c = exp(m_old - m_new)
+//     O  = O c + PV   in registers (64 dims per thread), rescaled by c = exp(m_old - m_new); written at the end as the
+//                     bf16 plane(s) the Wo GEMM reads, so no fp32 round trip and no separate splitting kernel
 // S and PV are double-buffered in TMEM (all 512 columns): the MMA thread issues S of tile t + 1 before it waits for P
 // of tile t, and the softmax warps fold PV of tile t - 1 into O after they have posted P of tile t, so the exponentials
 // (the bottleneck: 16 K of them per tile on the SFUs) run back to back while the tensor pipe works beside them.
@@ -114,7 +115,8 @@ __device__ __forceinline__ void at_ld32(uint32_t (&r)[32], uint32_t taddr) {
 
 struct PrefillAttnTcArgs {
     const float* qkv;     // [T, 4096] fp32 after head_prep (q normalised + RoPE, unscaled)
-    float* attn;          // [T, 2048]
+    bf16_raw* planes;     // [nsplit][plane_rows][2048] bf16: the output, already split for the Wo GEMM (hi, then lo = what hi left)
+    int plane_rows, nsplit;
     int T;
     int paired;           // the grid has half as many blocks as query tiles
     uint32_t* status;
@@ -342,11 +344,20 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
             pm[half][row] = lsum;
             asm volatile("bar.sync 1, 256;" ::: "memory");
             const float inv = 1.f / (lsum + pm[half ^ 1][row]);
-            if (ok && qpos < a.T) {
-                float* dst = a.attn + (size_t)qpos * Q_DIM + (2 * g + (row >> 6)) * HEAD_DIM + half * 64;
+            if (ok && qpos < a.T) {   // 64 dims = 128 contiguous bytes per plane
+                const size_t off = (size_t)qpos * Q_DIM + (2 * g + (row >> 6)) * HEAD_DIM + half * 64;
 #pragma unroll
-                for (int j = 0; j < 64; j += 4)
-                    *reinterpret_cast<float4*>(dst + j) = make_float4(o[j] * inv, o[j + 1] * inv, o[j + 2] * inv, o[j + 3] * inv);
+                for (int j = 0; j < 64; j += 8) {
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float x = o[j + 2 * q] * inv, y = o[j + 2 * q + 1] * inv;
+                        hi[q] = at_pack_bf16(x, y);
+                        lo[q] = at_pack_bf16(x - bf_lo(hi[q]), y - bf_hi(hi[q]));
+                    }
+                    *reinterpret_cast<uint4*>(a.planes + off + j) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    if (a.nsplit > 1) *reinterpret_cast<uint4*>(a.planes + (size_t)a.plane_rows * Q_DIM + off + j) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                }
             }
         }
         it0 += n_kt;
@@ -360,8 +371,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
     }
 }
 
-cudaError_t launch_prefill_attn_tc(const float* qkv, const void* kcache_layer, const void* vcache_layer, int cap_rows, float* attn, int T,
-                                   uint32_t* status, cudaStream_t st) {
+cudaError_t launch_prefill_attn_tc(const float* qkv, const void* kcache_layer, const void* vcache_layer, int cap_rows, void* planes,
+                                   int plane_rows, int nsplit, int T, uint32_t* status, cudaStream_t st) {
+    if (nsplit < 1 || nsplit > 2) return cudaErrorInvalidValue;
     CUtensorMap tk, tv;
     // the layer's cache as a [cap_rows, 1024] bf16 matrix; boxes of 64 columns x 128 rows (keys past the cache read as zeros)
     if (!tc_cached_map(kcache_layer, (uint64_t)cap_rows, (uint64_t)KV_DIM, AT_KT, &tk)) return cudaErrorUnknown;
@@ -379,7 +391,7 @@ cudaError_t launch_prefill_attn_tc(const float* qkv, const void* kcache_layer, c
     }
     const int n_qt = (T + AT_QT - 1) / AT_QT;
     const int paired = n_qt * KV_HEADS > 148 ? 1 : 0;   // pair a light and a heavy tile per CTA once the unpaired grid would not fit one wave
-    PrefillAttnTcArgs a{qkv, attn, T, paired, status};
+    PrefillAttnTcArgs a{qkv, reinterpret_cast<bf16_raw*>(planes), plane_rows, nsplit, T, paired, status};
     prefill_attn_tc_kernel<<<dim3(paired ? (n_qt + 1) / 2 : n_qt, KV_HEADS), AT_THREADS, AT_SMEM, st>>>(tk, tv, a);
     return cudaGetLastError();
 }
