@@ -6,11 +6,11 @@
 // the key tiles (128 keys) up to its diagonal:
 //     S  = Q K^T      M 128 x N 128 keys x K 128 dims: Q as TWO bf16 planes (hi + lo, so the scores carry fp32-grade
 //                     accuracy into the exponent), both K-major operands      -> TMEM columns [0, 128) / [128, 256)
-//     P  = exp(S - m) eight warps, two threads per row (64 keys each): tcgen05.ld, causal mask on the diagonal tile,
+//     P  = exp(S - m) sixteen warps, four threads per row (32 keys each): tcgen05.ld, causal mask on the diagonal tile,
 //                     running max / sum, P rounded to bf16 into shared memory in the K-major swizzled operand layout
 //     PV = P V        M 128 x N 128 dims x K 128 keys; V is the MN-major B operand straight from its TMA tile
 //                                                                             -> TMEM columns [256, 384) / [384, 512)
-//     O  = O c + PV   in registers (64 dims per thread), rescaled by c = exp(m_old - m_new); written at the end as the
+//     O  = O c + PV   in registers (32 dims per thread), rescaled by c = exp(m_old - m_new); written at the end as the
 //                     bf16 plane(s) the Wo GEMM reads, so no fp32 round trip and no separate splitting kernel
 // S and PV are double-buffered in TMEM (all 512 columns): the MMA thread issues S of tile t + 1 before it waits for P
 // of tile t, and the softmax warps fold PV of tile t - 1 into O after they have posted P of tile t, so the exponentials
@@ -26,13 +26,17 @@
 
 namespace q3 {
 
-constexpr int AT_THREADS = 320;           // warps 0..7 softmax / output, warp 8 TMA producer, warp 9 MMA issuer + TMEM owner
+constexpr int AT_PARTS = 4;               // threads per row in the softmax: each takes 128 / AT_PARTS columns of S and of O
+constexpr int AT_SOFT = 128 * AT_PARTS;   // softmax / output threads: warps 0..15
+constexpr int AT_THREADS = AT_SOFT + 64;  // + warp 16 TMA producer, warp 17 MMA issuer and TMEM owner
 constexpr int AT_QT = 64;                 // query positions per CTA pass
 constexpr int AT_KT = 128;                // keys per tile
 constexpr int AT_STAGES = 2;
 constexpr uint32_t AT_BOX = 128 * 128;    // bytes of one [128 rows x 64 columns] bf16 box, 128-byte swizzle
 constexpr uint32_t AT_Q_BYTES = 2 * AT_BOX, AT_P_BYTES = 2 * AT_BOX, AT_KV_BYTES = 2 * AT_BOX;   // 128 x 128 bf16 = two boxes
-constexpr size_t AT_SMEM = 1024 + 2 * AT_Q_BYTES + AT_P_BYTES + AT_STAGES * 2 * AT_KV_BYTES;     // Q hi, Q lo, P, stages x (K, V)
+// Q hi, Q lo, P, stages x (K, V) = 224 KB; with the 3 KB of static shared memory below that is all an SM has, so the
+// dynamic part must start 1024-aligned by itself (the extern array is declared so) and the static part must stay <= 3 KB
+constexpr size_t AT_SMEM = 2 * AT_Q_BYTES + AT_P_BYTES + AT_STAGES * 2 * AT_KV_BYTES;
 constexpr unsigned long long AT_WAIT_NS = 200ull * 1000 * 1000;
 
 __device__ __forceinline__ uint32_t at_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -128,12 +132,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
     __shared__ __align__(8) uint64_t k_full[AT_STAGES], v_full[AT_STAGES], k_empty[AT_STAGES], v_empty[AT_STAGES], s_full[2], p_full, o_full[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
-    __shared__ float pm[2][128];   // per-row partial maxima of the two column halves; reused for the partial sums at the end
+    __shared__ float pm[AT_PARTS][128];   // per-row partial maxima of the column parts; reused for the partial sums at the end
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = blockIdx.y;                       // kv head; query heads 2g and 2g + 1
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(at_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* sQh = base;
+    unsigned char* sQh = at_raw;
     unsigned char* sQl = sQh + AT_Q_BYTES;
     unsigned char* sP = sQl + AT_Q_BYTES;
     unsigned char* sKV = sP + AT_P_BYTES;           // stage s: K at s * 2 * AT_KV_BYTES, V right after it
@@ -149,11 +152,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&s_full[b])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(at_smem(&o_full[b])) : "memory");
         }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 256;" ::"r"(at_smem(&p_full)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(at_smem(&p_full)), "r"(AT_SOFT) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         abort_flag = 0;
     }
-    if (warp == 9) {
+    if (warp == AT_SOFT / 32 + 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(&tmem_base_s)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -187,7 +190,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
 
-        if (warp == 8) {
+        if (warp == AT_SOFT / 32) {
             // ------------------------------------------------------------------ TMA producer
             if (lane == 0) {
                 // K and V of a tile share a stage but are released separately: the K half is free as soon as S of its tile has
@@ -210,7 +213,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
                                      ::"r"(at_smem(sv + b * AT_BOX)), "l"(&tm_v), "r"(g * HEAD_DIM + 64 * b), "r"(t * AT_KT), "r"(at_smem(&v_full[s])) : "memory");
                 }
             }
-        } else if (warp == 9) {
+        } else if (warp == AT_SOFT / 32 + 1) {
             // ------------------------------------------------------------------ MMA issuer
             if (lane == 0) {
                 // D fp32, A and B bf16, M 128, N 128; bit 16: B is MN-major (V)
@@ -261,29 +264,24 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
                 }
             }
         } else {
-            // ------------------------------------------------------------------ softmax and output: row = TMEM lane, half = 64 columns
-            const int row = (warp & 3) * 32 + lane, half = warp >> 2;
+            // ------------------------------------------------------------------ softmax and output: row = TMEM lane, part = 32 columns
+            const int row = (warp & 3) * 32 + lane, part = warp >> 2;
             const int qpos = q0 + (row & 63);
-            const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            float o[64];
+            const uint32_t trow = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(part * 32);
+            float o[32];
 #pragma unroll
-            for (int j = 0; j < 64; ++j) o[j] = 0.f;
+            for (int j = 0; j < 32; ++j) o[j] = 0.f;
             float m = -INFINITY, lsum = 0.f, c_prev = 1.f;
             bool ok = true;
-            // O = O c + PV of tile `it` (this thread's 64 dims), once its MMAs have completed
+            // O = O c + PV of tile `it` (this thread's 32 dims), once its MMAs have completed
             auto fold = [&](int it, float c) -> bool {
                 if (!at_wait(&o_full[it & 1], (it >> 1) & 1, &abort_flag, a.status, 45)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t v0[32], v1[32];
-                const uint32_t col = 256u + (uint32_t)(it & 1) * 128u + (uint32_t)(half * 64);
-                at_ld32(v0, trow + col);
-                at_ld32(v1, trow + col + 32u);
+                uint32_t v0[32];
+                at_ld32(v0, trow + 256u + (uint32_t)(it & 1) * 128u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    o[j] = fmaf(o[j], c, __uint_as_float(v0[j]));
-                    o[32 + j] = fmaf(o[32 + j], c, __uint_as_float(v1[j]));
-                }
+                for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], c, __uint_as_float(v0[j]));
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 return true;
             };
@@ -292,44 +290,40 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
                 ok = at_wait(&s_full[it & 1], (it >> 1) & 1, &abort_flag, a.status, 44);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t r0[32], r1[32];
-                const uint32_t scol = (uint32_t)(it & 1) * 128u + (uint32_t)(half * 64);
-                at_ld32(r0, trow + scol);
-                at_ld32(r1, trow + scol + 32u);
+                uint32_t r0[32];
+                at_ld32(r0, trow + (uint32_t)(it & 1) * 128u);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int key0 = t * AT_KT + half * 64;
+                const int key0 = t * AT_KT + part * 32;
                 if (t == n_kt - 1) {   // the diagonal tile: causal mask (it also hides keys past the prompt)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 32; ++j)
                         if (key0 + j > qpos) r0[j] = 0xff800000u;            // -inf
-                        if (key0 + 32 + j > qpos) r1[j] = 0xff800000u;
-                    }
                 }
                 float tmax = -INFINITY;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
-                pm[half][row] = tmax;
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                const float mn = fmaxf(m, fmaxf(tmax, pm[half ^ 1][row]));   // finite: key 0 is visible to every row
+                for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(r0[j]));
+                pm[part][row] = tmax;
+                asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFT) : "memory");
+                float mn = m;                                   // finite from the first tile on: key 0 is visible to every row
+#pragma unroll
+                for (int q = 0; q < AT_PARTS; ++q) mn = fmaxf(mn, pm[q][row]);
                 const float c = at_ex2(m - mn);
                 m = mn;
                 float psum = 0.f;
-                uint32_t pk[32];
+                uint32_t pk[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const float e0 = at_ex2(__uint_as_float(r0[2 * j]) - mn), e1 = at_ex2(__uint_as_float(r0[2 * j + 1]) - mn);
-                    const float e2 = at_ex2(__uint_as_float(r1[2 * j]) - mn), e3 = at_ex2(__uint_as_float(r1[2 * j + 1]) - mn);
-                    psum += (e0 + e1) + (e2 + e3);
+                    psum += e0 + e1;
                     pk[j] = at_pack_bf16(e0, e1);
-                    pk[16 + j] = at_pack_bf16(e2, e3);
                 }
                 lsum = lsum * c + psum;
                 // the P buffer is free once PV of the previous tile has completed (long ago in practice)
                 if (t > 0 && !at_wait(&o_full[(it - 1) & 1], ((it - 1) >> 1) & 1, &abort_flag, a.status, 46)) { ok = false; break; }
-                // P[row][64 half .. 64 half + 63] as eight 16-byte chunks of box `half`
+                // P[row][32 part .. 32 part + 31]: four 16-byte chunks of box part / 2, chunk slots 4 (part & 1) + ch
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch)
-                    *reinterpret_cast<uint4*>(sP + (uint32_t)half * AT_BOX + (uint32_t)row * 128u + (uint32_t)((ch ^ (row & 7)) << 4)) =
+                for (int ch = 0; ch < 4; ++ch)
+                    *reinterpret_cast<uint4*>(sP + (uint32_t)(part >> 1) * AT_BOX + (uint32_t)row * 128u + (uint32_t)((((part & 1) * 4 + ch) ^ (row & 7)) << 4)) =
                         make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -339,15 +333,18 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
                 c_prev = c;
             }
             if (ok) ok = fold(it0 + n_kt - 1, c_prev);
-            // the row sum is split over the two halves' key ranges
-            asm volatile("bar.sync 1, 256;" ::: "memory");   // the last tile's maxima have been read
-            pm[half][row] = lsum;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            const float inv = 1.f / (lsum + pm[half ^ 1][row]);
-            if (ok && qpos < a.T) {   // 64 dims = 128 contiguous bytes per plane
-                const size_t off = (size_t)qpos * Q_DIM + (2 * g + (row >> 6)) * HEAD_DIM + half * 64;
+            // the row sum is split over the parts' key ranges
+            asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFT) : "memory");   // the last tile's maxima have been read
+            pm[part][row] = lsum;
+            asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFT) : "memory");
+            float ltot = 0.f;
 #pragma unroll
-                for (int j = 0; j < 64; j += 8) {
+            for (int q = 0; q < AT_PARTS; ++q) ltot += pm[q][row];
+            const float inv = 1.f / ltot;
+            if (ok && qpos < a.T) {   // 32 dims = 64 contiguous bytes per plane
+                const size_t off = (size_t)qpos * Q_DIM + (2 * g + (row >> 6)) * HEAD_DIM + part * 32;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
                     uint32_t hi[4], lo[4];
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
@@ -365,7 +362,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 9) {
+    if (warp == AT_SOFT / 32 + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
