@@ -37,6 +37,9 @@ extern "C" {
 #define Q3_F_APPEND_KV    0x1u  /* write the new K/V rows into cache slot seq_len[b], then seq_len[b] += 1 */
 #define Q3_F_PATH_AUTO    0x0u  /* engine picks: persistent kernel for small batches, layered otherwise    */
 #define Q3_F_PATH_LAYERED 0x10u /* one launch per phase (debug ladder, large batches)                      */
+#define Q3_F_PATH_FUSED   0x30u /* layered, but batches of 4..64 run two launches per layer: split attention + one persistent
+                                   kernel for Wo, norm, gate/up, SiLU, down, norm and the next layer's q/k/v (opt-in: measured
+                                   slower than the launch chain so far) */
 #define Q3_F_PATH_PERSIST 0x20u /* one persistent cooperative launch per step                              */
 #define Q3_F_PATH_MASK    0xf0u
 #define Q3_F_GRAPH        0x100u /* layered path: capture the step's launches into a CUDA graph and replay it on later calls with the same arguments */

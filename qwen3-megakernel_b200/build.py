@@ -16,7 +16,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "qwen3mk" / "libq3mk.so"
 STAMP = HERE / "qwen3mk" / ".libq3mk.stamp"
-SOURCES = ["q3_api.cu", "q3_layered.cu", "q3_persist.cu", "q3_static.cu", "q3_gemm_tc.cu", "q3_prefill_attn_tc.cu", "q3_sample.cu"]
+SOURCES = ["q3_api.cu", "q3_layered.cu", "q3_persist.cu", "q3_static.cu", "q3_gemm_tc.cu", "q3_prefill_attn_tc.cu", "q3_sample.cu", "q3_layer_tc.cu", "q3_attn_mma.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared", "--fmad=true"]
 

@@ -8,6 +8,7 @@
 
 #include "q3_engine.h"
 #include "q3_gemm_tc.h"
+#include "q3_layer_tc.h"
 
 using namespace q3;
 
@@ -107,6 +108,7 @@ extern "C" int q3_create(int device, const q3_config* cfg, q3_engine** out) {
         (tc && ((rc = alloc(e, &e->planes, 3 * cap_pad * INTER * 2)) ||
                 (rc = alloc(e, (void**)&e->gate, B * INTER * 4)) ||
                 (rc = alloc(e, (void**)&e->up, B * INTER * 4)) ||
+                (rc = alloc(e, &e->lk_state, LK_STATE_BYTES)) ||
                 (cfg->max_batch >= Q3_TC_MIN_BATCH && (rc = alloc(e, (void**)&e->logits_tc, (size_t)cfg->max_batch * cfg->vocab * 4)))))) {
         strncpy(g_create_error, e->err, sizeof(g_create_error) - 1);
         q3_destroy(e);
@@ -138,7 +140,7 @@ extern "C" void q3_destroy(q3_engine* e) {
     delete static_cast<std::vector<GraphEntry>*>(e->graphs);
     if (e->capture_stream) cudaStreamDestroy(static_cast<cudaStream_t>(e->capture_stream));
     persist_teardown(e);
-    void* bufs[] = {e->x, e->qkv, e->attn, e->hid, e->part, e->pval, e->pidx, e->status, e->sync, e->pf_desc, e->planes, e->gate, e->up, e->logits_tc};
+    void* bufs[] = {e->x, e->qkv, e->attn, e->hid, e->part, e->pval, e->pidx, e->status, e->sync, e->pf_desc, e->planes, e->gate, e->up, e->logits_tc, e->lk_state};
     for (void* p : bufs)
         if (p) cudaFree(p);
     delete e;
@@ -227,6 +229,7 @@ extern "C" int q3_status(q3_engine* e, void* stream, uint32_t* words, int32_t n)
     // leave the engine reusable: clear the status and the barrier words
     CU(e, cudaMemset(e->status, 0, Q3_STATUS_WORDS * 4));
     CU(e, cudaMemset(e->sync, 0, Q3_SYNC_WORDS * 4));
+    if (e->lk_state) CU(e, cudaMemset(e->lk_state, 0, LK_STATE_BYTES));
     if (persist_recover(e) != Q3_OK) return Q3_ERR_CUDA;
     return fail(e, Q3_ERR_DEVICE_WAIT, "device status: code %u at site %u, CTA %u, value %u", h[0], h[1], h[2], h[3]);
 }
@@ -256,7 +259,7 @@ static int splits_for(const q3_engine* e, int batch, int max_len) {
     return s;
 }
 
-int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes, const PrefillCtx* prompt) {
+int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes, const PrefillCtx* prompt, bool layer_kernel) {
     const bool last_token_only = prompt != nullptr;
     const int B = a->batch, L = e->cfg.n_layers, V = e->cfg.vocab;
     const q3_weights& w = e->w;
@@ -294,7 +297,26 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
     if (cover > e->rope_n - 1) cover = e->rope_n - 1;
     const int len_bound = (int)cover;
     LAUNCH(launch_embed(reinterpret_cast<const long long*>(a->token), bf(w.embed), V, e->x, e->status, B, st, arg_keys, arg_tickets, a->seq_len, len_bound));
-    for (int l = 0; l < L; ++l) {
+    // Decode batches of 4..64 sequences: two launches per layer, the split attention and the persistent layer kernel
+    // (everything between two attentions: merge, Wo, norm, gate/up, SiLU, down, norm, q/k/v of the next layer).
+    const bool lk = layer_kernel && tc && prompt == nullptr && tc_planes == 3 && layer_tc_supports(e, B);
+    if (lk) LAUNCH(launch_layer_tc(e, LK_MODE_FIRST, 0, B, st));
+    for (int l = 0; lk && l < L; ++l) {
+        AttnArgs t{};
+        t.qkv = e->qkv; t.seq_k = a->seq_k; t.seq_v = a->seq_v;
+        t.seq_layer_stride = reinterpret_cast<const long long*>(a->seq_layer_stride);
+        t.seq_len = a->seq_len; t.part = e->part; t.layer = l; t.n_splits = ns;
+        t.chunk_pad = pad; t.len_bound = len_bound;
+        t.fused_prep = 1; t.qn = bf(w.qn); t.kn = bf(w.kn); t.rope = e->rope;
+        t.k_write = reinterpret_cast<bf16_raw*>(a->k_write); t.v_write = reinterpret_cast<bf16_raw*>(a->v_write);
+        t.n_layers = L; t.append = append;
+        t.row_ssq = reinterpret_cast<const float*>(e->lk_state);   // the q/k/v rows still lack their norm's scale
+        t.merged = e->attn;                                        // the last block of a (sequence, kv head) merges its splits
+        t.merge_count = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(e->lk_state) + LK_STATE_MERGE_OFFSET);
+        LAUNCH(launch_attn_split(t, B, st));
+        LAUNCH(launch_layer_tc(e, l + 1 < L ? LK_MODE_MID : LK_MODE_LAST, l, B, st));
+    }
+    for (int l = 0; !lk && l < L; ++l) {
         GemvArgs g{};
         // qkv = rms(x, ln1) @ [wq; wk; wv]^T
         if (tc) {
@@ -438,8 +460,9 @@ extern "C" int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream) {
             return fail(e, Q3_ERR_UNSUPPORTED, "q3_decode: the persistent kernel does not serve batch %d at length %d", a->batch, a->max_len);
         return persist_decode(e, a, st);
     }
-    if (path != Q3_F_PATH_LAYERED) return fail(e, Q3_ERR_INVALID, "q3_decode: unknown path flag 0x%x", path);
-    if (!(a->flags & Q3_F_GRAPH)) return decode_layered(e, a, st);
+    if (path != Q3_F_PATH_LAYERED && path != Q3_F_PATH_FUSED) return fail(e, Q3_ERR_INVALID, "q3_decode: unknown path flag 0x%x", path);
+    const bool layer_kernel = path == Q3_F_PATH_FUSED;
+    if (!(a->flags & Q3_F_GRAPH)) return decode_layered(e, a, st, 3, nullptr, layer_kernel);
 
     // graph replay: the key is the argument block with max_len replaced by what it determines in the captured
     // launches: the split count and the padded chunk length (which also sizes the attention kernel's shared memory)
@@ -462,12 +485,12 @@ extern "C" int q3_decode(q3_engine* e, const q3_decode_args* a, void* stream) {
         e->launches += hit->launches;
         return Q3_OK;
     }
-    if (hit->seen++ == 0) return decode_layered(e, a, st);   // first use: plain launches
+    if (hit->seen++ == 0) return decode_layered(e, a, st, 3, nullptr, layer_kernel);   // first use: plain launches
     const int64_t before = e->launches;
     // capture on the engine's own stream (the legacy default stream cannot be captured); nothing runs during capture
     cudaStream_t cs = static_cast<cudaStream_t>(e->capture_stream);
     CU(e, cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
-    const int rc = decode_layered(e, a, cs);
+    const int rc = decode_layered(e, a, cs, 3, nullptr, layer_kernel);
     cudaGraph_t graph = nullptr;
     const cudaError_t end = cudaStreamEndCapture(cs, &graph);
     if (rc != Q3_OK) { if (graph) cudaGraphDestroy(graph); return rc; }

@@ -42,6 +42,7 @@ struct q3_engine {
     float* gate;        // [cap, 3072]
     float* up;          // [cap, 3072]
     float* logits_tc;   // [max_batch, vocab] when the caller passes no logits buffer
+    void* lk_state;     // the layer kernel's row sums of squares and barrier words (q3_layer_tc.h)
     // persistent kernel geometry
     int p_grid, p_threads, p_smem;
     void* p_state;  // owned by q3_persist.cu
@@ -72,7 +73,10 @@ struct PrefillCtx {
     const void* vcache;
     long long layer_stride;
 };
-int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes = 3, const PrefillCtx* prompt = nullptr);
+// layer_kernel: decode batches the persistent layer kernel serves take it (two launches per layer); false keeps one
+// launch per phase
+int decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, int tc_planes = 3, const PrefillCtx* prompt = nullptr,
+                   bool layer_kernel = false);
 cudaError_t launch_prefill_attn_tc(const float* qkv, const void* kcache_layer, const void* vcache_layer, int cap_rows, void* planes,
                                    int plane_rows, int nsplit, int T, uint32_t* status, cudaStream_t st);
 }  // namespace q3

@@ -317,7 +317,8 @@ __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
         if (warp < 4) {   // warp r: q head 2g, q head 2g + 1, k, v; four dims a lane
             const float* src = warp == 0 ? q0p : warp == 1 ? q1p : warp == 2 ? knp : vnp;
             const float4 v4 = *reinterpret_cast<const float4*>(src + lane * 4);
-            float v[4] = {v4.x, v4.y, v4.z, v4.w};
+            const float rs = a.row_ssq ? rsqrtf(a.row_ssq[b] / (float)HIDDEN + EPS) : 1.f;
+            float v[4] = {v4.x * rs, v4.y * rs, v4.z * rs, v4.w * rs};
             if (warp < 3) {
                 float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
 #pragma unroll
@@ -487,6 +488,30 @@ __global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
         float* out = a.part + (((size_t)b * Q_HEADS + 2 * g + hh) * a.n_splits + sp) * ATTN_PART_STRIDE;
         if (d == 0) { out[0] = hh ? M1 : M0; out[1] = L; }   // an empty chunk publishes (-inf, 0, 0)
         out[4 + d] = o;
+    }
+    if (a.merged != nullptr) {
+        // the last block of this (sequence, kv head) to get here merges all splits of its two heads: no merge launch
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(a.merge_count + b * KV_HEADS + g, 1) == a.n_splits - 1;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const int hh = tid >> 7, d = tid & 127;
+            const float* p = a.part + ((size_t)b * Q_HEADS + 2 * g + hh) * a.n_splits * ATTN_PART_STRIDE;
+            float M = -INFINITY;
+            for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, __ldcg(p + s * ATTN_PART_STRIDE));
+            float L = 0.f, o = 0.f;
+            for (int s = 0; s < a.n_splits; ++s) {
+                const float ms = __ldcg(p + s * ATTN_PART_STRIDE);
+                const float w = (ms > -INFINITY) ? expf(ms - M) : 0.f;
+                L = fmaf(__ldcg(p + s * ATTN_PART_STRIDE + 1), w, L);
+                o = fmaf(__ldcg(p + s * ATTN_PART_STRIDE + 4 + d), w, o);
+            }
+            a.merged[(size_t)b * Q_DIM + (2 * g + hh) * HEAD_DIM + d] = o / L;
+            if (tid == 0) a.merge_count[b * KV_HEADS + g] = 0;
+        }
     }
 }
 
@@ -742,17 +767,31 @@ cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st) 
     return launch_chain(head_prep_kernel, dim3((Q_HEADS + KV_HEADS) / 8, batch), dim3(256), 0, st, a);
 }
 
+// the split kernel: tensor-core streaming kernel (q3_attn_mma.cu), or the CUDA-core one above when built with Q3_ATTN_SPLIT
+static cudaError_t launch_split(const AttnArgs& a, int batch, cudaStream_t st) {
+#ifdef Q3_ATTN_SPLIT
+    return launch_chain(attn_split_kernel, dim3(a.n_splits, KV_HEADS, batch), dim3(256), (size_t)2 * a.chunk_pad * sizeof(float), st, a);
+#else
+    return launch_attn_mma(a, batch, st);
+#endif
+}
+
+cudaError_t launch_attn_split(const AttnArgs& a, int batch, cudaStream_t st) {
+    if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.chunk_pad > ATTN_CHUNK_MAX || !a.fused_prep) return cudaErrorInvalidValue;
+    return launch_split(a, batch, st);
+}
+
 // split attention whose merge writes the bf16 planes of the Wo GEMM's input directly
 cudaError_t launch_attn_planes(const AttnArgs& a, bf16_raw* planes, int plane_rows, int nsplit, int batch, cudaStream_t st) {
     if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.chunk_pad > ATTN_CHUNK_MAX) return cudaErrorInvalidValue;
-    cudaError_t e = launch_chain(attn_split_kernel, dim3(a.n_splits, KV_HEADS, batch), dim3(256), (size_t)2 * a.chunk_pad * sizeof(float), st, a);
+    cudaError_t e = launch_split(a, batch, st);
     if (e != cudaSuccess) return e;
     return launch_chain(attn_merge_planes_kernel, dim3(Q_HEADS, plane_rows), dim3(128), 0, st, a.part, a.n_splits, planes, plane_rows, nsplit, batch);
 }
 
 cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st) {
     if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.chunk_pad > ATTN_CHUNK_MAX) return cudaErrorInvalidValue;
-    cudaError_t e = launch_chain(attn_split_kernel, dim3(a.n_splits, KV_HEADS, batch), dim3(256), (size_t)2 * a.chunk_pad * sizeof(float), st, a);
+    cudaError_t e = launch_split(a, batch, st);
     if (e != cudaSuccess) return e;
     attn_merge_kernel<<<dim3(Q_HEADS, batch), 128, 0, st>>>(a.part, a.n_splits, attn_out);
     return cudaGetLastError();

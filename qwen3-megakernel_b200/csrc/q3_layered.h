@@ -68,6 +68,13 @@ struct AttnArgs {
     bf16_raw* v_write;
     int n_layers, append;
     int len_bound;                    // n_splits * chunk_pad - 1 and the RoPE table's last row, whichever is smaller
+    // fused_prep only: per-sequence sums of squares of the vector the q/k/v projections were taken of, when the producer
+    // left the RMS norm's scale rsqrt(ssq / 1024 + eps) to this kernel (the layer kernel does); nullptr: already applied
+    const float* row_ssq;
+    // the block that finishes a (sequence, kv head) last merges its splits into merged[b, 2048] (nullptr: a separate
+    // merge kernel follows); merge_count[b * 8 + g] counts the arrivals and is left at zero
+    float* merged;
+    int* merge_count;
 };
 
 cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStream_t st);
@@ -77,6 +84,8 @@ cudaError_t launch_embed(const long long* token, const bf16_raw* embed, int voca
 cudaError_t launch_argmax_final(const float* pval, const int* pidx, int nblk, long long* next_token, int* seq_len, int append, int batch, cudaStream_t st);
 cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st);
 cudaError_t launch_attn(const AttnArgs& a, float* attn_out, int batch, cudaStream_t st);
+cudaError_t launch_attn_split(const AttnArgs& a, int batch, cudaStream_t st);   // the split kernel alone: partials only
+cudaError_t launch_attn_mma(const AttnArgs& a, int batch, cudaStream_t st);     // q3_attn_mma.cu: the split kernel on mma.sync + cp.async
 cudaError_t launch_attn_planes(const AttnArgs& a, bf16_raw* planes, int plane_rows, int nsplit, int batch, cudaStream_t st);
 cudaError_t launch_silu_planes(const float* g, const float* u, bf16_raw* planes, int plane_rows, int nsplit, int n_tok, cudaStream_t st);
 // up to two fp32 buffers whose first n_tok rows act_split clears on the side (the outputs of the split-K GEMM that follows)

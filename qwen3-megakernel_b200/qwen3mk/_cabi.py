@@ -7,7 +7,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libq3mk.so"
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NOT_RESIDENT, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 0, -1, -2, -3, -4, -5
-F_APPEND_KV, F_PATH_AUTO, F_PATH_LAYERED, F_PATH_PERSIST, F_GRAPH = 0x1, 0x0, 0x10, 0x20, 0x100
+F_APPEND_KV, F_PATH_AUTO, F_PATH_LAYERED, F_PATH_PERSIST, F_PATH_FUSED, F_GRAPH = 0x1, 0x0, 0x10, 0x20, 0x30, 0x100
 
 # every symbol include/q3mk.h declares
 SYMBOLS = ("q3_create", "q3_destroy", "q3_set_weights", "q3_invalidate_weights", "q3_set_rope", "q3_tp_export", "q3_tp_attach", "q3_decode", "q3_decode_noalloc", "q3_noalloc_status", "q3_linear_tc", "q3_prefill", "q3_sample", "q3_status",

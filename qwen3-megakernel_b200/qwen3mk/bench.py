@@ -99,7 +99,7 @@ def gpu_info(device) -> dict:
 
 
 def batched(device, w: dict, batch: int = 64, context: int = 1024, steps: int = 20, warmup: int = 3, seed: int = 0,
-            lens: list[int] | None = None, graph: bool = True) -> dict:
+            lens: list[int] | None = None, graph: bool = True, path: str = "auto") -> dict:
     """Microseconds per decode step of `batch` sequences with `context` cached positions each (or the given `lens`):
     seeded random caches and tokens, one engine on `device`, CUDA-event time of `steps` back-to-back launches.
     Also returns the kernels launched per step and the algorithmic HBM bytes of a step (every weight once, the norm
@@ -112,7 +112,7 @@ def batched(device, w: dict, batch: int = 64, context: int = 1024, steps: int = 
     g = torch.Generator(device=dev).manual_seed(seed)
     cache = lambda n: (torch.randn(layers, n, KV_HEADS, HEAD_DIM, device=dev, generator=g) * 0.1).to(torch.bfloat16)
     kcs, vcs = [cache(n) for n in lens], [cache(n) for n in lens]
-    mk = Megakernel(dev, max_batch=batch, layers=layers, vocab=vocab, max_positions=max(8192, max(lens) + 8))
+    mk = Megakernel(dev, max_batch=batch, layers=layers, vocab=vocab, max_positions=max(8192, max(lens) + 8), path=path)
     toks = torch.randint(0, vocab, (batch,), device=dev, generator=g)
     mk.bind_sequences(w, toks, SeqTable(kcs, vcs), graph=graph)
     for _ in range(warmup):

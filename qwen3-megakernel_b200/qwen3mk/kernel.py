@@ -130,7 +130,8 @@ class Megakernel:
     path: fixed inputs, outputs overwritten by every launch, no synchronisation.
     `bind_sequences` is the batched / growing-cache form of `bind`.
 
-    path: "auto" (persistent kernel when it serves the batch, else layered), "layered" or "persist".
+    path: "auto" (persistent kernel when it serves the batch, else layered), "layered" (one launch per phase), "fused" (layered, with
+    one persistent kernel for everything between two attentions for batches of 4..64; opt-in) or "persist".
     """
 
     def __init__(self, device=None, *, max_batch: int = 1, layers: int = LAYERS, vocab: int = VOCAB,
@@ -149,7 +150,8 @@ class Megakernel:
         major, minor = torch.cuda.get_device_capability(self.device)
         self.arch = f"sm_{major}{minor}"
         self.layers, self.vocab, self.max_batch = int(layers), int(vocab), int(max_batch)
-        self._path_flag = {"auto": _cabi.F_PATH_AUTO, "layered": _cabi.F_PATH_LAYERED, "persist": _cabi.F_PATH_PERSIST}[path]
+        self._path_flag = {"auto": _cabi.F_PATH_AUTO, "layered": _cabi.F_PATH_LAYERED, "persist": _cabi.F_PATH_PERSIST,
+                           "fused": _cabi.F_PATH_FUSED}[path]
         cfg = _cabi.Config(self.layers, self.vocab, self.max_batch, int(max_tokens), int(grid_limit), int(wait_limit_us))
         h = ctypes.c_void_p()
         rc = self.lib.q3_create(self.device.index or 0, ctypes.byref(cfg), ctypes.byref(h))

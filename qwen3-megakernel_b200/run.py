@@ -191,7 +191,7 @@ def cmd_batch(args) -> int:
         lens = torch.randint(128, ctx + 1, (B,), generator=torch.Generator().manual_seed(args.seed)).tolist()
     if world > 1:
         dist.barrier()
-    res = bench_mod.batched(dev, w, B, ctx, steps=args.steps, seed=args.seed, lens=lens, graph=not args.plain)
+    res = bench_mod.batched(dev, w, B, ctx, steps=args.steps, seed=args.seed, lens=lens, graph=not args.plain, path=args.path)
     us = res["us_per_step"]
     if world > 1:
         us = replicas.max_over_ranks(us, dev)
@@ -274,6 +274,8 @@ def main(argv=None) -> int:
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--plain", action="store_true", help="plain launches instead of CUDA-graph replay")
     p.add_argument("--ragged", action="store_true", help="cache lengths drawn uniformly from [128, --context]")
+    p.add_argument("--path", default="auto", choices=["auto", "layered", "fused"],
+                   help="fused: the persistent layer kernel between the attention launches instead of one launch per phase")
     p = sub.add_parser("prefill")
     p.add_argument("--tokens", type=int, default=2048)
     p.add_argument("--reps", type=int, default=5)

@@ -127,10 +127,11 @@ def test_persist_reports_a_cache_longer_than_the_host_said(oracle):
     mk.status()
 
 
-@pytest.mark.parametrize("path", ["layered", "auto"])
+@pytest.mark.parametrize("path", ["layered", "auto", "fused"])
 @pytest.mark.parametrize("batch", [2, 3, 4, 5, 8, 9, 33, 64])
 def test_ragged_batch(oracle, path, batch):
-    """Batches of 4 or more run their projections as tcgen05 GEMMs over three bf16 planes of the activations."""
+    """Batches of 4 or more run their projections as tcgen05 GEMMs over three bf16 planes of the activations; "fused" runs
+    everything between two attentions of such a batch in one persistent kernel."""
     from qwen3mk.kernel import SeqTable
 
     shp = oracle.Shape(layers=2, vocab=2048)
