@@ -243,11 +243,10 @@ static int chunk_pad_for(int max_len, int ns) { return (((max_len + 1 + ns - 1) 
 static int splits_for(const q3_engine* e, int batch, int max_len) {
     const int n = max_len + 1;
     int by_len = (n + 31) / 32;                                   // at least 32 positions per split
-    // Small batches: about two blocks per SM (more splits only add merge work: batch 8 x 1024 positions, 5 / 10 / 21
-    // splits 1879 / 1918 / 2048 us per step).  Batches that fill the GPU on their own: three blocks of the split kernel
-    // fit an SM, and about three waves of them even out the last, partly filled one (batch 64 x 1024 positions,
-    // 1 / 2 / 3 / 6 / 7 splits: 3690 / 3437 / 3439 / 3551 / 3713 us per step).
-    const int fill_blocks = (KV_HEADS * batch >= e->sm_count ? 9 : 2) * e->sm_count;
+    // Small batches: about two blocks per SM (more splits only add merge work).  Batches whose (sequence, kv head)
+    // pairs fill the GPU on their own: as few splits as possible, every block pays a prologue and an epilogue that long
+    // runs amortise (batch 64 x 1024 positions, 1 / 2 / 3 / 4 splits: 2524 / 2623 / 2691 / 2716 us per step).
+    const int fill_blocks = (KV_HEADS * batch >= e->sm_count ? 3 : 2) * e->sm_count;
     int by_fill = (fill_blocks + KV_HEADS * batch - 1) / (KV_HEADS * batch);
     int s = by_len < by_fill ? by_len : by_fill;
     if (s < 1) s = 1;

@@ -1,5 +1,4 @@
-// Split attention of a decode step on the tensor cores: one block per (split, kv head, sequence), like the CUDA-core
-// kernel it replaces (attn_split_kernel), but the K and V rows of the chunk stream through shared memory by cp.async
+// Split attention of a decode step on the tensor cores: one block per (split, kv head, sequence).  The K and V rows of the chunk stream through shared memory by cp.async
 // (16-byte copies, three stages of 16 positions per warp, no register staging) and both products run as mma.sync
 // m16n8k16 with the POSITIONS as the M dimension:
 //
@@ -8,11 +7,11 @@
 //
 // Only two of the eight head columns are real (the GQA pair that shares the K/V stream); the rest is padding the tensor
 // pipe does not mind, because the kernel is bound by bytes: the point of the tensor cores here is the INSTRUCTION count.
-// The CUDA-core kernel spends about 26 instructions per 256-byte row (unpack, 32 FMAs, shuffles) and tops out near 4 TB/s
+// The CUDA-core kernel this replaced spent about 26 instructions per 256-byte row (unpack, 32 FMAs, shuffles) and topped out near 4 TB/s
 // on issue slots; this one spends about 8.  Accuracy: Q and P enter as two bf16 planes each (hi + lo), so scores and
 // outputs carry fp32-grade inputs against the exact bf16 K and V; the softmax runs in fp32 on base-2 exponentials
 // (log2 e is folded into the scale of Q).  Each warp owns a contiguous run of the chunk's positions with its own running
-// maximum; the four warps and the new token's fp32 row are combined at the end, and the partial (max, sum, o[128]) per
+// maximum; the warps and the new token's fp32 row are combined at the end, and the partial (max, sum, o[128]) per
 // head goes out in the format of the split kernel, so the merge (fused or separate) is unchanged.
 //
 // Replaces the per-head score and value loops of the reference's attention phase for batches and long caches
@@ -21,13 +20,15 @@
 
 namespace q3 {
 
-constexpr int AM_WARPS = 4;
-constexpr int AM_THREADS = AM_WARPS * 32;
+// Two shapes of block.  Four warps (96 KB of stages, two blocks per SM) when the (sequence, kv head) pairs alone fill the
+// GPU: long runs per warp, few blocks.  Two warps (48 KB, four blocks per SM) for small batches, where the launch is
+// bound by latency and more, shorter blocks help.  Measured per decode step (28 launches): batch 64 x 1024 positions
+// 2524 us with four warps and one split (2691 with three splits, 2705 with eight warps), batch 8 x 1024 positions
+// 1174 us with two warps against 1232 with four.
 constexpr int AM_TILE = 16;                        // positions per stage
 constexpr int AM_STAGES = 3;
 constexpr int AM_HALF = AM_TILE * 256;             // bytes of a stage's K (or V) tile: 16 rows of 128 bf16
 constexpr int AM_STAGE = 2 * AM_HALF;
-constexpr size_t AM_SMEM = (size_t)AM_WARPS * AM_STAGES * AM_STAGE;   // 96 KB: two blocks per SM
 constexpr float AM_LOG2E = 1.4426950408889634f, AM_LN2 = 0.6931471805599453f;
 
 __device__ __forceinline__ uint32_t am_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -51,7 +52,9 @@ __device__ __forceinline__ uint32_t am_transpose(uint32_t w) {   // 8 x 8 matrix
     return d;
 }
 
-__global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_kernel(const AttnArgs a) {
+template <int AM_WARPS>
+__global__ void __launch_bounds__(AM_WARPS * 32, 8 / AM_WARPS) attn_mma_kernel(const AttnArgs a) {
+    constexpr int AM_THREADS = AM_WARPS * 32;
     pdl_launch();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char am_raw[];
@@ -100,19 +103,19 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_kernel(const AttnArgs 
     for (int i = 0; i < AM_STAGES - 1; ++i) issue(i);
 
     // ---- the two q heads, the k row and the v row of the new token: as prepared by head_prep_kernel, or prepared here ----
+    for (int role = warp; role < 4; role += AM_WARPS) {   // a warp per vector: q head 2g, q head 2g + 1, k, v; four dims a lane
     if (a.fused_prep) {
-        // warp r: q head 2g, q head 2g + 1, k, v; four dims a lane
-        const float* src = warp == 0 ? qkv + (2 * g) * HEAD_DIM : warp == 1 ? qkv + (2 * g + 1) * HEAD_DIM
-                         : warp == 2 ? qkv + Q_DIM + g * HEAD_DIM : qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
+        const float* src = role == 0 ? qkv + (2 * g) * HEAD_DIM : role == 1 ? qkv + (2 * g + 1) * HEAD_DIM
+                         : role == 2 ? qkv + Q_DIM + g * HEAD_DIM : qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
         const float4 v4 = *reinterpret_cast<const float4*>(src + lane * 4);
         const float rs = a.row_ssq ? rsqrtf(a.row_ssq[b] / (float)HIDDEN + EPS) : 1.f;
         float v[4] = {v4.x * rs, v4.y * rs, v4.z * rs, v4.w * rs};
-        if (warp < 3) {
+        if (role < 3) {
             float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float r = rsqrtf(ss / (float)HEAD_DIM + EPS);
-            const bf16_raw* gain = (warp < 2 ? a.qn : a.kn) + (size_t)a.layer * HEAD_DIM + lane * 4;
+            const bf16_raw* gain = (role < 2 ? a.qn : a.kn) + (size_t)a.layer * HEAD_DIM + lane * 4;
             const float* tab = a.rope + (size_t)len * HEAD_DIM;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -123,23 +126,24 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_kernel(const AttnArgs 
                 v[i] = nrm * tab[d] + rot * tab[64 + d];
             }
         }
-        *reinterpret_cast<float4*>(&s_new[warp][lane * 4]) = make_float4(v[0], v[1], v[2], v[3]);
-        if (warp >= 2 && sp == 0) {   // one block per (sequence, kv head) stores the new rows, rounded to bf16
-            bf16_raw* wr = warp == 2 ? a.k_write : a.v_write;
+        *reinterpret_cast<float4*>(&s_new[role][lane * 4]) = make_float4(v[0], v[1], v[2], v[3]);
+        if (role >= 2 && sp == 0) {   // one block per (sequence, kv head) stores the new rows, rounded to bf16
+            bf16_raw* wr = role == 2 ? a.k_write : a.v_write;
             const size_t wofs = (((size_t)b * a.n_layers + a.layer) * KV_HEADS + g) * HEAD_DIM + lane * 4;
             uint2 pk;
             pk.x = (uint32_t)f_to_bf(v[0]) | ((uint32_t)f_to_bf(v[1]) << 16);
             pk.y = (uint32_t)f_to_bf(v[2]) | ((uint32_t)f_to_bf(v[3]) << 16);
             if (wr) *reinterpret_cast<uint2*>(wr + wofs) = pk;
             if (a.append) {
-                bf16_raw* cache = reinterpret_cast<bf16_raw*>(warp == 2 ? a.seq_k[b] : a.seq_v[b]);
+                bf16_raw* cache = reinterpret_cast<bf16_raw*>(role == 2 ? a.seq_k[b] : a.seq_v[b]);
                 *reinterpret_cast<uint2*>(cache + (size_t)a.layer * a.seq_layer_stride[b] + (size_t)len * KV_DIM + g * HEAD_DIM + lane * 4) = pk;
             }
         }
     } else {
-        const float* src = warp == 0 ? qkv + (2 * g) * HEAD_DIM : warp == 1 ? qkv + (2 * g + 1) * HEAD_DIM
-                         : warp == 2 ? qkv + Q_DIM + g * HEAD_DIM : qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
-        *reinterpret_cast<float4*>(&s_new[warp][lane * 4]) = *reinterpret_cast<const float4*>(src + lane * 4);
+        const float* src = role == 0 ? qkv + (2 * g) * HEAD_DIM : role == 1 ? qkv + (2 * g + 1) * HEAD_DIM
+                         : role == 2 ? qkv + Q_DIM + g * HEAD_DIM : qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
+        *reinterpret_cast<float4*>(&s_new[role][lane * 4]) = *reinterpret_cast<const float4*>(src + lane * 4);
+    }
     }
     __syncthreads();
 
@@ -250,7 +254,7 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_kernel(const AttnArgs 
     __syncthreads();
     {
         // thread d: both heads; combine the warps' partials and the new token under one maximum
-        const int d = tid;
+        for (int d = tid; d < HEAD_DIM; d += AM_THREADS)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             float M = has_new ? s_ns[hh] : -INFINITY;
@@ -281,7 +285,7 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_kernel(const AttnArgs 
         __syncthreads();
         if (s_last) {
             __threadfence();
-            const int d = tid;
+            for (int d = tid; d < HEAD_DIM; d += AM_THREADS)
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const float* p = a.part + ((size_t)b * Q_HEADS + 2 * g + hh) * a.n_splits * ATTN_PART_STRIDE;
@@ -303,18 +307,21 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_kernel(const AttnArgs 
 
 cudaError_t launch_attn_mma(const AttnArgs& a, int batch, cudaStream_t st) {
     if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.n_splits < 1) return cudaErrorInvalidValue;
-    {
-        static bool attr_set[64] = {};
-        int dev = 0;
-        cudaError_t e = cudaGetDevice(&dev);
-        if (e != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-        if (!attr_set[dev]) {   // (a benign race between host threads: the attribute is set to the same value)
-            e = cudaFuncSetAttribute(attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AM_SMEM);
-            if (e != cudaSuccess) return e;
-            attr_set[dev] = true;
-        }
+    static int sm_count[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!sm_count[dev]) {   // (a benign race between host threads: the same values are written)
+        constexpr size_t big = (size_t)4 * AM_STAGES * AM_STAGE, small = (size_t)2 * AM_STAGES * AM_STAGE;
+        if ((e = cudaFuncSetAttribute(attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big)) != cudaSuccess) return e;
+        if ((e = cudaFuncSetAttribute(attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small)) != cudaSuccess) return e;
+        int n = 0;
+        if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+        sm_count[dev] = n;
     }
-    return launch_chain(attn_mma_kernel, dim3(a.n_splits, KV_HEADS, batch), dim3(AM_THREADS), AM_SMEM, st, a);
+    const dim3 grid(a.n_splits, KV_HEADS, batch);
+    if (KV_HEADS * batch >= sm_count[dev]) return launch_chain(attn_mma_kernel<4>, grid, dim3(128), (size_t)4 * AM_STAGES * AM_STAGE, st, a);
+    return launch_chain(attn_mma_kernel<2>, grid, dim3(64), (size_t)2 * AM_STAGES * AM_STAGE, st, a);
 }
 
 }  // namespace q3

@@ -8,7 +8,7 @@
 // Phases per layer (reference: csrc/qwen3_step.cu:531-772, semantics qwen3mk/reference.py:61-82):
 //   gemv<RMS, STORE>      qkv  = rms(x, ln1) @ [wq; wk; wv]^T
 //   head_prep             q, k = rope(rms_head(.)), K/V rows written (bf16), optional cache append
-//   attn_split, attn_merge  softmax(q K^T / sqrt(128)) V over cached positions + the new one
+//   attn_merge              combines the splits of the attention kernel (q3_attn_mma.cu)
 //   gemv<RESID>           x   += attn @ wo^T
 //   gemv<RMS, SILU>       hid  = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
 //   gemv<RESID>           x   += hid @ wd^T
@@ -265,256 +265,9 @@ __global__ void __launch_bounds__(256) head_prep_kernel(const HeadPrepArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// attn_split: one block per (split, kv-head, sequence).  Both q heads of the GQA pair share the
-// K/V stream.  A quarter-warp owns one position at a time: lane `sub` of the quarter holds head
-// dims [8 sub, 8 sub + 8) and [64 + 8 sub, +8), i.e. two 16-byte units of the 256-byte row.
-// Cached rows are bf16; the new token's row (position seq_len[b]) is read in fp32 from `qkv`,
-// unrounded, as the reference does (qwen3mk/reference.py:74-78).
-// Output per (b, head, split): running max m, sum l, unnormalised o[128].
+// attention of a decode step: the split kernel lives in q3_attn_mma.cu (one block per (split, kv head, sequence); output
+// per (b, head, split): running max m, sum l, unnormalised o[128]); the merges follow here.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
-    f[0] = bf_lo(u.x); f[1] = bf_hi(u.x); f[2] = bf_lo(u.y); f[3] = bf_hi(u.y);
-    f[4] = bf_lo(u.z); f[5] = bf_hi(u.z); f[6] = bf_lo(u.w); f[7] = bf_hi(u.w);
-}
-
-// Two passes over the block's chunk of positions, both bound by bytes in flight rather than arithmetic, so both keep
-// several rows per thread requested ahead of their use and the kernel keeps its registers low enough for three
-// blocks per SM:
-//   1. scores: a quarter-warp per position (K row = 2 x 16 bytes a lane), both GQA heads against the same row;
-//      scores go to shared memory, the maxima are reduced over the block;
-//   2. P.V: a warp per position, four dims a lane (V row = 8 bytes a lane): every lane forms the same two
-//      probabilities from the shared scores, so nothing crosses lanes; eight per-warp sums are added at the end.
-// The new token's own K/V rows are fp32 in `qkv` (not yet rounded into the cache) and are handled by warp 0.
-__global__ void __launch_bounds__(256, 3) attn_split_kernel(const AttnArgs a) {
-    pdl_launch();
-    pdl_wait();
-    extern __shared__ __align__(16) float attn_sc[];          // [2][chunk_pad] scores of the chunk
-    __shared__ float s_red[2][8], s_l[8][2];
-    __shared__ __align__(16) float s_o[8][2][HEAD_DIM];       // 8 KB
-
-    const int sp = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int quarter = lane >> 3, sub = lane & 7;
-    const int len = min(max(a.seq_len[b], 0), a.len_bound);
-    const int n = len + 1;
-    const int chunk = (n + a.n_splits - 1) / a.n_splits;
-    const int p0 = sp * chunk, p1 = min(min(p0 + chunk, n), p0 + a.chunk_pad);
-    const int pc = min(p1, len);                              // cached positions of the chunk: [p0, pc)
-    const bool has_new = p0 <= len && len < p1;               // the new token's row belongs to this chunk
-    float* sc0 = attn_sc;
-    float* sc1 = attn_sc + a.chunk_pad;
-
-    const float* qkv = a.qkv + (size_t)b * QKV_DIM;
-    const bf16_raw* kbase = reinterpret_cast<const bf16_raw*>(a.seq_k[b]) + (size_t)a.layer * a.seq_layer_stride[b] + g * HEAD_DIM;
-    const bf16_raw* vbase = reinterpret_cast<const bf16_raw*>(a.seq_v[b]) + (size_t)a.layer * a.seq_layer_stride[b] + g * HEAD_DIM;
-    // the two q heads, the k row and the v row of the new token: as prepared by head_prep_kernel, or prepared here
-    __shared__ __align__(16) float s_new[4][HEAD_DIM];
-    const float* q0p = qkv + (2 * g) * HEAD_DIM;
-    const float* q1p = qkv + (2 * g + 1) * HEAD_DIM;
-    const float* knp = qkv + Q_DIM + g * HEAD_DIM;
-    const float* vnp = qkv + Q_DIM + KV_DIM + g * HEAD_DIM;
-    if (a.fused_prep) {
-        if (warp < 4) {   // warp r: q head 2g, q head 2g + 1, k, v; four dims a lane
-            const float* src = warp == 0 ? q0p : warp == 1 ? q1p : warp == 2 ? knp : vnp;
-            const float4 v4 = *reinterpret_cast<const float4*>(src + lane * 4);
-            const float rs = a.row_ssq ? rsqrtf(a.row_ssq[b] / (float)HIDDEN + EPS) : 1.f;
-            float v[4] = {v4.x * rs, v4.y * rs, v4.z * rs, v4.w * rs};
-            if (warp < 3) {
-                float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                const float r = rsqrtf(ss / (float)HEAD_DIM + EPS);
-                const bf16_raw* gain = (warp < 2 ? a.qn : a.kn) + (size_t)a.layer * HEAD_DIM + lane * 4;
-                const float* tab = a.rope + (size_t)len * HEAD_DIM;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float nrm = (v[i] * r) * bf_to_f(gain[i]);
-                    const float partner = __shfl_xor_sync(0xffffffffu, nrm, 16);   // dim d +- 64 sits 16 lanes away
-                    const float rot = (lane < 16) ? -partner : partner;
-                    const int d = (lane * 4 + i) & 63;
-                    v[i] = nrm * tab[d] + rot * tab[64 + d];
-                }
-            }
-            *reinterpret_cast<float4*>(&s_new[warp][lane * 4]) = make_float4(v[0], v[1], v[2], v[3]);
-            if (warp >= 2 && sp == 0) {   // one block per (sequence, kv head) stores the new rows, rounded to bf16
-                bf16_raw* wr = warp == 2 ? a.k_write : a.v_write;
-                const size_t wofs = (((size_t)b * a.n_layers + a.layer) * KV_HEADS + g) * HEAD_DIM + lane * 4;
-                uint2 pk;
-                pk.x = (uint32_t)f_to_bf(v[0]) | ((uint32_t)f_to_bf(v[1]) << 16);
-                pk.y = (uint32_t)f_to_bf(v[2]) | ((uint32_t)f_to_bf(v[3]) << 16);
-                if (wr) *reinterpret_cast<uint2*>(wr + wofs) = pk;
-                if (a.append) {
-                    bf16_raw* cache = reinterpret_cast<bf16_raw*>(warp == 2 ? a.seq_k[b] : a.seq_v[b]);
-                    *reinterpret_cast<uint2*>(cache + (size_t)a.layer * a.seq_layer_stride[b] + (size_t)len * KV_DIM + g * HEAD_DIM + lane * 4) = pk;
-                }
-            }
-        }
-        __syncthreads();
-        q0p = s_new[0]; q1p = s_new[1]; knp = s_new[2]; vnp = s_new[3];
-    }
-
-    // ---------------------------------------------------------------- pass 1: scores
-    float tmax0 = -INFINITY, tmax1 = -INFINITY;
-    {
-        float q[2][16];
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            const float* qp = hh ? q1p : q0p;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                q[hh][i] = qp[sub * 8 + i] * ATTN_SCALE;
-                q[hh][8 + i] = qp[64 + sub * 8 + i] * ATTN_SCALE;
-            }
-        }
-        // position of this quarter-warp in iteration `it`: p0 + 32 it + 4 warp + quarter
-        auto request = [&](int it, uint4& k0, uint4& k1) {
-            const int p = p0 + 32 * it + 4 * warp + quarter;
-            const bool live = p < pc;
-            const uint4* kr = reinterpret_cast<const uint4*>(kbase + (size_t)(live ? p : 0) * KV_DIM);
-            ld_row16(k0, kr + sub, live); ld_row16(k1, kr + 8 + sub, live);
-        };
-        auto score = [&](int it, const uint4& k0, const uint4& k1) {
-            const int p = p0 + 32 * it + 4 * warp + quarter;
-            float kf[16];
-            unpack8(k0, kf); unpack8(k1, kf + 8);
-            float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { s0 = fmaf(q[0][i], kf[i], s0); s1 = fmaf(q[1][i], kf[i], s1); }
-#pragma unroll
-            for (int o = 1; o <= 4; o <<= 1) {
-                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            }
-            if (p < pc) {
-                tmax0 = fmaxf(tmax0, s0); tmax1 = fmaxf(tmax1, s1);
-                if (sub == 0) { sc0[p - p0] = s0; sc1[p - p0] = s1; }
-            }
-        };
-        const int iters = (pc - p0 + 31) / 32;                // block-uniform
-        uint4 ka0, ka1, kb0, kb1, kc0, kc1, kd0, kd1;         // four iterations of rows in flight
-        request(0, ka0, ka1);
-        request(1, kb0, kb1);
-        request(2, kc0, kc1);
-        for (int it = 0; it < iters; it += 4) {
-            request(it + 3, kd0, kd1);
-            score(it, ka0, ka1);
-            if (it + 1 >= iters) break;
-            request(it + 4, ka0, ka1);
-            score(it + 1, kb0, kb1);
-            if (it + 2 >= iters) break;
-            request(it + 5, kb0, kb1);
-            score(it + 2, kc0, kc1);
-            if (it + 3 >= iters) break;
-            request(it + 6, kc0, kc1);
-            score(it + 3, kd0, kd1);
-        }
-        if (has_new && warp == 0) {   // q . k_new in fp32, four dims a lane
-            const float4 kn = *reinterpret_cast<const float4*>(knp + lane * 4);
-            const float4 q0 = *reinterpret_cast<const float4*>(q0p + lane * 4);
-            const float4 q1 = *reinterpret_cast<const float4*>(q1p + lane * 4);
-            float s0 = (q0.x * kn.x + q0.y * kn.y + q0.z * kn.z + q0.w * kn.w) * ATTN_SCALE;
-            float s1 = (q1.x * kn.x + q1.y * kn.y + q1.z * kn.z + q1.w * kn.w) * ATTN_SCALE;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            }
-            tmax0 = fmaxf(tmax0, s0); tmax1 = fmaxf(tmax1, s1);
-            if (lane == 0) { sc0[len - p0] = s0; sc1[len - p0] = s1; }
-        }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, o));
-        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, o));
-    }
-    if (lane == 0) { s_red[0][warp] = tmax0; s_red[1][warp] = tmax1; }
-    __syncthreads();
-    float M0 = -INFINITY, M1 = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) { M0 = fmaxf(M0, s_red[0][w]); M1 = fmaxf(M1, s_red[1][w]); }
-
-    // ---------------------------------------------------------------- pass 2: P.V
-    float l0 = 0.f, l1 = 0.f, acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    {
-        // position of this warp's row j of batch `bt`: p0 + 64 bt + 8 j + warp
-        auto request = [&](int bt, uint2 (&v)[8]) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int p = p0 + 64 * bt + 8 * j + warp;
-                const bool live = p < pc;
-                ld_row8(v[j].x, v[j].y, vbase + (size_t)(live ? p : 0) * KV_DIM + lane * 4, live);
-            }
-        };
-        auto accumulate = [&](int bt, const uint2 (&v)[8]) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int i = 64 * bt + 8 * j + warp;
-                const bool live = p0 + i < pc;
-                const float pr0 = live ? __expf(sc0[i] - M0) : 0.f, pr1 = live ? __expf(sc1[i] - M1) : 0.f;
-                l0 += pr0; l1 += pr1;
-                const float f0 = bf_lo(v[j].x), f1 = bf_hi(v[j].x), f2 = bf_lo(v[j].y), f3 = bf_hi(v[j].y);
-                acc[0][0] = fmaf(pr0, f0, acc[0][0]); acc[0][1] = fmaf(pr0, f1, acc[0][1]); acc[0][2] = fmaf(pr0, f2, acc[0][2]); acc[0][3] = fmaf(pr0, f3, acc[0][3]);
-                acc[1][0] = fmaf(pr1, f0, acc[1][0]); acc[1][1] = fmaf(pr1, f1, acc[1][1]); acc[1][2] = fmaf(pr1, f2, acc[1][2]); acc[1][3] = fmaf(pr1, f3, acc[1][3]);
-            }
-        };
-        const int batches = (pc - p0 + 63) / 64;              // block-uniform
-        uint2 va[8], vb[8];                                   // two batches of eight rows in flight per warp
-        request(0, va);
-        for (int bt = 0; bt < batches; bt += 2) {
-            request(bt + 1, vb);
-            accumulate(bt, va);
-            if (bt + 1 >= batches) break;
-            request(bt + 2, va);
-            accumulate(bt + 1, vb);
-        }
-        if (has_new && warp == 0) {   // the new token's V row in fp32
-            const float4 vn = *reinterpret_cast<const float4*>(vnp + lane * 4);
-            const float pr0 = __expf(sc0[len - p0] - M0), pr1 = __expf(sc1[len - p0] - M1);
-            l0 += pr0; l1 += pr1;
-            acc[0][0] = fmaf(pr0, vn.x, acc[0][0]); acc[0][1] = fmaf(pr0, vn.y, acc[0][1]); acc[0][2] = fmaf(pr0, vn.z, acc[0][2]); acc[0][3] = fmaf(pr0, vn.w, acc[0][3]);
-            acc[1][0] = fmaf(pr1, vn.x, acc[1][0]); acc[1][1] = fmaf(pr1, vn.y, acc[1][1]); acc[1][2] = fmaf(pr1, vn.z, acc[1][2]); acc[1][3] = fmaf(pr1, vn.w, acc[1][3]);
-        }
-    }
-    *reinterpret_cast<float4*>(&s_o[warp][0][lane * 4]) = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
-    *reinterpret_cast<float4*>(&s_o[warp][1][lane * 4]) = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
-    if (lane == 0) { s_l[warp][0] = l0; s_l[warp][1] = l1; }
-    __syncthreads();
-    {
-        const int hh = tid >> 7, d = tid & 127;
-        float L = 0.f, o = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) { L += s_l[w][hh]; o += s_o[w][hh][d]; }
-        float* out = a.part + (((size_t)b * Q_HEADS + 2 * g + hh) * a.n_splits + sp) * ATTN_PART_STRIDE;
-        if (d == 0) { out[0] = hh ? M1 : M0; out[1] = L; }   // an empty chunk publishes (-inf, 0, 0)
-        out[4 + d] = o;
-    }
-    if (a.merged != nullptr) {
-        // the last block of this (sequence, kv head) to get here merges all splits of its two heads: no merge launch
-        __shared__ int s_last;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) s_last = atomicAdd(a.merge_count + b * KV_HEADS + g, 1) == a.n_splits - 1;
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-            const int hh = tid >> 7, d = tid & 127;
-            const float* p = a.part + ((size_t)b * Q_HEADS + 2 * g + hh) * a.n_splits * ATTN_PART_STRIDE;
-            float M = -INFINITY;
-            for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, __ldcg(p + s * ATTN_PART_STRIDE));
-            float L = 0.f, o = 0.f;
-            for (int s = 0; s < a.n_splits; ++s) {
-                const float ms = __ldcg(p + s * ATTN_PART_STRIDE);
-                const float w = (ms > -INFINITY) ? expf(ms - M) : 0.f;
-                L = fmaf(__ldcg(p + s * ATTN_PART_STRIDE + 1), w, L);
-                o = fmaf(__ldcg(p + s * ATTN_PART_STRIDE + 4 + d), w, o);
-            }
-            a.merged[(size_t)b * Q_DIM + (2 * g + hh) * HEAD_DIM + d] = o / L;
-            if (tid == 0) a.merge_count[b * KV_HEADS + g] = 0;
-        }
-    }
-}
-
 // attn_merge: combine the splits of one (sequence, head): grid (16, B), 128 threads
 __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ part, int n_splits, float* __restrict__ attn) {
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
@@ -767,14 +520,7 @@ cudaError_t launch_head_prep(const HeadPrepArgs& a, int batch, cudaStream_t st) 
     return launch_chain(head_prep_kernel, dim3((Q_HEADS + KV_HEADS) / 8, batch), dim3(256), 0, st, a);
 }
 
-// the split kernel: tensor-core streaming kernel (q3_attn_mma.cu), or the CUDA-core one above when built with Q3_ATTN_SPLIT
-static cudaError_t launch_split(const AttnArgs& a, int batch, cudaStream_t st) {
-#ifdef Q3_ATTN_SPLIT
-    return launch_chain(attn_split_kernel, dim3(a.n_splits, KV_HEADS, batch), dim3(256), (size_t)2 * a.chunk_pad * sizeof(float), st, a);
-#else
-    return launch_attn_mma(a, batch, st);
-#endif
-}
+static cudaError_t launch_split(const AttnArgs& a, int batch, cudaStream_t st) { return launch_attn_mma(a, batch, st); }
 
 cudaError_t launch_attn_split(const AttnArgs& a, int batch, cudaStream_t st) {
     if (a.chunk_pad < 32 || a.chunk_pad % 32 || a.chunk_pad > ATTN_CHUNK_MAX || !a.fused_prep) return cudaErrorInvalidValue;
