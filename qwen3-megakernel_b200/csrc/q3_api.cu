@@ -377,6 +377,19 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
             // x += attn @ wo^T
             LAUNCH(gemm(bf(w.wo) + (size_t)l * HIDDEN * Q_DIM, HIDDEN, Q_DIM, e->x, HIDDEN, e->x, HIDDEN));
             // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
+            // A long prompt: gate and up in one work item of the persistent GEMM, SiLU in its epilogue, the product written as
+            // the down GEMM's input plane into the second third of the plane buffer (one plane in use, so that third is free).
+            if (prompt != nullptr && tc_planes == 1 && gemm_tc_silu_fits(INTER, B)) {
+                LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st, nullptr));
+                bf16_raw* hplane = planes + (size_t)((e->cap + 127) / 128 * 128) * INTER;
+                GemmTcSiluCall c{bf(w.wg) + (size_t)l * INTER * HIDDEN, bf(w.wu) + (size_t)l * INTER * HIDDEN, planes, hplane,
+                                 INTER, B, HIDDEN, tc_planes, prow, prow, e->status};
+                LAUNCH(launch_gemm_tc_silu(c, st));
+                GemmTcCall d{bf(w.wd) + (size_t)l * HIDDEN * INTER, hplane, e->x, e->x, HIDDEN, HIDDEN, HIDDEN, B, INTER, 1, prow, e->status};
+                LAUNCH(launch_gemm_tc(d, st));
+                continue;
+            }
+            // hid = silu(rms(x, ln2) @ wg^T) * (rms(x, ln2) @ wu^T)
             const ZeroRows zf{{e->gate, e->up}, {INTER, INTER}, {INTER, INTER}};
             LAUNCH(launch_act_split(e->x, HIDDEN, HIDDEN, bf(w.ln2) + (size_t)l * HIDDEN, planes, prow, tc_planes, B, st,
                                     gemm_tc_splits_k(2 * INTER, B, HIDDEN) ? &zf : nullptr));

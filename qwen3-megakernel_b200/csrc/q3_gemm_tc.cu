@@ -227,6 +227,235 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 }
 
 // ------------------------------------------------------------------------------------------------
+// The same GEMM for prompts as a PERSISTENT kernel: one CTA per SM walks a list of work items (a tile of 128 weight rows x
+// 256 tokens).  What the one-tile-per-CTA kernel does in
+// series - fill the pipeline, the MMAs, the read-back of 128 KB of accumulator - overlaps here:
+//   * the TMA ring never drains between items (the producer runs ahead into the next item's k blocks),
+//   * two accumulators in TMEM (2 x 256 columns = all of it): the epilogue warps read item i out while the MMA thread
+//     already accumulates item i + 1,
+//   * N = 256 per tcgen05.mma halves the shared-memory operand traffic per flop against N = 128.
+// Items are numbered with the weight tile fastest, so that the CTAs of a round share a few token tiles in L2.
+// ------------------------------------------------------------------------------------------------
+//
+// DUAL: the FFN's gate and up in one item - the same 128 rows of Wg and of Wu against a tile of 128 tokens, four
+// accumulators of 128 columns - and an epilogue that writes silu(gate) * up as the bf16 plane the down GEMM reads.  The
+// fp32 gate and up matrices (2 x 25 MB per layer at 2048 tokens) and the kernel that read them back are gone, and the
+// exponentials of the epilogue hide behind the next item's MMAs.
+constexpr int TP_BN = 256;
+constexpr int TP_THREADS = 64 + 256;   // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two warps per TMEM lane quadrant, half the columns each)
+struct GemmPersistItems {
+    int n_items, m_tiles, n_ttiles;   // items = token tiles x weight tiles
+    bf16_raw* silu_out;               // DUAL: [silu_rows][n_rows] bf16
+    int silu_rows;                    // rows of that plane (multiple of 128): rows past the prompt are written as zeros
+};
+
+template <bool DUAL>
+__global__ void __launch_bounds__(TP_THREADS, 1) gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tm_w0,
+                                                                        const __grid_constant__ CUtensorMap tm_w1,
+                                                                        const __grid_constant__ CUtensorMap tm_w2,
+                                                                        const __grid_constant__ CUtensorMap tm_x, const GemmTcParams p,
+                                                                        const GemmPersistItems w) {
+    constexpr int BN = DUAL ? 128 : TP_BN;          // tokens per item
+    constexpr int ACC = DUAL ? 2 * BN : BN;         // TMEM columns of one accumulator buffer (DUAL: gate | up)
+    extern __shared__ __align__(1024) unsigned char tc_smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nsplit = p.nsplit, stages = p.stages;
+    const uint32_t a_bytes = (DUAL ? 2 : 1) * TC_BM * TC_BK * 2, b_bytes = BN * TC_BK * 2;   // DUAL: the Wg tile, then the Wu tile
+    const uint32_t stage_bytes = a_bytes + nsplit * b_bytes;
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&full_bar[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&empty_bar[s])) : "memory");
+        }
+        for (int b = 0; b < 2; ++b) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&acc_full[b])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 256;" ::"r"(tc_smem(&acc_empty[b])) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        abort_flag = 0;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&tmem_base_s)), "r"((uint32_t)(2 * ACC)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_launch();
+
+    // item -> (k slice, token tile, weight tile -> matrix of a grouped launch and row inside it)
+    struct Item { int grp, m0, n0, kb_begin, nkb; };
+    auto decode = [&](int it) {
+        Item r;
+        const int per_slice = w.m_tiles * w.n_ttiles;
+        const int ks = it / per_slice, rem = it - ks * per_slice;
+        int tile = rem % w.m_tiles;
+        r.n0 = (rem / w.m_tiles) * BN;
+        r.grp = 0;
+        if (!DUAL && p.n_groups > 1) {
+            if (tile >= p.g_tiles[0]) { tile -= p.g_tiles[0]; r.grp = 1; }
+            if (r.grp == 1 && p.n_groups > 2 && tile >= p.g_tiles[1]) { tile -= p.g_tiles[1]; r.grp = 2; }
+        }
+        r.m0 = tile * TC_BM;
+        r.kb_begin = ks * p.kb_per_split;
+        r.nkb = min(p.K / TC_BK - r.kb_begin, p.kb_per_split);
+        return r;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            pdl_wait();
+            int gi = 0;
+            for (int it = blockIdx.x; it < w.n_items && !abort_flag; it += gridDim.x) {
+                const Item r = decode(it);
+                const CUtensorMap* tm_w = r.grp == 0 ? &tm_w0 : (r.grp == 1 ? &tm_w1 : &tm_w2);
+                for (int kb = 0; kb < r.nkb; ++kb, ++gi) {
+                    const int s = gi % stages;
+                    if (gi >= stages && !tc_wait(&empty_bar[s], ((gi / stages) - 1) & 1, &abort_flag, p.status, 36)) break;
+                    unsigned char* st = base + (size_t)s * stage_bytes;
+                    asm volatile("mbarrier.arrive.expect_tx.release.cta.shared::cta.b64 _, [%0], %1;" ::"r"(tc_smem(&full_bar[s])), "r"(stage_bytes) : "memory");
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                 ::"r"(tc_smem(st)), "l"(tm_w), "r"((r.kb_begin + kb) * TC_BK), "r"(r.m0), "r"(tc_smem(&full_bar[s])) : "memory");
+                    if (DUAL)
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                     ::"r"(tc_smem(st + a_bytes / 2)), "l"(&tm_w1), "r"((r.kb_begin + kb) * TC_BK), "r"(r.m0), "r"(tc_smem(&full_bar[s])) : "memory");
+                    for (int sp = 0; sp < nsplit; ++sp)
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                     ::"r"(tc_smem(st + a_bytes + sp * b_bytes)), "l"(&tm_x), "r"((r.kb_begin + kb) * TC_BK), "r"(sp * p.plane_rows + r.n0),
+                                       "r"(tc_smem(&full_bar[s])) : "memory");
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            int gi = 0, li = 0;
+            bool ok = true;
+            for (int it = blockIdx.x; it < w.n_items && ok; it += gridDim.x, ++li) {
+                const Item r = decode(it);
+                const int acc = li & 1;
+                // the accumulator is free once the epilogue warps have read its previous tenant out
+                if (li >= 2) ok = tc_wait(&acc_empty[acc], ((li >> 1) - 1) & 1, &abort_flag, p.status, 37);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int kb = 0; kb < r.nkb && ok; ++kb, ++gi) {
+                    const int s = gi % stages;
+                    ok = tc_wait(&full_bar[s], (gi / stages) & 1, &abort_flag, p.status, 38);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = tc_smem(base + (size_t)s * stage_bytes);
+                    for (int sp = 0; sp < nsplit; ++sp) {
+                        const uint32_t sb = sa + a_bytes + sp * b_bytes;
+#pragma unroll
+                        for (int k = 0; k < TC_BK / 16; ++k) {
+                            const uint64_t da = tc_desc(sa + k * 32), db = tc_desc(sb + k * 32);
+                            const uint32_t accumulate = (kb | sp | k) ? 1u : 0u;
+                            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                                         ::"r"(tmem_base + (uint32_t)(acc * ACC)), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+                            if (DUAL) {
+                                const uint64_t du = tc_desc(sa + a_bytes / 2 + k * 32);
+                                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                                             ::"r"(tmem_base + (uint32_t)(acc * ACC + BN)), "l"(du), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+                            }
+                        }
+                    }
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&empty_bar[s])) : "memory");
+                }
+                if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&acc_full[acc])) : "memory");
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: TMEM -> registers -> global
+        const int quad = warp & 3, half = (warp - 2) >> 2;   // TMEM lanes [32 quad, +32), columns [half BN / 2, + BN / 2)
+        pdl_wait();   // before the first store (the output may be something the predecessor still reads)
+        int li = 0;
+        bool ok = true;
+        for (int it = blockIdx.x; it < w.n_items && ok; it += gridDim.x, ++li) {
+            const Item r = decode(it);
+            const int acc = li & 1;
+            float* const out = p.n_groups > 1 ? (r.grp == 0 ? p.g_out[0] : r.grp == 1 ? p.g_out[1] : p.g_out[2]) : p.out;
+            const int ldo = p.n_groups > 1 ? (r.grp == 0 ? p.g_ldo[0] : r.grp == 1 ? p.g_ldo[1] : p.g_ldo[2]) : p.ldo;
+            ok = tc_wait(&acc_full[acc], (li >> 1) & 1, &abort_flag, p.status, 39);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = r.m0 + quad * 32 + lane;    // weight row = output column (every tile is a full 128 rows)
+            if (DUAL) {
+                // Reading TMEM while the MMAs of the next item run costs about a microsecond per round trip, whatever its width:
+                // two rounds of 64 tokens (gate and up requested together, one wait) instead of sixteen narrow ones
+                for (int c = half; c == half; ++c) {   // 64 tokens: this warp's half of the item
+                    if (r.n0 + c * 64 >= w.silu_rows) break;
+                    uint32_t g[64], u[64];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * ACC + c * 64);
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+                                 : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]), "=r"(g[8]), "=r"(g[9]), "=r"(g[10]), "=r"(g[11]), "=r"(g[12]), "=r"(g[13]), "=r"(g[14]), "=r"(g[15]), "=r"(g[16]), "=r"(g[17]), "=r"(g[18]), "=r"(g[19]), "=r"(g[20]), "=r"(g[21]), "=r"(g[22]), "=r"(g[23]), "=r"(g[24]), "=r"(g[25]), "=r"(g[26]), "=r"(g[27]), "=r"(g[28]), "=r"(g[29]), "=r"(g[30]), "=r"(g[31]), "=r"(g[32]), "=r"(g[33]), "=r"(g[34]), "=r"(g[35]), "=r"(g[36]), "=r"(g[37]), "=r"(g[38]), "=r"(g[39]), "=r"(g[40]), "=r"(g[41]), "=r"(g[42]), "=r"(g[43]), "=r"(g[44]), "=r"(g[45]), "=r"(g[46]), "=r"(g[47]), "=r"(g[48]), "=r"(g[49]), "=r"(g[50]), "=r"(g[51]), "=r"(g[52]), "=r"(g[53]), "=r"(g[54]), "=r"(g[55]), "=r"(g[56]), "=r"(g[57]), "=r"(g[58]), "=r"(g[59]), "=r"(g[60]), "=r"(g[61]), "=r"(g[62]), "=r"(g[63]) : "r"(taddr) : "memory");
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+                                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]), "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]), "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31]), "=r"(u[32]), "=r"(u[33]), "=r"(u[34]), "=r"(u[35]), "=r"(u[36]), "=r"(u[37]), "=r"(u[38]), "=r"(u[39]), "=r"(u[40]), "=r"(u[41]), "=r"(u[42]), "=r"(u[43]), "=r"(u[44]), "=r"(u[45]), "=r"(u[46]), "=r"(u[47]), "=r"(u[48]), "=r"(u[49]), "=r"(u[50]), "=r"(u[51]), "=r"(u[52]), "=r"(u[53]), "=r"(u[54]), "=r"(u[55]), "=r"(u[56]), "=r"(u[57]), "=r"(u[58]), "=r"(u[59]), "=r"(u[60]), "=r"(u[61]), "=r"(u[62]), "=r"(u[63]) : "r"(taddr + (uint32_t)BN) : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    bf16_raw* dst = w.silu_out + (size_t)(r.n0 + c * 64) * p.n_rows + row;
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        const int t = r.n0 + c * 64 + j;
+                        if (t < w.silu_rows) {          // rows past the prompt are the token tile's padding: zeros
+                            const float a = __uint_as_float(g[j]), b = __uint_as_float(u[j]);
+                            const float x = t < p.n_tok ? __fdividef(a, 1.f + __expf(-a)) * b : 0.f;   // (a prompt's gates are 1e-2)
+                            dst[(size_t)j * p.n_rows] = f_to_bf(x);
+                        }
+                    }
+                }
+            } else
+#pragma unroll 1
+            for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+                if (r.n0 + c * 32 >= p.n_tok) break;    // the rest of the token tile is padding
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * ACC + c * 32);
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                               "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                               "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                               "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                             : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int t = r.n0 + c * 32 + j;
+                    if (t < p.n_tok) {
+                        float x = __uint_as_float(v[j]);
+                        float* dst = out + (size_t)t * ldo + row;
+                        if (p.epi == TC_EPI_ATOMIC) {
+                            atomicAdd(dst, x);   // split-K: `out` already holds zero or the residual
+                        } else {
+                            if (p.epi == TC_EPI_RESID) x += p.resid[(size_t)t * p.ldr + row];
+                            *dst = x;
+                        }
+                    }
+                }
+            }
+            // this accumulator may be overwritten by the item after next
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&acc_empty[acc])) : "memory");
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * ACC)) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -269,6 +498,51 @@ static int k_slices(int n_rows, int n_tok, int bn, int nkb, int sm_count) {
     int ksplit = fill * sm_count / tiles;
     if (ksplit > nkb / 2) ksplit = nkb / 2;
     return ksplit < 1 ? 1 : ksplit;
+}
+
+// A prompt's GEMM takes the persistent kernel when its 128 x 256 tiles alone fill the GPU (q/k/v and gate/up from about
+// 1200 tokens on).  Measured inside a prefill of 2048 tokens: q/k/v 23.9 us against 32.3 us, gate/up 32.7 against 36.3;
+// with K cut in slices for the launches of few tiles (Wo, down) it was no faster than the one-tile-per-CTA kernel with
+// three CTAs per SM (19.1 / 23.1 us against 19.0 / 19.0), and at 512 tokens slower throughout, so those stay there.
+static bool persist_serves(int n_rows, int n_tok, int nsplit, int plane_rows, int sm_count) {
+#ifdef Q3_NO_PERSIST_GEMM
+    return false;
+#endif
+    // one activation plane (what prompts use): with more the 256-token stages no longer fit four deep
+    (void)plane_rows;
+    return n_tok >= TP_BN && nsplit == 1 && (n_rows / TC_BM) * ((n_tok + TP_BN - 1) / TP_BN) >= sm_count;
+}
+
+template <bool DUAL>
+static cudaError_t launch_persist(const CUtensorMap* tw, const CUtensorMap& tx, GemmTcParams p, int n_rows, int n_tok, int sm_count, cudaStream_t st,
+                                  bf16_raw* silu_out = nullptr, int silu_rows = 0) {
+    constexpr int BN = DUAL ? 128 : TP_BN;
+    p.kb_per_split = p.K / TC_BK;   // K is never cut here
+    const uint32_t stage_bytes = (DUAL ? 2 : 1) * TC_BM * TC_BK * 2 + p.nsplit * BN * TC_BK * 2;
+    int stages = (int)((200u * 1024u) / stage_bytes);
+    if (stages > 8) stages = 8;
+    if (stages < 2) return cudaErrorInvalidValue;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    {
+        static bool attr_set[MAX_DEVICES] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> hold(host_lock());
+        if (!attr_set[dev]) {
+            e = cudaFuncSetAttribute(gemm_tc_persist_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+            if (e != cudaSuccess) return e;
+            attr_set[dev] = true;
+        }
+    }
+    GemmPersistItems w{};
+    w.m_tiles = n_rows / TC_BM;
+    w.n_ttiles = (n_tok + BN - 1) / BN;
+    w.n_items = w.m_tiles * w.n_ttiles;
+    w.silu_out = silu_out; w.silu_rows = silu_rows;
+    const int grid = w.n_items < sm_count ? w.n_items : sm_count;
+    return launch_chain(gemm_tc_persist_kernel<DUAL>, dim3(grid), dim3(TP_THREADS), smem, st, tw[0], tw[1], tw[2], tx, p, w);
 }
 
 template <int BN>
@@ -342,6 +616,8 @@ static bool cached_map(const void* ptr, uint64_t rows, uint64_t cols, uint32_t b
     return true;
 }
 bool gemm_tc_splits_k(int n_rows, int n_tok, int K) {
+    // (the persistent kernel never cuts K; the callers that ask pass a prompt's single plane)
+    if (persist_serves(n_rows, n_tok, 1, 0, sm_count_of_current_device())) return false;
     const int bn = n_tok <= 32 ? 32 : (n_tok <= 64 ? 64 : 128);
     return k_slices(n_rows, n_tok, bn, K / TC_BK, sm_count_of_current_device()) > 1;
 }
@@ -371,6 +647,11 @@ cudaError_t launch_gemm_tc(const GemmTcCall& c, cudaStream_t st) {
     const int sm_count = sm_count_of_current_device();
     if (sm_count < 1) return cudaErrorInvalidDevice;
     const CUtensorMap maps[3] = {tw, tw, tw};
+    if (persist_serves(c.n_rows, c.n_tok, c.nsplit, c.plane_rows, sm_count)) {
+        CUtensorMap txp;
+        if (!cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)TP_BN, &txp)) return cudaErrorUnknown;
+        return launch_persist<false>(maps, txp, p, c.n_rows, c.n_tok, sm_count, st);
+    }
     if (bn == 32) return launch_bn<32>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st);
     if (bn == 64) return launch_bn<64>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st);
     return launch_bn<128>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st);
@@ -396,9 +677,37 @@ cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st) {
     p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = TC_EPI_STORE; p.status = c.status; p.out_is_zero = c.out_is_zero;
     const int sm_count = sm_count_of_current_device();
     if (sm_count < 1) return cudaErrorInvalidDevice;
+    if (persist_serves(rows, c.n_tok, c.nsplit, c.plane_rows, sm_count)) {
+        CUtensorMap txp;
+        if (!cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, (uint32_t)TP_BN, &txp)) return cudaErrorUnknown;
+        return launch_persist<false>(maps, txp, p, rows, c.n_tok, sm_count, st);
+    }
     if (bn == 32) return launch_bn<32>(maps, tx, p, rows, c.n_tok, sm_count, st);
     if (bn == 64) return launch_bn<64>(maps, tx, p, rows, c.n_tok, sm_count, st);
     return launch_bn<128>(maps, tx, p, rows, c.n_tok, sm_count, st);
+}
+
+bool gemm_tc_silu_fits(int n_rows, int n_tok) {
+#ifdef Q3_NO_DUAL
+    return false;
+#endif
+    const int sm = sm_count_of_current_device();
+    return n_tok >= 128 && sm > 0 && (n_rows / TC_BM) * ((n_tok + 127) / 128) >= 2 * sm;
+}
+
+cudaError_t launch_gemm_tc_silu(const GemmTcSiluCall& c, cudaStream_t st) {
+    if (c.K % TC_BK || c.n_rows % TC_BM || c.nsplit != 1 || c.n_tok < 1 || c.out_rows % 128 || c.out_rows < c.n_tok)
+        return cudaErrorInvalidValue;
+    CUtensorMap maps[3], tx;
+    if (!cached_map(c.wg, (uint64_t)c.n_rows, (uint64_t)c.K, TC_BM, &maps[0])) return cudaErrorUnknown;
+    if (!cached_map(c.wu, (uint64_t)c.n_rows, (uint64_t)c.K, TC_BM, &maps[1])) return cudaErrorUnknown;
+    maps[2] = maps[0];
+    if (!cached_map(c.x_planes, (uint64_t)c.nsplit * c.plane_rows, (uint64_t)c.K, 128u, &tx)) return cudaErrorUnknown;
+    GemmTcParams p{};
+    p.n_rows = c.n_rows; p.n_tok = c.n_tok; p.K = c.K; p.nsplit = c.nsplit; p.plane_rows = c.plane_rows; p.epi = TC_EPI_STORE; p.status = c.status;
+    const int sm_count = sm_count_of_current_device();
+    if (sm_count < 1) return cudaErrorInvalidDevice;
+    return launch_persist<true>(maps, tx, p, c.n_rows, c.n_tok, sm_count, st, reinterpret_cast<bf16_raw*>(c.out_plane), c.out_rows);
 }
 
 }  // namespace q3

@@ -59,6 +59,19 @@ struct GemmTcGroupCall {
 };
 cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st);
 
+// Prompts: out_plane = the bf16 plane of silu(x wg^T) * (x wu^T), both products in one work item of the persistent kernel,
+// for the down GEMM to read; no fp32 gate / up matrices.  gemm_tc_silu_fits: the items fill the GPU at least twice.
+struct GemmTcSiluCall {
+    const void* wg;        // bf16 [n_rows, K]
+    const void* wu;        // bf16 [n_rows, K]
+    const void* x_planes;  // bf16 [nsplit, plane_rows, K]
+    void* out_plane;       // bf16 [out_rows, n_rows]; must not overlap x_planes; rows n_tok.. are written as zeros
+    int n_rows, n_tok, K, nsplit, plane_rows, out_rows;
+    uint32_t* status;
+};
+bool gemm_tc_silu_fits(int n_rows, int n_tok);
+cudaError_t launch_gemm_tc_silu(const GemmTcSiluCall& c, cudaStream_t st);
+
 // Whether a launch of n_rows weight rows (all groups together) against n_tok tokens will slice K, i.e. add partial tiles
 // into an output that must hold zeros (or the residual) beforehand.
 bool gemm_tc_splits_k(int n_rows, int n_tok, int K);
