@@ -123,6 +123,7 @@ struct PrefillAttnTcArgs {
     int plane_rows, nsplit;
     int T;
     int paired;           // the grid has half as many blocks as query tiles
+    int heavy_first;      // a one-dimensional grid of (query tile, kv group) blocks, the tiles with the most key tiles first
     uint32_t* status;
 };
 
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
     __shared__ float pm[AT_PARTS][128];   // per-row partial maxima of the column parts; reused for the partial sums at the end
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = blockIdx.y;                       // kv head; query heads 2g and 2g + 1
+    const int g = a.heavy_first ? (int)blockIdx.x % KV_HEADS : (int)blockIdx.y;   // kv head; query heads 2g and 2g + 1
     unsigned char* sQh = at_raw;
     unsigned char* sQl = sQh + AT_Q_BYTES;
     unsigned char* sP = sQl + AT_Q_BYTES;
@@ -168,8 +169,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
     const int n_qt = (a.T + AT_QT - 1) / AT_QT;
     int it0 = 0;                                    // key tiles consumed before this pass: every barrier's phase is counted on it
     for (int pass = 0; pass < 2; ++pass) {
-        const int qt = pass ? n_qt - 1 - (int)blockIdx.x : (int)blockIdx.x;
-        if (pass && (!a.paired || qt <= (int)blockIdx.x)) break;
+        const int qt = a.heavy_first ? n_qt - 1 - (int)blockIdx.x / KV_HEADS : (pass ? n_qt - 1 - (int)blockIdx.x : (int)blockIdx.x);
+        if (pass && (a.heavy_first || !a.paired || qt <= (int)blockIdx.x)) break;
         const int q0 = qt * AT_QT;
         const int n_kt = (q0 + AT_QT - 1) / AT_KT + 1;          // key tiles up to and including the diagonal one
 
@@ -387,9 +388,17 @@ cudaError_t launch_prefill_attn_tc(const float* qkv, const void* kcache_layer, c
         }
     }
     const int n_qt = (T + AT_QT - 1) / AT_QT;
-    const int paired = n_qt * KV_HEADS > 148 ? 1 : 0;   // pair a light and a heavy tile per CTA once the unpaired grid would not fit one wave
-    PrefillAttnTcArgs a{qkv, reinterpret_cast<bf16_raw*>(planes), plane_rows, nsplit, T, paired, status};
-    prefill_attn_tc_kernel<<<dim3(paired ? (n_qt + 1) / 2 : n_qt, KV_HEADS), AT_THREADS, AT_SMEM, st>>>(tk, tv, a);
+    // More blocks than SMs: one block per (query tile, kv group), dispatched in the order of their work (a query tile has
+    // 1..n key tiles), so that the SMs that finish early pick up the light tiles: greedy longest-first over all 148 SMs,
+    // where pairing a light with a heavy tile per CTA used 128 of them (measured at 2048 tokens: see the profile).
+#ifndef Q3_AT_PAIRED
+    const int heavy_first = n_qt * KV_HEADS > 148 ? 1 : 0, paired = 0;
+#else
+    const int heavy_first = 0, paired = n_qt * KV_HEADS > 148 ? 1 : 0;
+#endif
+    PrefillAttnTcArgs a{qkv, reinterpret_cast<bf16_raw*>(planes), plane_rows, nsplit, T, paired, heavy_first, status};
+    const dim3 grid = heavy_first ? dim3(n_qt * KV_HEADS) : dim3(paired ? (n_qt + 1) / 2 : n_qt, KV_HEADS);
+    prefill_attn_tc_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(tk, tv, a);
     return cudaGetLastError();
 }
 
