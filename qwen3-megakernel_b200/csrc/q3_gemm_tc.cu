@@ -110,8 +110,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         abort_flag = 0;
     }
+    // The planes of a stage lie one after the other in shared memory, each BN rows of 128 bytes: up to 256 rows they are
+    // ONE B operand of nsplit * BN columns, so a k step is one tcgen05.mma instead of nsplit (an instruction costs about 150
+    // clocks here whatever its N), and the epilogue adds the planes' column groups.  Beyond 256 columns: one MMA per plane
+    // into the same BN columns.
+    const bool wide = nsplit > 1 && nsplit * BN <= 256;
+    const uint32_t tmem_cols = wide ? (nsplit * BN <= 128 ? 128u : 256u) : (uint32_t)(BN < 32 ? 32 : BN);
     if (warp == 1) {   // TMEM allocation: one warp, power-of-two column count >= 32
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&tmem_base_s)), "r"((uint32_t)(BN < 32 ? 32 : BN)) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&tmem_base_s)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -153,8 +159,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            // instruction descriptor: D fp32, A and B bf16, both K-major, N = BN, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            // instruction descriptor: D fp32, A and B bf16, both K-major, N = BN (or all planes side by side), M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((wide ? nsplit * BN : BN) >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            const int n_mma = wide ? 1 : nsplit;
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % stages;
@@ -162,7 +169,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t sa = tc_smem(base + (size_t)s * stage_bytes);
-                for (int sp = 0; sp < nsplit; ++sp) {
+                for (int sp = 0; sp < n_mma; ++sp) {
                     const uint32_t sb = sa + a_bytes + sp * b_bytes;
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k) {
@@ -199,6 +206,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
                                "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                              : "r"(taddr) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (wide) {   // add the other planes' columns of the same tokens
+                    for (int sp = 1; sp < nsplit; ++sp) {
+                        uint32_t q[32];
+                        const uint32_t qaddr = taddr + (uint32_t)(sp * BN);
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                                     "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                                     : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]),
+                                       "=r"(q[8]), "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15]),
+                                       "=r"(q[16]), "=r"(q[17]), "=r"(q[18]), "=r"(q[19]), "=r"(q[20]), "=r"(q[21]), "=r"(q[22]), "=r"(q[23]),
+                                       "=r"(q[24]), "=r"(q[25]), "=r"(q[26]), "=r"(q[27]), "=r"(q[28]), "=r"(q[29]), "=r"(q[30]), "=r"(q[31])
+                                     : "r"(qaddr) : "memory");
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+                    }
+                }
                 if (row < n_rows) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -222,7 +246,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(BN < 32 ? 32 : BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
