@@ -17,7 +17,8 @@ fp32 decode step (oracle/) on the host cores for the same workload, a bounded nu
 
 Extra records in the line: `reference_kernel` (the reference project's own CUDA kernel timed on this GPU through its
 own launcher and timing code, from baseline/_ref, in a child process; `unavailable` with the reason otherwise),
-`batch64_ctx1024` (the replicated batched-decode configuration: 64 sequences of 1024 cached positions per GPU) and
+`batch64_ctx1024` (the replicated batched-decode configuration: 64 sequences of 1024 cached positions per GPU),
+`prefill_t2048` (a causal forward over 2048 tokens, single-GPU runs) and
 `static_ctx128` (position 128 held fixed, the case the reference's published figure is quoted on).
 """
 from __future__ import annotations
@@ -85,6 +86,29 @@ def reference_kernel_record(timeout_s: int = 240) -> dict:
         return {"unavailable": f"no answer within {timeout_s} s"}
     except Exception as e:  # noqa: BLE001
         return {"unavailable": f"{type(e).__name__}: {e}"}
+
+
+def prefill_record(dev, w: dict, tokens: int = 2048, reps: int = 3) -> dict:
+    """Milliseconds of a causal forward over `tokens` seeded random ids through `prefill.prefill` (CUDA events, median of
+    `reps` after one untimed call; includes allocating the cache), with the algorithmic flops of the projections and of the
+    causal QK^T and PV products."""
+    from qwen3mk import Megakernel, prefill as prefill_mod
+
+    ids = torch.randint(0, w["embed"].shape[0], (tokens,), generator=torch.Generator().manual_seed(0))
+    mk = Megakernel(dev, max_tokens=tokens, max_positions=max(tokens + 1, 256))
+    times = []
+    for i in range(reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        prefill_mod.prefill(w, ids, dev, engine=mk)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        if i:
+            times.append(e0.elapsed_time(e1))
+    mk.status()
+    ms = sorted(times)[len(times) // 2]
+    flop = 2.0 * tokens * 15_728_640 * 28 + 4.0 * 28 * 16 * 128 * (tokens * (tokens + 1) / 2)
+    return {"ms": ms, "tokens_per_s": tokens / ms * 1e3, "algorithmic_tflops": flop / ms / 1e9, "tokens": tokens, "activation_planes": 1}
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -352,6 +376,14 @@ def main() -> int:
         b64_us = replicas.max_over_ranks(b64["us_per_step"], dev)
         barrier()
 
+    # ---- the prompt configuration: causal forward over 2048 tokens (rank 0 of a single-GPU run) ----------------------
+    prefill_rec = None
+    if not args.skip_extras and world == 1:
+        try:
+            prefill_rec = prefill_record(dev, weights_only)
+        except Exception as e:  # noqa: BLE001
+            prefill_rec = {"unavailable": f"{type(e).__name__}: {e}"}
+
     # ---- tensor parallelism over all N GPUs: the same stream as one job instead of N replicas ------------------------
     tp_rec = None
     if world in (2, 4, 8) and not args.skip_extras:
@@ -401,6 +433,8 @@ def main() -> int:
     }
     if tp_rec is not None:
         line["tp"] = tp_rec
+    if prefill_rec is not None:
+        line["prefill_t2048"] = prefill_rec
     if b64 is not None:
         line["batch64_ctx1024"] = {"us_per_step_slowest": b64_us, "tokens_per_s_job": world * 64 * 1e6 / b64_us,
                                    "tokens_per_s_per_gpu": 64 * 1e6 / b64_us, "kernels_per_step": b64["kernels_per_step"],
