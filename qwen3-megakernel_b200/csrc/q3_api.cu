@@ -350,6 +350,7 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
         // A prompt's tokens attend rows that earlier tokens of the same launch append: those need the separate kernel.
         // A decode step prepares the heads inside the attention kernel (one launch less per layer).
         const bool fused_prep = prompt == nullptr;
+        h.skip_k_store = (prompt != nullptr && B >= 64) ? 1 : 0;   // the tcgen05 attention of a long prompt reads K from the cache
         if (!fused_prep) LAUNCH(launch_head_prep(h, B, st));
 
         AttnArgs t{};

@@ -514,6 +514,8 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t co
 // (the Wo and down launches have 128 tiles of long K: one wave of long serial CTAs unless K is cut), batch-8 decode step
 // 1322 / 1250 / 1249 us, batch 64 3017 / 3031 / 3000 us; a prompt of 128 tokens (one 128-token tile) is the exception:
 // 1.70 / 1.86 / 1.82 ms.  k blocks per slice at least 2 (batch 64 / batch 8 steps: 2 -> 3077 / 1433 us, 4 -> 3121 / 1477).
+// Capping the slices of a batch-64 launch at two CTAs per SM (what its 256 TMEM columns per CTA allow at once) was slower:
+// 2509 against 2479 us per step.
 static int sm_count_of_current_device();
 static int k_slices(int n_rows, int n_tok, int bn, int nkb, int sm_count) {
     const int tiles = ((n_rows + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);

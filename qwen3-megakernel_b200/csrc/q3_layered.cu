@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(256) head_prep_kernel(const HeadPrepArgs a) {
         const int d = (lane * 4 + i) & 63;
         v[i] = n * tab[d] + rot * tab[64 + d];
     }
-    *reinterpret_cast<float4*>(src) = make_float4(v[0], v[1], v[2], v[3]);
+    if (is_q || !a.skip_k_store) *reinterpret_cast<float4*>(src) = make_float4(v[0], v[1], v[2], v[3]);
     if (!is_q) {
         const float4 vv = *reinterpret_cast<const float4*>(a.qkv + (size_t)b * QKV_DIM + Q_DIM + KV_DIM + g * HEAD_DIM + lane * 4);
         uint2 kb, vb;
@@ -374,8 +374,22 @@ __global__ void __launch_bounds__(256) act_split_kernel(const float* __restrict_
         for (int e = 2 * tid; e < K; e += 512) store_planes2(planes, plane_rows, nsplit, K, t, e, 0.f, 0.f);
         return;
     }
-    // two neighbouring elements a thread (K is even): 8-byte loads, one 32-bit store per plane
     const float* row = x + (size_t)t * ldx;
+    if (K == 4 * 256 && (ldx & 3) == 0) {
+        // the usual width (1024): the row lives in registers, four elements a thread, read once
+        const float4 v = *reinterpret_cast<const float4*>(row + 4 * tid);
+        float4 y = v;
+        if (gain != nullptr) {
+            const float ss = block_sum<8>(fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w))), red);
+            const float r = rsqrtf(ss / (float)K + EPS);
+            const uint2 gg = *reinterpret_cast<const uint2*>(gain + 4 * tid);
+            y.x = (v.x * r) * bf_lo(gg.x); y.y = (v.y * r) * bf_hi(gg.x); y.z = (v.z * r) * bf_lo(gg.y); y.w = (v.w * r) * bf_hi(gg.y);
+        }
+        store_planes2(planes, plane_rows, nsplit, K, t, 4 * tid, y.x, y.y);
+        store_planes2(planes, plane_rows, nsplit, K, t, 4 * tid + 2, y.z, y.w);
+        return;
+    }
+    // two neighbouring elements a thread (K is even): 8-byte loads, one 32-bit store per plane
     float r = 1.f;
     if (gain != nullptr) {
         float ss = 0.f;

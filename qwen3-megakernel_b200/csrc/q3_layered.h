@@ -47,6 +47,7 @@ struct HeadPrepArgs {
     const long long* seq_layer_stride;
     int layer, n_layers, append;
     int len_bound;                    // lengths are clamped to [0, len_bound] (the embed kernel reports a longer cache)
+    int skip_k_store;                 // the prepared k rows are only needed as bf16 cache rows (a long prompt's attention reads the cache): leave qkv's k as it is
 };
 
 struct AttnArgs {

@@ -254,7 +254,13 @@ def test_prefill_matches_oracle(oracle, small, T):
     assert oracle.rel_l2(kc[:, :T], rk) <= GATE_KV_REL_L2
     assert float(kc[:, T:].abs().max()) == 0.0
     assert oracle.max_rel(last, rlast) <= GATE_MAX_REL
-    assert int(last.argmax()) == int(rlast.argmax())
+    # the arg-max agrees, or the two candidates are a near-tie inside the logit gate (one bf16 activation plane: an
+    # error of GATE_MAX_REL of the largest logit on either candidate can swap them)
+    top, want = int(last.argmax()), int(rlast.argmax())
+    if top != want:
+        margin = float(rlast[want] - rlast[top])
+        assert margin <= 2 * GATE_MAX_REL * float(rlast.abs().max()), f"arg-max {top} against {want}, margin {margin:.3e}"
+        print(f"prefill T={T}: arg-max {top} against {want} on a near-tie (margin {margin:.3e})")
 
 
 def test_error_paths():
