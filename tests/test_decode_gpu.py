@@ -237,9 +237,10 @@ def test_rebound_launches_are_stable(oracle, small, path):
     assert 0 <= int(mk.chain_token) < 4096
 
 
-@pytest.mark.parametrize("T", [5, 37, 64, 200, 700])
+@pytest.mark.parametrize("T", [5, 37, 64, 200, 700, 1600])
 def test_prefill_matches_oracle(oracle, small, T):
-    """T < 9: matrix-vector kernels; T >= 9: tcgen05 GEMMs; T >= 64: the tiled causal attention kernel."""
+    """T < 9: matrix-vector kernels; T >= 9: tcgen05 GEMMs; T >= 64: the tiled causal attention kernel; 1600: the persistent
+    GEMM (q/k/v, and gate + up with SiLU in the epilogue) with a last token tile that is partly padding."""
     from qwen3mk import prefill
 
     shp, inp, w = small
