@@ -56,8 +56,12 @@ def prefill(w: dict, ids, device="cuda", *, capacity: int | None = None, engine:
     layers, vocab = wb["wq"].shape[0], wb["embed"].shape[0]
     mk = engine if engine is not None else Megakernel(dev, layers=layers, vocab=vocab, max_tokens=n, max_positions=max(cap + 1, 256))
     mk._set_weights(wb)
-    kc = torch.zeros((layers, cap, KV_HEADS, HEAD_DIM), dtype=torch.bfloat16, device=dev)
-    vc = torch.zeros_like(kc)
+    # every slot below n is written by the launch; only the spare slots are cleared (235 MB of memset at 2048 tokens otherwise)
+    kc = torch.empty((layers, cap, KV_HEADS, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+    vc = torch.empty_like(kc)
+    if cap > n:
+        kc[:, n:].zero_()
+        vc[:, n:].zero_()
     logits = torch.empty(vocab, dtype=torch.float32, device=dev)
     nxt = torch.empty((), dtype=torch.int64, device=dev)
     a = _cabi.PrefillArgs(n, cap, ids_t.data_ptr(), kc.data_ptr(), vc.data_ptr(), logits.data_ptr(), nxt.data_ptr())
