@@ -386,7 +386,7 @@ def main() -> int:
 
     # ---- tensor parallelism over all N GPUs: the same stream as one job instead of N replicas ------------------------
     tp_rec = None
-    if world in (2, 4, 8) and not args.skip_extras:
+    if world in (2, 4, 8):
         try:
             tp_rec = tensor_parallel_record(dev, inputs, world, barrier)
         except Exception as e:  # noqa: BLE001  (the replica figures above stand on their own)
