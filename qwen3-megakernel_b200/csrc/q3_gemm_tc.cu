@@ -68,6 +68,17 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
     return d;
 }
 
+__device__ __forceinline__ void tc_ld32(uint32_t (&r)[32], uint32_t taddr) {   // 32 columns of this warp's 32 TMEM lanes; no wait
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
                                                                 const __grid_constant__ CUtensorMap tm_w1,
@@ -197,30 +208,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                             : "r"(taddr) : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (wide) {   // add the other planes' columns of the same tokens
-                    for (int sp = 1; sp < nsplit; ++sp) {
-                        uint32_t q[32];
-                        const uint32_t qaddr = taddr + (uint32_t)(sp * BN);
-                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                                     "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                                     : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]),
-                                       "=r"(q[8]), "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15]),
-                                       "=r"(q[16]), "=r"(q[17]), "=r"(q[18]), "=r"(q[19]), "=r"(q[20]), "=r"(q[21]), "=r"(q[22]), "=r"(q[23]),
-                                       "=r"(q[24]), "=r"(q[25]), "=r"(q[26]), "=r"(q[27]), "=r"(q[28]), "=r"(q[29]), "=r"(q[30]), "=r"(q[31])
-                                     : "r"(qaddr) : "memory");
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                tc_ld32(r, taddr);
+                if constexpr (BN >= 64) {
+                    // all column groups of these tokens are requested before the one wait (a TMEM round trip each otherwise:
+                    // batch 64 x 1024 2478 -> 2424 us per step).  Not for the 32-token tile: the 64 extra registers cost it
+                    // two of its five CTAs per SM (batch 8 x 1024 1083 -> 1153 us).
+                    uint32_t q1[32], q2[32];
+                    if (wide) {
+                        tc_ld32(q1, taddr + (uint32_t)BN);
+                        if (nsplit > 2) tc_ld32(q2, taddr + (uint32_t)(2 * BN));
+                    }
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (wide) {   // add the other planes' columns of the same tokens
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+                        for (int j = 0; j < 32; ++j) {
+                            float v = __uint_as_float(r[j]) + __uint_as_float(q1[j]);
+                            if (nsplit > 2) v += __uint_as_float(q2[j]);
+                            r[j] = __float_as_uint(v);
+                        }
+                    }
+                } else {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (wide) {
+                        for (int sp = 1; sp < nsplit; ++sp) {
+                            uint32_t q[32];
+                            tc_ld32(q, taddr + (uint32_t)(sp * BN));
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+                        }
                     }
                 }
                 if (row < n_rows) {
