@@ -366,6 +366,11 @@ int q3::decode_layered(q3_engine* e, const q3_decode_args* a, cudaStream_t st, i
             const bf16_raw* vc = bf(prompt->vcache) + (size_t)l * prompt->layer_stride;
             // tcgen05 attention; it writes the Wo GEMM's input planes itself
             LAUNCH(launch_prefill_attn_tc(e->qkv, kc, vc, (int)(prompt->layer_stride / KV_DIM), planes, prow, tc_planes, B, e->status, st));
+        } else if (tc && ns == 1 && fused_prep && tc_planes == 3) {
+            // one split: the attention blocks write the Wo GEMM's input planes themselves, no merge launch (the padding rows of the
+            // token tile keep whatever they held: their columns of the product are never stored)
+            t.planes_out = planes; t.plane_rows = prow;
+            LAUNCH(launch_attn_split(t, B, st));
         } else if (tc) {
             LAUNCH(launch_attn_planes(t, planes, prow, tc_planes, B, st));   // the merge writes the Wo GEMM's input planes
             ++e->launches;  // two kernels

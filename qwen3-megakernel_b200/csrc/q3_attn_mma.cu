@@ -272,6 +272,17 @@ __global__ void __launch_bounds__(AM_WARPS * 32, 8 / AM_WARPS) attn_mma_kernel(c
                 L += wgt;
                 acc = fmaf(s_new[3][d], wgt, acc);
             }
+            if (a.planes_out != nullptr && a.n_splits == 1) {   // the only split: this is the head's output (the new token is in it, so L > 0)
+                const float v = acc / L;
+                const bf16_raw h = f_to_bf(v);
+                const float r1 = v - bf_to_f(h);
+                const bf16_raw m = f_to_bf(r1);
+                bf16_raw* dst = a.planes_out + (size_t)b * Q_DIM + (size_t)(2 * g + hh) * HEAD_DIM + d;
+                dst[0] = h;
+                dst[(size_t)a.plane_rows * Q_DIM] = m;
+                dst[(size_t)2 * a.plane_rows * Q_DIM] = f_to_bf(r1 - bf_to_f(m));
+                continue;
+            }
             float* out = a.part + (((size_t)b * Q_HEADS + 2 * g + hh) * a.n_splits + sp) * ATTN_PART_STRIDE;
             if (d == 0) { out[0] = M * AM_LN2; out[1] = L; }     // an empty chunk publishes (-inf, 0, 0); the maximum in natural units
             out[4 + d] = acc;

@@ -34,7 +34,7 @@ struct GemmTcParams {
 // host-side call
 struct GemmTcCall {
     const void* w;         // bf16 [n_rows, K] row-major
-    const void* x_planes;  // bf16 [nsplit, plane_rows, K]: fp32 activations split as hi (+ mid (+ lo)); rows >= n_tok are zero
+    const void* x_planes;  // bf16 [nsplit, plane_rows, K]: fp32 activations split as hi (+ mid (+ lo)); rows >= n_tok may hold anything (their columns of the product are never stored)
     float* out;
     const float* resid;    // nullptr: plain store
     int ldo, ldr;

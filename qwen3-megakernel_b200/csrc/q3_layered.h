@@ -76,6 +76,10 @@ struct AttnArgs {
     // merge kernel follows); merge_count[b * 8 + g] counts the arrivals and is left at zero
     float* merged;
     int* merge_count;
+    // a launch of ONE split needs no merge: its blocks write the normalised output as the three bf16 planes (hi, mid, lo)
+    // [3][plane_rows][2048] the Wo GEMM reads
+    bf16_raw* planes_out;
+    int plane_rows;
 };
 
 cudaError_t launch_gemv(int K, int epi, const GemvArgs& a, int grid_x, cudaStream_t st);
