@@ -243,30 +243,26 @@ static int chunk_pad_for(int max_len, int ns) { return (((max_len + 1 + ns - 1) 
 static int splits_for(const q3_engine* e, int batch, int max_len) {
     const int n = max_len + 1;
     int by_len = (n + 31) / 32;                                   // at least 32 positions per split
-    // Small batches: about two blocks per SM (more splits only add merge work).
-    int s;
-    if (KV_HEADS * batch < e->sm_count) {
-        const int fill_blocks = 2 * e->sm_count;
-        const int by_fill = (fill_blocks + KV_HEADS * batch - 1) / (KV_HEADS * batch);
-        s = by_len < by_fill ? by_len : by_fill;
-    } else {
-        // Batches whose (sequence, kv head) pairs fill the GPU on their own (four-warp blocks, two per SM): the split count
-        // with the shortest estimated launch.  A launch takes `waves` rounds of blocks; a block costs a fixed 4 us (prologue
-        // with the head preparation, combine) plus 23 ns per position (512 bytes at half an SM's share of the copy bandwidth);
-        // more than one split adds the merge launch (5 us), one split writes the output planes itself.  Fitted to, per step:
-        // batch 64 x 1024, 1 / 2 / 3 / 4 splits: 2524 / 2623 / 2691 / 2716 us; batch 32 x 2048, 1 / 2: 2057 / 2149;
-        // batch 24 x 1024, 1 / 3: 1336 / 1463; batch 48 x 1024, 1 / 2: 2235 / 2214; batch 20 x 4096, 2 / 3: 2814 / 2415.
-        const int slots = 2 * e->sm_count, pairs = KV_HEADS * batch;
-        double best = 1e30;
-        s = 1;
-        for (int c = 1; c <= 8 && c <= by_len; ++c) {
-            const int waves = (pairs * c + slots - 1) / slots, per = (n + c - 1) / c;
-            const double t = waves * (4.0 + 0.023 * per) + (c > 1 ? 5.0 : 0.0);
-            if (t < best - 1e-9) { best = t; s = c; }
-        }
+    // The split count with the shortest estimated launch.  A launch takes `waves` rounds of blocks; a block costs a fixed
+    // 4 us (prologue with the head preparation, combine) plus its positions at the block's share of an SM's part of the copy
+    // bandwidth; more than one split adds the merge launch (5 us), one split writes the output planes itself.
+    //   Batches whose (sequence, kv head) pairs fill the GPU: four-warp blocks, two per SM, 23 ns per position.  Fitted to,
+    //   per step: batch 64 x 1024, 1 / 2 / 3 / 4 splits: 2524 / 2623 / 2691 / 2716 us; batch 32 x 2048, 1 / 2: 2057 / 2149;
+    //   batch 24 x 1024, 1 / 3: 1336 / 1463; batch 48 x 1024, 1 / 2: 2235 / 2214; batch 20 x 4096, 2 / 3: 2814 / 2415.
+    //   Smaller batches: eight-warp blocks, one per SM, 6 ns per position.  Batch 8 x 1024, 1 / 2 splits: 1000 / 1035 us;
+    //   batch 4 x 512: 882 / 920; batch 16 x 2048: 1446 / 1597.
+    const bool big = KV_HEADS * batch >= e->sm_count;
+    const int slots = (big ? 2 : 1) * e->sm_count, pairs = KV_HEADS * batch;
+    const double per_pos = big ? 0.023 : 0.006;
+    double best = 1e30;
+    int s = 1;
+    for (int c = 1; c <= 16 && c <= by_len; ++c) {
+        const int waves = (pairs * c + slots - 1) / slots, per = (n + c - 1) / c;
+        const double t = waves * (4.0 + per_pos * per) + (c > 1 ? 5.0 : 0.0);
+        if (t < best - 1e-9) { best = t; s = c; }
     }
     if (s < 1) s = 1;
-    const int by_chunk = (n + ATTN_CHUNK_MAX - 1) / ATTN_CHUNK_MAX;   // a block's scores must fit its shared memory
+    const int by_chunk = (n + ATTN_CHUNK_MAX - 1) / ATTN_CHUNK_MAX;   // a split takes at most ATTN_CHUNK_MAX positions (the launchers check it)
     if (s < by_chunk) s = by_chunk;
     if (s > e->max_splits) s = e->max_splits;
     if (e->part_slots > 0 && s * batch > e->part_slots) s = e->part_slots / batch;

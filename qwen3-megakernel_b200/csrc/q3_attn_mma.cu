@@ -21,10 +21,11 @@
 namespace q3 {
 
 // Two shapes of block.  Four warps (96 KB of stages, two blocks per SM) when the (sequence, kv head) pairs alone fill the
-// GPU: long runs per warp, few blocks.  Two warps (48 KB, four blocks per SM) for small batches, where the launch is
-// bound by latency and more, shorter blocks help.  Measured per decode step (28 launches): batch 64 x 1024 positions
-// 2524 us with four warps and one split (2691 with three splits, 2705 with eight warps), batch 8 x 1024 positions
-// 1174 us with two warps against 1232 with four.
+// GPU: long runs per warp, few blocks.  Eight warps (192 KB, one block per SM) for smaller batches, preferably with ONE
+// split, so that the block writes the output planes itself and no merge launch follows.  Measured per decode step (28
+// launches): batch 64 x 1024 positions 2524 us with four warps and one split (2691 with three splits, 2705 with eight
+// warps); batch 8 x 1024 positions 1000 us with eight warps and one split, 1085 with two warps and five splits, 1153 with
+// four warps and one split; batch 16 x 2048 1446 against 1560.
 constexpr int AM_TILE = 16;                        // positions per stage
 constexpr int AM_STAGES = 3;
 constexpr int AM_HALF = AM_TILE * 256;             // bytes of a stage's K (or V) tile: 16 rows of 128 bf16
@@ -53,7 +54,7 @@ __device__ __forceinline__ uint32_t am_transpose(uint32_t w) {   // 8 x 8 matrix
 }
 
 template <int AM_WARPS>
-__global__ void __launch_bounds__(AM_WARPS * 32, 8 / AM_WARPS) attn_mma_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(AM_WARPS * 32, AM_WARPS == 4 ? 2 : 1) attn_mma_kernel(const AttnArgs a) {
     constexpr int AM_THREADS = AM_WARPS * 32;
     pdl_launch();
     pdl_wait();
@@ -323,16 +324,16 @@ cudaError_t launch_attn_mma(const AttnArgs& a, int batch, cudaStream_t st) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!sm_count[dev]) {   // (a benign race between host threads: the same values are written)
-        constexpr size_t big = (size_t)4 * AM_STAGES * AM_STAGE, small = (size_t)2 * AM_STAGES * AM_STAGE;
-        if ((e = cudaFuncSetAttribute(attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big)) != cudaSuccess) return e;
-        if ((e = cudaFuncSetAttribute(attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small)) != cudaSuccess) return e;
+        constexpr size_t four = (size_t)4 * AM_STAGES * AM_STAGE;
+        if ((e = cudaFuncSetAttribute(attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)four)) != cudaSuccess) return e;
+        if ((e = cudaFuncSetAttribute(attn_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * four))) != cudaSuccess) return e;
         int n = 0;
         if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
         sm_count[dev] = n;
     }
     const dim3 grid(a.n_splits, KV_HEADS, batch);
     if (KV_HEADS * batch >= sm_count[dev]) return launch_chain(attn_mma_kernel<4>, grid, dim3(128), (size_t)4 * AM_STAGES * AM_STAGE, st, a);
-    return launch_chain(attn_mma_kernel<2>, grid, dim3(64), (size_t)2 * AM_STAGES * AM_STAGE, st, a);
+    return launch_chain(attn_mma_kernel<8>, grid, dim3(256), (size_t)8 * AM_STAGES * AM_STAGE, st, a);
 }
 
 }  // namespace q3
