@@ -542,17 +542,19 @@ static int k_slices(int n_rows, int n_tok, int bn, int nkb, int sm_count) {
     return ksplit < 1 ? 1 : ksplit;
 }
 
-// A prompt's GEMM takes the persistent kernel when its 128 x 256 tiles alone fill the GPU (q/k/v and gate/up from about
-// 1200 tokens on).  Measured inside a prefill of 2048 tokens: q/k/v 23.9 us against 32.3 us, gate/up 32.7 against 36.3;
-// with K cut in slices for the launches of few tiles (Wo, down) it was no faster than the one-tile-per-CTA kernel with
-// three CTAs per SM (19.1 / 23.1 us against 19.0 / 19.0), and at 512 tokens slower throughout, so those stay there.
+// A prompt's GEMM takes the persistent kernel when its 128 x 256 items occupy at least 0.6 of the SMs (q/k/v from about
+// 520 tokens on, gate + up from about 420).  Measured inside a prefill of 2048 tokens: q/k/v 23.9 us against 32.3 us,
+// gate/up 32.7 against 36.3; whole prefills with the threshold at 1.0 / 0.6 / 0.4 of the SMs: 512 tokens 2.39 / 2.28 /
+// 2.29 ms, 768 tokens 2.90 / 2.49 / 2.49, 1000 tokens 3.34 / 2.96 / 2.97, 300 tokens 2.05 / 2.05 / 2.13.  With K cut in
+// slices for the launches of few tiles (Wo, down) it was no faster than the one-tile-per-CTA kernel with three CTAs per
+// SM (19.1 / 23.1 us against 19.0 / 19.0), so those stay there.
 static bool persist_serves(int n_rows, int n_tok, int nsplit, int plane_rows, int sm_count) {
 #ifdef Q3_NO_PERSIST_GEMM
     return false;
 #endif
     // one activation plane (what prompts use): with more the 256-token stages no longer fit four deep
     (void)plane_rows;
-    return n_tok >= TP_BN && nsplit == 1 && (n_rows / TC_BM) * ((n_tok + TP_BN - 1) / TP_BN) >= sm_count;
+    return n_tok >= TP_BN && nsplit == 1 && (n_rows / TC_BM) * ((n_tok + TP_BN - 1) / TP_BN) * 10 >= sm_count * 6;
 }
 
 template <bool DUAL>
@@ -734,7 +736,7 @@ bool gemm_tc_silu_fits(int n_rows, int n_tok) {
     return false;
 #endif
     const int sm = sm_count_of_current_device();
-    return n_tok >= 128 && sm > 0 && (n_rows / TC_BM) * ((n_tok + 127) / 128) >= 2 * sm;
+    return n_tok >= 128 && sm > 0 && (n_rows / TC_BM) * ((n_tok + 127) / 128) * 10 >= sm * 6;
 }
 
 cudaError_t launch_gemm_tc_silu(const GemmTcSiluCall& c, cudaStream_t st) {

@@ -60,7 +60,7 @@ struct GemmTcGroupCall {
 cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st);
 
 // Prompts: out_plane = the bf16 plane of silu(x wg^T) * (x wu^T), both products in one work item of the persistent kernel,
-// for the down GEMM to read; no fp32 gate / up matrices.  gemm_tc_silu_fits: the items fill the GPU at least twice.
+// for the down GEMM to read; no fp32 gate / up matrices.  gemm_tc_silu_fits: the items occupy at least 0.6 of the SMs.
 struct GemmTcSiluCall {
     const void* wg;        // bf16 [n_rows, K]
     const void* wu;        // bf16 [n_rows, K]
