@@ -133,7 +133,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
     __shared__ __align__(8) uint64_t k_full[AT_STAGES], v_full[AT_STAGES], k_empty[AT_STAGES], v_empty[AT_STAGES], s_full[2], p_full, o_full[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
-    __shared__ float pm[AT_PARTS][128];   // per-row partial maxima of the column parts; reused for the partial sums at the end
+    // Per-row partial maxima of the four column parts, exchanged once per key tile with ONE barrier: two buffers, picked by the
+    // tile's parity, so that a warp that is a tile ahead never overwrites what a slower one has yet to read.  Stored as bf16
+    // rounded UP (the shared maximum only has to be an upper bound that every thread of the row agrees on), which keeps the
+    // two buffers in the 2 KB the kernel has left.  The same bytes hold the fp32 partial sums at the end.
+    __shared__ __align__(16) unsigned short pm16[2][AT_PARTS][128];
+    float (*pm)[128] = reinterpret_cast<float (*)[128]>(&pm16[0][0][0]);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = a.heavy_first ? (int)blockIdx.x % KV_HEADS : (int)blockIdx.y;   // kv head; query heads 2g and 2g + 1
@@ -303,11 +308,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_attn_tc_kernel(const __
                 float tmax = -INFINITY;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(r0[j]));
-                pm[part][row] = tmax;
+                {
+                    const uint32_t tb = __float_as_uint(tmax);   // towards +inf: truncation for negative values, carry for positive ones
+                    pm16[it & 1][part][row] = (unsigned short)((tb & 0x80000000u) ? (tb >> 16) : ((tb + 0xffffu) >> 16));
+                }
                 asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFT) : "memory");
                 float mn = m;                                   // finite from the first tile on: key 0 is visible to every row
 #pragma unroll
-                for (int q = 0; q < AT_PARTS; ++q) mn = fmaxf(mn, pm[q][row]);
+                for (int q = 0; q < AT_PARTS; ++q) mn = fmaxf(mn, __uint_as_float((uint32_t)pm16[it & 1][q][row] << 16));
                 const float c = at_ex2(m - mn);
                 m = mn;
                 float psum = 0.f;
