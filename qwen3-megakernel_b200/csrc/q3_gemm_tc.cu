@@ -538,7 +538,7 @@ static int k_slices(int n_rows, int n_tok, int bn, int nkb, int sm_count) {
     const int fill = (n_tok > 64 && n_tok < 256) ? 1 : 3;
     if (tiles >= fill * sm_count) return 1;
     int ksplit = fill * sm_count / tiles;
-    if (ksplit > nkb / 2) ksplit = nkb / 2;
+    if (ksplit > nkb / 2) ksplit = nkb / 2;   // (one / two / three k blocks per slice at least: batch 64 x 1024 2498 / 2369 / 2414 us per step)
     return ksplit < 1 ? 1 : ksplit;
 }
 
