@@ -37,9 +37,7 @@ constexpr int LK_A_STAGES = 8;                  // weight tiles in flight: 8 x 1
 constexpr int LK_B_SLOTS = 3;
 constexpr uint32_t LK_A_BYTES = 128 * 128;      // 128 weight rows x 64 k bf16
 constexpr int LK_MAX_PHASES = 4;
-#ifndef LK_WORKER_SPIN
-#define LK_WORKER_SPIN false
-#endif
+constexpr bool LK_WORKER_SPIN = false;   // the workers' waits park (try_wait)
 constexpr int LK_CHUNK = 6;                     // k blocks whose activations a builder thread requests at once (three with two source arrays)
 
 enum { LK_ZERO = 0, LK_WO = 1, LK_GU = 2, LK_DN = 3, LK_QKV = 4 };
@@ -135,9 +133,6 @@ struct LkArgs {
     int n_tok;
     int n_phases;
     int phase[LK_MAX_PHASES];
-#ifdef Q3_LK_TRACE
-    unsigned long long* trace;   // [G][16][8] time stamps of the worker thread 0 (experiments)
-#endif
 };
 
 // all worker threads of all CTAs clear n floats (n a multiple of 4, p 16-byte aligned)
@@ -219,16 +214,6 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
 
     // Arrive at the grid barrier and wait for all G CTAs (the threads of warps 1..9; the producer warp runs ahead).
     int barriers = 0;
-#ifdef Q3_LK_TRACE
-#define LK_STAMP(ph, i) do { if (a.trace && tid == 64 && a.n_phases == LK_MAX_PHASES) a.trace[((size_t)c * 16 + (ph)) * 16 + (i)] = lk_ns(); } while (0)
-#define LK_STAMP_M(ph, i) do { if (a.trace && a.n_phases == LK_MAX_PHASES) a.trace[((size_t)c * 16 + 8 + (ph)) * 16 + (i)] = lk_ns(); } while (0)
-#define LK_STAMP_W(row, i) do { if (a.trace && lane == 0 && a.n_phases == LK_MAX_PHASES) a.trace[((size_t)c * 16 + (row)) * 16 + (i)] = lk_ns(); } while (0)
-#else
-#define LK_STAMP(ph, i) do { } while (0)
-#define LK_STAMP_M(ph, i) do { } while (0)
-#define LK_STAMP_W(row, i) do { } while (0)
-#endif
-    LK_STAMP(7, 0);
     auto grid_barrier = [&]() {
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         asm volatile("bar.sync 1, %0;" ::"n"(LK_SYNCED) : "memory");
@@ -309,9 +294,7 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                 for (int kb = 0; kb < u.nkb && ok; ++kb, ++ai, ++bi) {
                     const int s = ai % LK_A_STAGES, sb = bi % LK_B_SLOTS;
                     ok = lk_wait<true>(&b_ready[sb], (bi / LK_B_SLOTS) & 1, cx, 62);
-                    LK_STAMP_M(ph, 2 * kb);
                     ok = ok && lk_wait<true>(&a_full[s], (ai / LK_A_STAGES) & 1, cx, 61);
-                    LK_STAMP_M(ph, 2 * kb + 1);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t wa = lk_smem(sA + (size_t)s * LK_A_BYTES), xb = lk_smem(sB + (size_t)sb * B_BYTES);
@@ -352,7 +335,6 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
         for (int ph = 0; ph < a.n_phases; ++ph) {
             const int kind = a.phase[ph];
             const LkUnit u = lk_unit(kind, c, G);
-            LK_STAMP(ph, 0);
             // ---- buffers nobody reads or adds into during this phase ----
             if (kind == LK_ZERO || kind == LK_WO) {
                 lk_zero(a.qkv, a.n_tok * QKV_DIM, c, G, wt);
@@ -363,7 +345,6 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                 lk_zero(a.up, a.n_tok * INTER, c, G, wt);
                 if (c == G - 1 && wt < 64) a.ssq[64 + wt] = 0.f;
             }
-            LK_STAMP(ph, 1);
             if (u.has && !abort_flag) {
                 bool ok = true;
                 if (builder) {
@@ -371,11 +352,7 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                     // blocks are requested before the first one is used: a build is one L2 round trip, not one per block
                     const bool two = kind == LK_DN;                 // two source arrays (gate and up)
                     const int ld = kind == LK_WO ? Q_DIM : kind == LK_DN ? INTER : HIDDEN;
-#ifdef Q3_LK_EXP_CONST
-                    const float* src0 = (kind == LK_WO ? a.attn : kind == LK_DN ? a.gate : a.attn) + (size_t)t * ld + kq;
-#else
                     const float* src0 = (kind == LK_WO ? a.attn : kind == LK_DN ? a.gate : a.x) + (size_t)t * ld + kq;
-#endif
                     const float* src1 = a.up + (size_t)t * INTER + kq;
                     const bf16_raw* gain = kind == LK_GU ? a.gain_ffn : a.gain_qkv;
                     const bool sums = (kind == LK_GU || kind == LK_QKV) && u.mt == 0;   // the CTAs of weight tile 0 cover every k once
@@ -433,10 +410,9 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                                     const float gg = q[2 * j][i] * r_tok;
                                     q[2 * j][i] = __fdividef(gg, 1.f + __expf(-gg)) * (q[2 * j + 1][i] * r_tok);
                                 }
-                            LK_STAMP(ph, 6);
 #pragma unroll
                             for (int j = 0; j < LK_CHUNK / 2; ++j)
-                                if (ok && kb0 + j < u.nkb) { ok = emit(q[2 * j]); LK_STAMP(ph, 7 + j); }
+                                if (ok && kb0 + j < u.nkb) ok = emit(q[2 * j]);
                         } else {
 #pragma unroll
                             for (int j = 0; j < LK_CHUNK; ++j) load8(q[j], src0 + (size_t)(u.kb0 + kb0 + j) * 64, live && kb0 + j < u.nkb);
@@ -451,13 +427,11 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                                     }
                                 }
                             }
-                            LK_STAMP(ph, 6);
 #pragma unroll
                             for (int j = 0; j < LK_CHUNK; ++j)
-                                if (ok && kb0 + j < u.nkb) { ok = emit(q[j]); LK_STAMP(ph, 7 + j); }
+                                if (ok && kb0 + j < u.nkb) ok = emit(q[j]);
                         }
                     }
-                    LK_STAMP_W(12 + ph, warp - 2);
                     if (sums) {   // (uniform over the warp: the kind and the tile are the CTA's)
                         ss += __shfl_xor_sync(0xffffffffu, ss, 1);
                         ss += __shfl_xor_sync(0xffffffffu, ss, 2);
@@ -467,10 +441,8 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                 } else {
                     bi += u.nkb;
                 }
-                LK_STAMP(ph, 2);
                 // ---- epilogue: the partial tile is added into the output (x itself for Wo and down) ----
                 if (ok) ok = lk_wait<LK_WORKER_SPIN>(&acc_full, ui & 1, cx, 64);
-                LK_STAMP(ph, 3);
                 ++ui;
                 if (ok) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -495,9 +467,7 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
             } else if (u.has) {
                 bi += u.nkb; ++ui;
             }
-            LK_STAMP(ph, 4);
             if (ph + 1 < a.n_phases) grid_barrier();
-            LK_STAMP(ph, 5);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -549,9 +519,6 @@ cudaError_t launch_layer_tc(q3_engine* e, int mode, int layer, int n_tok, cudaSt
     }
     a.gain_ffn = ln2 + (size_t)a.layer * HIDDEN;
     a.gain_qkv = ln1 + (size_t)(a.layer_qkv < L ? a.layer_qkv : 0) * HIDDEN;
-#ifdef Q3_LK_TRACE
-    a.trace = e->trace_words >= (int64_t)e->sm_count * 256 ? e->trace : nullptr;
-#endif
 
     const int bn = n_tok <= 32 ? 32 : 64;
     auto kernel = bn == 32 ? layer_tc_kernel<32> : layer_tc_kernel<64>;
