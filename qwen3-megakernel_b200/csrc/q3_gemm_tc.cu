@@ -549,9 +549,6 @@ static int k_slices(int n_rows, int n_tok, int bn, int nkb, int sm_count) {
 // slices for the launches of few tiles (Wo, down) it was no faster than the one-tile-per-CTA kernel with three CTAs per
 // SM (19.1 / 23.1 us against 19.0 / 19.0), so those stay there.
 static bool persist_serves(int n_rows, int n_tok, int nsplit, int plane_rows, int sm_count) {
-#ifdef Q3_NO_PERSIST_GEMM
-    return false;
-#endif
     // one activation plane (what prompts use): with more the 256-token stages no longer fit four deep
     (void)plane_rows;
     return n_tok >= TP_BN && nsplit == 1 && (n_rows / TC_BM) * ((n_tok + TP_BN - 1) / TP_BN) * 10 >= sm_count * 6;
@@ -732,9 +729,6 @@ cudaError_t launch_gemm_tc_group(const GemmTcGroupCall& c, cudaStream_t st) {
 }
 
 bool gemm_tc_silu_fits(int n_rows, int n_tok) {
-#ifdef Q3_NO_DUAL
-    return false;
-#endif
     const int sm = sm_count_of_current_device();
     return n_tok >= 128 && sm > 0 && (n_rows / TC_BM) * ((n_tok + 127) / 128) * 10 >= sm * 6;
 }

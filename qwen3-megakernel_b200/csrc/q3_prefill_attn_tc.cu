@@ -399,11 +399,7 @@ cudaError_t launch_prefill_attn_tc(const float* qkv, const void* kcache_layer, c
     // More blocks than SMs: one block per (query tile, kv group), dispatched in the order of their work (a query tile has
     // 1..n key tiles), so that the SMs that finish early pick up the light tiles: greedy longest-first over all 148 SMs,
     // where pairing a light with a heavy tile per CTA used 128 of them (measured at 2048 tokens: see the profile).
-#ifndef Q3_AT_PAIRED
     const int heavy_first = n_qt * KV_HEADS > 148 ? 1 : 0, paired = 0;
-#else
-    const int heavy_first = 0, paired = n_qt * KV_HEADS > 148 ? 1 : 0;
-#endif
     PrefillAttnTcArgs a{qkv, reinterpret_cast<bf16_raw*>(planes), plane_rows, nsplit, T, paired, heavy_first, status};
     const dim3 grid = heavy_first ? dim3(n_qt * KV_HEADS) : dim3(paired ? (n_qt + 1) / 2 : n_qt, KV_HEADS);
     prefill_attn_tc_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(tk, tv, a);
