@@ -15,8 +15,9 @@
 // S and PV are double-buffered in TMEM (all 512 columns): the MMA thread issues S of tile t + 1 before it waits for P
 // of tile t, and the softmax warps fold PV of tile t - 1 into O after they have posted P of tile t, so the exponentials
 // (the bottleneck: 16 K of them per tile on the SFUs) run back to back while the tensor pipe works beside them.
-// A CTA takes a light and a heavy causal query tile (i and n - 1 - i), like the kernel it replaces, so the grid is
-// one even wave.  Every mbarrier wait is bounded.
+// Long prompts launch one block per (query tile, kv group) in order of work (a query tile has 1..n key tiles), so that
+// the SMs that finish early pick up the light tiles; short ones a (query tile, kv group) grid.  Every mbarrier wait is
+// bounded.
 //
 // Replaces the [16, T, T] masked score matrix of the reference's prefill (qwen3mk/prefill.py:71-75).
 #include <cuda.h>
