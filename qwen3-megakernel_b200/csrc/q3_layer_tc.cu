@@ -52,8 +52,8 @@ struct LkCtx {
 };
 
 // SPIN: poll (mbarrier.test_wait; the lowest latency, for the two single-thread roles).  Otherwise try_wait, which parks
-// the thread until the phase completes or a time slice ends: five hundred polling threads would take the shared-memory
-// bandwidth the tensor core reads its operands with.
+// the thread until the phase completes or a time slice ends and leaves the issue slots to the warps that still build
+// (measured equal to polling for the phase times).
 template <bool SPIN>
 __device__ __forceinline__ bool lk_wait(uint64_t* bar, uint32_t parity, const LkCtx& cx, uint32_t site) {
     unsigned it = 0;
@@ -176,6 +176,9 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                                                                  const __grid_constant__ CUtensorMap tm_wg, const __grid_constant__ CUtensorMap tm_wu,
                                                                  const __grid_constant__ CUtensorMap tm_wd, const LkArgs a) {
     constexpr uint32_t PLANE = BN * 128, B_BYTES = 3 * PLANE;
+    // the three planes of a slot lie one after the other: ONE B operand of 3 BN columns, one tcgen05.mma per k step (an
+    // instruction costs about 150 clocks here whatever its N); the epilogue adds the three column groups
+    constexpr uint32_t TMEM_COLS = 3 * BN <= 128 ? 128u : 256u;
     extern __shared__ __align__(1024) unsigned char lk_raw[];
     __shared__ __align__(8) uint64_t a_full[LK_A_STAGES], a_empty[LK_A_STAGES], b_ready[LK_B_SLOTS], b_free[LK_B_SLOTS], acc_full;
     __shared__ uint32_t tmem_base_s;
@@ -201,7 +204,7 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
         abort_flag = 0;
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lk_smem(&tmem_base_s)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(lk_smem(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -289,7 +292,7 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
             const LkUnit u = lk_unit(a.phase[ph], c, G);
             if (lane == 0 && u.has && !abort_flag) {
                 // D fp32, A and B bf16, both K-major, M 128, N = BN
-                const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+                const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((3 * BN) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
                 bool ok = true;
                 for (int kb = 0; kb < u.nkb && ok; ++kb, ++ai, ++bi) {
                     const int s = ai % LK_A_STAGES, sb = bi % LK_B_SLOTS;
@@ -298,12 +301,11 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t wa = lk_smem(sA + (size_t)s * LK_A_BYTES), xb = lk_smem(sB + (size_t)sb * B_BYTES);
-#pragma unroll
-                    for (int pl = 0; pl < 3; ++pl) {
+                    {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint64_t da = lk_desc(wa + k * 32), db = lk_desc(xb + pl * PLANE + k * 32);
-                            const uint32_t accumulate = (kb | pl | k) ? 1u : 0u;
+                            const uint64_t da = lk_desc(wa + k * 32), db = lk_desc(xb + k * 32);
+                            const uint32_t accumulate = (kb | k) ? 1u : 0u;
                             asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                                          "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
                                          ::"r"(tmem_base), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
@@ -454,9 +456,14 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
                         out = up ? a.up : a.gate; ldo = INTER; col0 = (u.mt - (up ? INTER / 128 : 0)) * 128;
                     } else { out = a.qkv; ldo = QKV_DIM; col0 = u.mt * 128; }
                     constexpr int NC = BN / 4;
-                    uint32_t r[NC];
-                    lk_tmem_ld<NC>(r, tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(part * NC));
+                    uint32_t r[NC], r1[NC], r2[NC];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(part * NC);
+                    lk_tmem_ld<NC>(r, taddr);
+                    lk_tmem_ld<NC>(r1, taddr + (uint32_t)BN);
+                    lk_tmem_ld<NC>(r2, taddr + (uint32_t)(2 * BN));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r1[j]) + __uint_as_float(r2[j]));
                     float* dst = out + col0 + quad * 32 + lane;
 #pragma unroll
                     for (int j = 0; j < NC; ++j) {
@@ -475,7 +482,7 @@ __global__ void __launch_bounds__(LK_THREADS, 1) layer_tc_kernel(const __grid_co
     if (c == 0 && tid == 64 && !abort_flag) a.sync[1] = epoch + (unsigned long long)G * (unsigned long long)(a.n_phases - 1);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
