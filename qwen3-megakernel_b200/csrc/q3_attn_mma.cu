@@ -273,7 +273,11 @@ __global__ void __launch_bounds__(AM_WARPS * 32, AM_WARPS == 4 ? 2 : 1) attn_mma
                 L += wgt;
                 acc = fmaf(s_new[3][d], wgt, acc);
             }
-            if (a.planes_out != nullptr && a.n_splits == 1) {   // the only split: this is the head's output (the new token is in it, so L > 0)
+            if (a.merged != nullptr && a.n_splits == 1) {       // the only split: this is the head's output (the new token is in it, so L > 0)
+                a.merged[(size_t)b * Q_DIM + (size_t)(2 * g + hh) * HEAD_DIM + d] = acc / L;
+                continue;
+            }
+            if (a.planes_out != nullptr && a.n_splits == 1) {   // ... or as the three bf16 planes
                 const float v = acc / L;
                 const bf16_raw h = f_to_bf(v);
                 const float r1 = v - bf_to_f(h);
@@ -289,7 +293,7 @@ __global__ void __launch_bounds__(AM_WARPS * 32, AM_WARPS == 4 ? 2 : 1) attn_mma
             out[4 + d] = acc;
         }
     }
-    if (a.merged != nullptr) {
+    if (a.merged != nullptr && a.n_splits > 1) {
         // the last block of this (sequence, kv head) to get here merges all splits of its two heads: no merge launch
         __threadfence();
         __syncthreads();
